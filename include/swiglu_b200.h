@@ -1,0 +1,148 @@
+/*
+ * swiglu_b200.h - C ABI of libswiglu_b200.so, the B200 (sm_100a) fused SwiGLU
+ * gate/up stage.
+ *
+ * The library replaces, for one hot path, the launch layer + CUDA kernels of
+ * tongzhou8086/swiglu_fused.  Citations are paths inside that project.
+ *
+ * Conventions
+ *   - every tensor is bf16, row-major, addressed by a raw device pointer and a
+ *     leading dimension (row pitch) in ELEMENTS;
+ *   - pointers must be 16-byte aligned and every leading dimension a multiple
+ *     of 8 elements (TMA needs 16-byte rows); K and N must be multiples of 8;
+ *     M is arbitrary (ragged tiles are zero-filled on load, clipped on store);
+ *   - inputs are borrowed for the duration of the enqueue only; the library
+ *     never allocates device memory and never synchronises unless stated;
+ *   - `stream` is a cudaStream_t / CUstream passed as void* (NULL = default);
+ *   - functions return 0 on success, a negative sgl_status on invalid use and a
+ *     positive cudaError_t value when the CUDA runtime or driver failed;
+ *     sgl_last_error() describes the last failure of the calling thread.
+ */
+#ifndef SWIGLU_B200_H_
+#define SWIGLU_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum sgl_status {
+  SGL_OK = 0,
+  SGL_ERR_NULL_POINTER = -1,
+  SGL_ERR_BAD_SHAPE = -2,      /* M,N,K < 1, or K/N not a multiple of 8 */
+  SGL_ERR_BAD_STRIDE = -3,     /* leading dimension too small or not a multiple of 8 */
+  SGL_ERR_MISALIGNED = -4,     /* pointer or column offset not 16-byte aligned */
+  SGL_ERR_BAD_CONFIG = -5,     /* tile configuration not supported / does not fit */
+  SGL_ERR_NO_DRIVER = -6,      /* cuTensorMapEncodeTiled could not be resolved */
+  SGL_ERR_UNSUPPORTED_DEVICE = -7, /* current device is not compute capability 10.x */
+  SGL_ERR_TENSOR_MAP = -8,     /* cuTensorMapEncodeTiled rejected a descriptor */
+  SGL_ERR_DEVICE_STATUS = -9,  /* a kernel reported a bounded-wait timeout */
+  SGL_ERR_BAD_ARGUMENT = -10
+} sgl_status;
+
+/* Operator forms. */
+enum { SGL_FORM_SILU_MUL = 0, SGL_FORM_FUSED_SWIGLU = 1 };
+
+/*
+ * One entry of the tile table.  Replaces the reference's (BN, BK, NS, GSM)
+ * tuples, swiglu/matmul_silu_mul.py:30-41 and swiglu/matmul_fused_swiglu.py:34-41.
+ * BM is 128 rows per CTA and the accumulator is 256 columns wide in every entry.
+ */
+typedef struct sgl_config {
+  int32_t cta_group; /* 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
+  int32_t block_k;   /* 64 or 128 */
+  int32_t stages;    /* shared-memory ring depth; 0 = deepest that fits */
+  int32_t group_m;   /* GROUP_SIZE_M of the tile order, in cluster-tile rows; >= 1 */
+  int32_t max_ctas;  /* cap on the persistent grid (0 = all SMs); for tests and sweeps */
+  int32_t reserved[3];
+} sgl_config;
+
+/*
+ * h[M,N] = silu(x[M,K] @ w_gate[K,N]) * up[M,N]
+ * Replaces matmul_silu_mul / _launch (swiglu/matmul_silu_mul.py:78-95,142-161)
+ * and the kernels matmul_silu_mul_bm128_* (swiglu/_matmul_silu_mul.cu:657-681).
+ * cfg may be NULL: the built-in tile table chooses.
+ */
+int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void* h, int64_t M,
+                        int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldup, int64_t ldh,
+                        const sgl_config* cfg, void* stream);
+
+/*
+ * h[M,N] = silu(x @ w[:, gate_col0 : gate_col0+N]) * (x @ w[:, up_col0 : up_col0+N])
+ * For the reference's packed weight W[K,2N] = [W_up | W_gate] pass up_col0 = 0,
+ * gate_col0 = N, ldw = 2N.  Other offsets let a column-parallel shard address
+ * the unsplit weight in place.  Replaces matmul_fused_swiglu / _launch
+ * (swiglu/matmul_fused_swiglu.py:85-103,152-172) and the kernels
+ * matmul_fused_swiglu_bm128_* (swiglu/_matmul_fused_swiglu.cu:513-533).
+ * x is streamed once: both products come from one K loop.
+ */
+int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
+                            int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
+                            int64_t gate_col0, const sgl_config* cfg, void* stream);
+
+/*
+ * Tile table access.  Replaces the module-level config lists and _legal /
+ * _legal_for_problem (swiglu/matmul_silu_mul.py:46-51,101-111).
+ * sgl_config_count: number of built-in configurations for a form.
+ * sgl_config_get:   copy configuration i (stages filled in with the deepest ring).
+ * sgl_config_default: the configuration a NULL cfg would use for this problem.
+ * sgl_config_smem_bytes: dynamic shared memory a configuration needs, or a
+ *                   negative sgl_status if it is not supported.
+ */
+int sgl_config_count(int form);
+int sgl_config_get(int form, int index, sgl_config* out);
+int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* out);
+int sgl_config_smem_bytes(int form, const sgl_config* cfg);
+
+/*
+ * Tile order of the persistent schedule: the (tile row, tile column) that linear
+ * tile index t maps to.  Host copy of the device function, exported so the
+ * order can be checked without a GPU.  Counterpart of the block-id swizzle in
+ * swiglu/_matmul_silu_mul.cu:357-384.
+ */
+int sgl_tile_coord(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m, int64_t* tile_m,
+                   int64_t* tile_n);
+
+/* Queries about the current device (no counterpart in the reference). */
+enum {
+  SGL_QUERY_SM_COUNT = 0,
+  SGL_QUERY_MAX_SMEM_OPTIN = 1,
+  SGL_QUERY_COMPUTE_CAPABILITY = 2, /* major*10 + minor */
+  SGL_QUERY_KERNEL_LAUNCHES = 3     /* kernels launched by this process through this library */
+};
+int sgl_query(int what, int64_t* out);
+
+/*
+ * Contiguous balanced partition used by the multi-GPU launchers: shard `rank`
+ * of `world` gets [*begin, *begin + *count) of `total` items, every boundary a
+ * multiple of `align` (the last shard takes the ragged tail).  Rows of x/h for
+ * the M-sharded launch, columns of W/h for the column-parallel launch.  The
+ * reference is single-GPU; this has no counterpart there.
+ */
+int sgl_shard_range(int64_t total, int64_t align, int world, int rank, int64_t* begin,
+                    int64_t* count);
+
+/*
+ * Device-side error record.  Every wait inside the kernels is bounded; a wait
+ * that runs out records {code, block, detail, count} and the kernel exits.
+ * sgl_device_status synchronises the current device, copies the 8 status words
+ * to `words` (may be NULL), clears them, and returns SGL_ERR_DEVICE_STATUS if a
+ * code was recorded.  The reference's waits spin forever
+ * (swiglu/_matmul_silu_mul.cu:152-161).
+ */
+int sgl_device_status(uint32_t* words);
+/* Per-wait time limit in nanoseconds for kernels launched afterwards (default 2e9). */
+int sgl_set_wait_limit_ns(uint64_t ns);
+
+/* Message for the last non-zero return on the calling thread ("" if none). */
+const char* sgl_last_error(void);
+
+/* Library version, major*100 + minor. */
+int sgl_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* SWIGLU_B200_H_ */

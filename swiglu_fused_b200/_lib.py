@@ -1,0 +1,211 @@
+"""ctypes binding of ``libswiglu_b200.so`` (the C ABI in ``include/swiglu_b200.h``).
+
+There is no fallback: if the library is missing, or the device is not a B200,
+the operators raise.  Nothing in this package computes on the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+from dataclasses import dataclass
+
+from . import build as _build
+
+FORM_SILU_MUL = 0
+FORM_FUSED_SWIGLU = 1
+
+QUERY_SM_COUNT = 0
+QUERY_MAX_SMEM_OPTIN = 1
+QUERY_COMPUTE_CAPABILITY = 2
+QUERY_KERNEL_LAUNCHES = 3
+
+# Every symbol include/swiglu_b200.h declares.
+EXPORTED_SYMBOLS = (
+    "sgl_matmul_silu_mul",
+    "sgl_matmul_fused_swiglu",
+    "sgl_config_count",
+    "sgl_config_get",
+    "sgl_config_default",
+    "sgl_config_smem_bytes",
+    "sgl_tile_coord",
+    "sgl_query",
+    "sgl_shard_range",
+    "sgl_device_status",
+    "sgl_set_wait_limit_ns",
+    "sgl_last_error",
+    "sgl_version",
+)
+
+
+class SglConfig(C.Structure):
+    """Mirror of ``struct sgl_config``."""
+
+    _fields_ = [
+        ("cta_group", C.c_int32),
+        ("block_k", C.c_int32),
+        ("stages", C.c_int32),
+        ("group_m", C.c_int32),
+        ("max_ctas", C.c_int32),
+        ("reserved", C.c_int32 * 3),
+    ]
+
+
+@dataclass(frozen=True)
+class TileConfig:
+    """One tile-table entry: the (cta_group, block_k, stages, group_m) the kernel runs with.
+
+    Counterpart of the reference's ``(BN, BK, NS, GSM)`` tuples
+    (``swiglu/matmul_silu_mul.py:30-41``).
+    """
+
+    cta_group: int = 2
+    block_k: int = 64
+    stages: int = 0
+    group_m: int = 8
+    max_ctas: int = 0
+
+    def to_c(self) -> SglConfig:
+        return SglConfig(self.cta_group, self.block_k, self.stages, self.group_m, self.max_ctas,
+                         (C.c_int32 * 3)(0, 0, 0))
+
+    @staticmethod
+    def from_c(c: SglConfig) -> "TileConfig":
+        return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas)
+
+
+class SglError(RuntimeError):
+    """A non-zero status from the library."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"libswiglu_b200 status {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+_lock = threading.Lock()
+_lib = None
+
+
+def lib_path() -> str:
+    return os.environ.get("SWIGLU_B200_LIB", _build.LIB_PATH)
+
+
+def load() -> C.CDLL:
+    """Load (once) and prototype the shared library."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        path = lib_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m swiglu_fused_b200.build` "
+                "(needs nvcc); there is no fallback path")
+        lib = C.CDLL(path)
+        i64, vp, ip = C.c_int64, C.c_void_p, C.c_int
+        cfgp = C.POINTER(SglConfig)
+        lib.sgl_matmul_silu_mul.restype = ip
+        lib.sgl_matmul_silu_mul.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
+                                            cfgp, vp]
+        lib.sgl_matmul_fused_swiglu.restype = ip
+        lib.sgl_matmul_fused_swiglu.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
+                                                i64, cfgp, vp]
+        lib.sgl_config_count.restype = ip
+        lib.sgl_config_count.argtypes = [ip]
+        lib.sgl_config_get.restype = ip
+        lib.sgl_config_get.argtypes = [ip, ip, cfgp]
+        lib.sgl_config_default.restype = ip
+        lib.sgl_config_default.argtypes = [ip, i64, i64, i64, cfgp]
+        lib.sgl_config_smem_bytes.restype = ip
+        lib.sgl_config_smem_bytes.argtypes = [ip, cfgp]
+        lib.sgl_tile_coord.restype = ip
+        lib.sgl_tile_coord.argtypes = [i64, i64, i64, i64, C.POINTER(i64), C.POINTER(i64)]
+        lib.sgl_query.restype = ip
+        lib.sgl_query.argtypes = [ip, C.POINTER(i64)]
+        lib.sgl_shard_range.restype = ip
+        lib.sgl_shard_range.argtypes = [i64, i64, ip, ip, C.POINTER(i64), C.POINTER(i64)]
+        lib.sgl_device_status.restype = ip
+        lib.sgl_device_status.argtypes = [C.POINTER(C.c_uint32)]
+        lib.sgl_set_wait_limit_ns.restype = ip
+        lib.sgl_set_wait_limit_ns.argtypes = [C.c_uint64]
+        lib.sgl_last_error.restype = C.c_char_p
+        lib.sgl_last_error.argtypes = []
+        lib.sgl_version.restype = ip
+        lib.sgl_version.argtypes = []
+        _lib = lib
+    return _lib
+
+
+def check(code: int) -> int:
+    """Raise on a non-zero status.  Invalid-argument codes become ValueError."""
+    if code == 0:
+        return 0
+    msg = load().sgl_last_error().decode("utf-8", "replace")
+    if -5 <= code <= -1 or code == -10:
+        raise ValueError(f"libswiglu_b200 status {code}: {msg}")
+    raise SglError(code, msg)
+
+
+def query(what: int) -> int:
+    out = C.c_int64(0)
+    check(load().sgl_query(what, C.byref(out)))
+    return out.value
+
+
+def kernel_launches() -> int:
+    """Kernels this process has launched through the library."""
+    return query(QUERY_KERNEL_LAUNCHES)
+
+
+def builtin_configs(form: int) -> list[TileConfig]:
+    lib = load()
+    n = lib.sgl_config_count(form)
+    if n < 0:
+        check(n)
+    out = []
+    for i in range(n):
+        c = SglConfig()
+        check(lib.sgl_config_get(form, i, C.byref(c)))
+        out.append(TileConfig.from_c(c))
+    return out
+
+
+def default_config(form: int, M: int, N: int, K: int) -> TileConfig:
+    c = SglConfig()
+    check(load().sgl_config_default(form, M, N, K, C.byref(c)))
+    return TileConfig.from_c(c)
+
+
+def config_smem_bytes(form: int, cfg: TileConfig) -> int:
+    c = cfg.to_c()
+    n = load().sgl_config_smem_bytes(form, C.byref(c))
+    if n < 0:
+        check(n)
+    return n
+
+
+def tile_coord(t: int, tiles_m: int, tiles_n: int, group_m: int) -> tuple[int, int]:
+    m, n = C.c_int64(), C.c_int64()
+    check(load().sgl_tile_coord(t, tiles_m, tiles_n, group_m, C.byref(m), C.byref(n)))
+    return m.value, n.value
+
+
+def shard_range(total: int, align: int, world: int, rank: int) -> tuple[int, int]:
+    b, c = C.c_int64(), C.c_int64()
+    check(load().sgl_shard_range(total, align, world, rank, C.byref(b), C.byref(c)))
+    return b.value, c.value
+
+
+def device_status() -> list[int]:
+    """Synchronise, fetch and clear the kernels' error record; raise if one was set."""
+    words = (C.c_uint32 * 8)()
+    code = load().sgl_device_status(words)
+    check(code)
+    return list(words)
+
+
+def set_wait_limit_ns(ns: int) -> None:
+    check(load().sgl_set_wait_limit_ns(ns))

@@ -1,0 +1,530 @@
+// C ABI of libswiglu_b200.so: argument validation, TMA descriptor encoding,
+// tile-table lookup and the kernel launches.  Replaces the reference's Python
+// launch layer (swiglu/matmul_silu_mul.py:62-95, swiglu/matmul_fused_swiglu.py:71-103),
+// its ctypes TMA helper (swiglu/_tma_utils.py:69-111) and its nvcc JIT loader
+// (swiglu/_pycuda_loader.py:128-144; this library is built ahead of time).
+//
+// No function here allocates device memory or synchronises, except
+// sgl_device_status, which is a debugging aid and says so.
+
+#include "../../include/swiglu_b200.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <string>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "swiglu_kernel.cuh"
+
+namespace {
+
+thread_local std::string t_last_error;
+std::atomic<int64_t> g_launches{0};
+std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  // Clear the sticky-free error so later calls are not poisoned by this one.
+  cudaGetLastError();
+  return fail(static_cast<int>(e), "%s: %s (%s)", what, cudaGetErrorName(e),
+              cudaGetErrorString(e));
+}
+
+// ---------------------------------------------------------------- driver entry point
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Rank-2 bf16 map over a row-major [rows, cols] tensor with row pitch `ld`
+// elements; box = box_cols (<= 64, one 128-byte swizzle row) x box_rows.
+int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld,
+             int box_rows, int box_cols, CUtensorMapL2promotion promo, const char* name) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(SGL_ERR_NO_DRIVER, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return fail(SGL_ERR_TENSOR_MAP,
+                "cuTensorMapEncodeTiled(%s) failed with CUresult %d (rows=%lld cols=%lld ld=%lld)",
+                name, static_cast<int>(r), static_cast<long long>(rows),
+                static_cast<long long>(cols), static_cast<long long>(ld));
+  }
+  return SGL_OK;
+}
+
+// ---------------------------------------------------------------- kernel variants
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                          const CUtensorMap, const sgl::KernelParams);
+
+struct Variant {
+  KernelFn fn;
+  int out_cols;
+  int stage_bytes;
+  int max_stages;
+  int (*smem_bytes)(int);
+};
+
+template <int F, int G, int BK>
+int smem_bytes_of(int stages) {
+  return sgl::KernelTraits<F, G, BK>::smem_bytes(stages);
+}
+
+template <int F, int G, int BK>
+Variant make_variant() {
+  using T = sgl::KernelTraits<F, G, BK>;
+  Variant v;
+  v.fn = sgl::swiglu_kernel<F, G, BK>;
+  v.out_cols = T::kOutCols;
+  v.stage_bytes = T::kStageBytes;
+  v.max_stages = T::max_stages();
+  v.smem_bytes = smem_bytes_of<F, G, BK>;
+  return v;
+}
+
+// Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
+const Variant& variant(int form, int cta_group, int block_k) {
+  static const Variant table[8] = {
+      make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
+      make_variant<sgl::FORM_SILU_MUL, 2, 64>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128>(),
+      make_variant<sgl::FORM_FUSED, 1, 64>(),     make_variant<sgl::FORM_FUSED, 1, 128>(),
+      make_variant<sgl::FORM_FUSED, 2, 64>(),     make_variant<sgl::FORM_FUSED, 2, 128>(),
+  };
+  return table[form * 4 + (cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
+}
+
+bool config_fields_ok(const sgl_config& c) {
+  return (c.cta_group == 1 || c.cta_group == 2) && (c.block_k == 64 || c.block_k == 128) &&
+         c.stages >= 0 && c.stages <= sgl::kMaxStages && c.group_m >= 1 && c.max_ctas >= 0;
+}
+
+// Built-in tile table (cta_group, block_k, stages (0 = deepest), group_m).
+const sgl_config kTable[] = {
+    {2, 64, 0, 8, 0, {0, 0, 0}},  {2, 64, 0, 4, 0, {0, 0, 0}},  {2, 64, 0, 16, 0, {0, 0, 0}},
+    {2, 64, 0, 1, 0, {0, 0, 0}},  {2, 64, 0, 32, 0, {0, 0, 0}}, {2, 128, 0, 8, 0, {0, 0, 0}},
+    {2, 128, 0, 16, 0, {0, 0, 0}}, {1, 64, 0, 8, 0, {0, 0, 0}}, {1, 64, 0, 16, 0, {0, 0, 0}},
+    {1, 64, 0, 1, 0, {0, 0, 0}},  {1, 128, 0, 8, 0, {0, 0, 0}},
+};
+constexpr int kTableSize = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
+
+// ---------------------------------------------------------------- per-device state
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc = 0;
+  int max_smem_optin = 0;
+  int max_clusters[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per variant, 0 = not yet queried
+  int smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // dynamic smem attribute already raised to
+};
+
+std::mutex g_dev_mutex;
+std::map<int, DeviceInfo> g_devices;
+
+int device_info(int* dev_out, DeviceInfo** info_out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  auto it = g_devices.find(dev);
+  if (it == g_devices.end()) {
+    DeviceInfo d;
+    int major = 0, minor = 0;
+    if ((e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev)) !=
+            cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev)) !=
+            cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev)) !=
+            cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                    dev)) != cudaSuccess) {
+      return fail_cuda(e, "cudaDeviceGetAttribute");
+    }
+    d.cc = major * 10 + minor;
+    it = g_devices.emplace(dev, d).first;
+  }
+  *dev_out = dev;
+  *info_out = &it->second;
+  return SGL_OK;
+}
+
+int validate_ptr(const void* p, const char* name) {
+  if (!p) return fail(SGL_ERR_NULL_POINTER, "%s is NULL", name);
+  if (reinterpret_cast<uintptr_t>(p) & 15u)
+    return fail(SGL_ERR_MISALIGNED, "%s is not 16-byte aligned", name);
+  return SGL_OK;
+}
+
+int validate_ld(int64_t ld, int64_t min_cols, const char* name) {
+  if (ld < min_cols)
+    return fail(SGL_ERR_BAD_STRIDE, "%s=%lld is smaller than the %lld columns it must hold", name,
+                static_cast<long long>(ld), static_cast<long long>(min_cols));
+  if (ld % 8 != 0)
+    return fail(SGL_ERR_BAD_STRIDE, "%s=%lld is not a multiple of 8 elements (16 bytes)", name,
+                static_cast<long long>(ld));
+  if (ld > 0x7fffffffll)
+    return fail(SGL_ERR_BAD_STRIDE, "%s=%lld does not fit 31 bits", name,
+                static_cast<long long>(ld));
+  return SGL_OK;
+}
+
+int validate_shape(int64_t M, int64_t N, int64_t K) {
+  if (M < 1 || N < 1 || K < 1)
+    return fail(SGL_ERR_BAD_SHAPE, "M=%lld N=%lld K=%lld must all be >= 1",
+                static_cast<long long>(M), static_cast<long long>(N), static_cast<long long>(K));
+  if (N % 8 != 0 || K % 8 != 0)
+    return fail(SGL_ERR_BAD_SHAPE, "N=%lld and K=%lld must be multiples of 8",
+                static_cast<long long>(N), static_cast<long long>(K));
+  if (M > 0x7fffff00ll || N > 0x7fffff00ll || K > 0x7fffff00ll)
+    return fail(SGL_ERR_BAD_SHAPE, "M, N and K must fit 31 bits");
+  return SGL_OK;
+}
+
+void default_config(int64_t M, sgl_config* c) {
+  std::memset(c, 0, sizeof(*c));
+  c->cta_group = (M > sgl::kBlockM) ? 2 : 1;
+  c->block_k = 64;
+  c->stages = 0;
+  c->group_m = 8;
+}
+
+// Resolves stages == 0 and checks that the configuration fits.
+int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
+  if (in) {
+    *out = *in;
+  } else {
+    default_config(M, out);
+  }
+  if (!config_fields_ok(*out))
+    return fail(SGL_ERR_BAD_CONFIG,
+                "unsupported tile configuration: cta_group=%d block_k=%d stages=%d group_m=%d",
+                out->cta_group, out->block_k, out->stages, out->group_m);
+  const Variant& v = variant(form, out->cta_group, out->block_k);
+  if (out->stages == 0) out->stages = v.max_stages;
+  if (out->stages < 2 || out->stages > v.max_stages)
+    return fail(SGL_ERR_BAD_CONFIG, "stages=%d outside [2, %d] for cta_group=%d block_k=%d",
+                out->stages, v.max_stages, out->cta_group, out->block_k);
+  return SGL_OK;
+}
+
+int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
+           const CUtensorMap& th, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           const sgl_config& cfg, DeviceInfo* info, void* stream) {
+  const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
+  const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
+  const int smem = v.smem_bytes(cfg.stages);
+  if (smem > info->max_smem_optin)
+    return fail(SGL_ERR_BAD_CONFIG, "configuration needs %d bytes of shared memory, device has %d",
+                smem, info->max_smem_optin);
+
+  const int rows_per_tile = sgl::kBlockM * cfg.cta_group;
+  const int64_t tiles_m = (M + rows_per_tile - 1) / rows_per_tile;
+  const int64_t tiles_n = (N + v.out_cols - 1) / v.out_cols;
+  if (tiles_m * tiles_n > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
+
+  cudaError_t e;
+  {
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (info->smem_set[vi] < smem) {
+      e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(max dynamic smem)");
+      info->smem_set[vi] = smem;
+    }
+    if (info->max_clusters[vi] == 0) {
+      int n = info->sm_count / cfg.cta_group;
+      if (cfg.cta_group == 2) {
+        cudaLaunchConfig_t qc = {};
+        qc.gridDim = dim3(static_cast<unsigned>(info->sm_count / 2 * 2), 1, 1);
+        qc.blockDim = dim3(sgl::kNumThreads, 1, 1);
+        qc.dynamicSmemBytes = static_cast<size_t>(v.smem_bytes(v.max_stages));
+        cudaLaunchAttribute qa[1];
+        qa[0].id = cudaLaunchAttributeClusterDimension;
+        qa[0].val.clusterDim.x = 2;
+        qa[0].val.clusterDim.y = 1;
+        qa[0].val.clusterDim.z = 1;
+        qc.attrs = qa;
+        qc.numAttrs = 1;
+        int q = 0;
+        // The attribute must cover the query's shared memory too.
+        cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
+                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             v.smem_bytes(v.max_stages));
+        if (info->smem_set[vi] < v.smem_bytes(v.max_stages))
+          info->smem_set[vi] = v.smem_bytes(v.max_stages);
+        e = cudaOccupancyMaxActiveClusters(&q, reinterpret_cast<const void*>(v.fn), &qc);
+        if (e == cudaSuccess && q > 0) {
+          if (q < n) n = q;
+        } else {
+          cudaGetLastError();
+        }
+      }
+      info->max_clusters[vi] = n > 0 ? n : 1;
+    }
+  }
+
+  int64_t clusters = info->max_clusters[vi];
+  if (cfg.max_ctas > 0 && cfg.max_ctas / cfg.cta_group < clusters)
+    clusters = cfg.max_ctas / cfg.cta_group;
+  if (clusters < 1) clusters = 1;
+  if (tiles_m * tiles_n < clusters) clusters = tiles_m * tiles_n;
+
+  sgl::KernelParams p;
+  p.M = static_cast<int>(M);
+  p.N = static_cast<int>(N);
+  p.K = static_cast<int>(K);
+  p.b_col0 = static_cast<int>(col0);
+  p.b_col1 = static_cast<int>(col1);
+  p.tiles_m = static_cast<int>(tiles_m);
+  p.tiles_n = static_cast<int>(tiles_n);
+  p.group_m = cfg.group_m;
+  p.stages = cfg.stages;
+  p.wait_limit_ns = g_wait_limit_ns.load();
+
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(static_cast<unsigned>(clusters * cfg.cta_group), 1, 1);
+  lc.blockDim = dim3(sgl::kNumThreads, 1, 1);
+  lc.dynamicSmemBytes = static_cast<size_t>(smem);
+  lc.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attrs[1];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = static_cast<unsigned>(cfg.cta_group);
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  lc.attrs = attrs;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, v.fn, tx, tw, tup, th, p);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
+  g_launches.fetch_add(1);
+  return SGL_OK;
+}
+
+int check_device(DeviceInfo** info) {
+  int dev = 0;
+  int rc = device_info(&dev, info);
+  if (rc != SGL_OK) return rc;
+  if ((*info)->cc / 10 != 10)
+    return fail(SGL_ERR_UNSUPPORTED_DEVICE,
+                "device %d has compute capability %d.%d; this library is built for sm_100a only",
+                dev, (*info)->cc / 10, (*info)->cc % 10);
+  return SGL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void* h, int64_t M,
+                        int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldup, int64_t ldh,
+                        const sgl_config* cfg, void* stream) {
+  int rc;
+  if ((rc = validate_ptr(x, "x")) || (rc = validate_ptr(w_gate, "w_gate")) ||
+      (rc = validate_ptr(up, "up")) || (rc = validate_ptr(h, "h")))
+    return rc;
+  if ((rc = validate_shape(M, N, K))) return rc;
+  if ((rc = validate_ld(ldx, K, "ldx")) || (rc = validate_ld(ldw, N, "ldw")) ||
+      (rc = validate_ld(ldup, N, "ldup")) || (rc = validate_ld(ldh, N, "ldh")))
+    return rc;
+  sgl_config c;
+  if ((rc = resolve_config(SGL_FORM_SILU_MUL, cfg, M, &c))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+
+  CUtensorMap tx, tw, tup, th;
+  if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "x")) ||
+      (rc = make_map(&tw, w_gate, K, N, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "w_gate")) ||
+      (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
+      (rc = make_map(&th, h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
+    return rc;
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, M, N, K, 0, 0, c, info, stream);
+}
+
+int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
+                            int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
+                            int64_t gate_col0, const sgl_config* cfg, void* stream) {
+  int rc;
+  if ((rc = validate_ptr(x, "x")) || (rc = validate_ptr(w, "w")) || (rc = validate_ptr(h, "h")))
+    return rc;
+  if ((rc = validate_shape(M, N, K))) return rc;
+  if (up_col0 < 0 || gate_col0 < 0)
+    return fail(SGL_ERR_BAD_ARGUMENT, "up_col0=%lld and gate_col0=%lld must be >= 0",
+                static_cast<long long>(up_col0), static_cast<long long>(gate_col0));
+  if (up_col0 % 8 != 0 || gate_col0 % 8 != 0)
+    return fail(SGL_ERR_MISALIGNED,
+                "up_col0=%lld and gate_col0=%lld must be multiples of 8 columns (16 bytes)",
+                static_cast<long long>(up_col0), static_cast<long long>(gate_col0));
+  const int64_t w_cols = (up_col0 > gate_col0 ? up_col0 : gate_col0) + N;
+  if ((rc = validate_ld(ldx, K, "ldx")) || (rc = validate_ld(ldw, w_cols, "ldw")) ||
+      (rc = validate_ld(ldh, N, "ldh")))
+    return rc;
+  sgl_config c;
+  if ((rc = resolve_config(SGL_FORM_FUSED_SWIGLU, cfg, M, &c))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+
+  CUtensorMap tx, tw, th;
+  if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "x")) ||
+      (rc = make_map(&tw, w, K, ldw, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "w")) ||
+      (rc = make_map(&th, h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
+    return rc;
+  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th, th, M, N, K, up_col0, gate_col0, c, info,
+                stream);
+}
+
+int sgl_config_count(int form) {
+  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+    return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
+  return kTableSize;
+}
+
+int sgl_config_get(int form, int index, sgl_config* out) {
+  if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
+  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+    return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
+  if (index < 0 || index >= kTableSize)
+    return fail(SGL_ERR_BAD_ARGUMENT, "config index %d outside [0, %d)", index, kTableSize);
+  *out = kTable[index];
+  out->stages = variant(form, out->cta_group, out->block_k).max_stages;
+  return SGL_OK;
+}
+
+int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* out) {
+  if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
+  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+    return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
+  int rc = validate_shape(M, N, K);
+  if (rc) return rc;
+  return resolve_config(form, nullptr, M, out);
+}
+
+int sgl_config_smem_bytes(int form, const sgl_config* cfg) {
+  if (!cfg) return fail(SGL_ERR_NULL_POINTER, "cfg is NULL");
+  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+    return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
+  sgl_config c;
+  int rc = resolve_config(form, cfg, 1 << 20, &c);
+  if (rc) return rc;
+  return variant(form, c.cta_group, c.block_k).smem_bytes(c.stages);
+}
+
+int sgl_tile_coord(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m, int64_t* tile_m,
+                   int64_t* tile_n) {
+  if (!tile_m || !tile_n) return fail(SGL_ERR_NULL_POINTER, "output pointer is NULL");
+  if (tiles_m < 1 || tiles_n < 1 || group_m < 1 || t < 0 || t >= tiles_m * tiles_n ||
+      tiles_m * tiles_n > 0x7fffffffll)
+    return fail(SGL_ERR_BAD_ARGUMENT, "tile index or grid out of range");
+  sgl::TileCoord c = sgl::tile_coord(static_cast<int>(t), static_cast<int>(tiles_m),
+                                     static_cast<int>(tiles_n), static_cast<int>(group_m));
+  *tile_m = c.m;
+  *tile_n = c.n;
+  return SGL_OK;
+}
+
+int sgl_query(int what, int64_t* out) {
+  if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
+  if (what == SGL_QUERY_KERNEL_LAUNCHES) {
+    *out = g_launches.load();
+    return SGL_OK;
+  }
+  int dev = 0;
+  DeviceInfo* info = nullptr;
+  int rc = device_info(&dev, &info);
+  if (rc) return rc;
+  switch (what) {
+    case SGL_QUERY_SM_COUNT: *out = info->sm_count; return SGL_OK;
+    case SGL_QUERY_MAX_SMEM_OPTIN: *out = info->max_smem_optin; return SGL_OK;
+    case SGL_QUERY_COMPUTE_CAPABILITY: *out = info->cc; return SGL_OK;
+    default: return fail(SGL_ERR_BAD_ARGUMENT, "unknown query %d", what);
+  }
+}
+
+int sgl_shard_range(int64_t total, int64_t align, int world, int rank, int64_t* begin,
+                    int64_t* count) {
+  if (!begin || !count) return fail(SGL_ERR_NULL_POINTER, "output pointer is NULL");
+  if (total < 0 || align < 1 || world < 1 || rank < 0 || rank >= world)
+    return fail(SGL_ERR_BAD_ARGUMENT, "bad shard request: total=%lld align=%lld world=%d rank=%d",
+                static_cast<long long>(total), static_cast<long long>(align), world, rank);
+  // Distribute whole `align`-sized blocks as evenly as possible; earlier ranks
+  // take the extra blocks, the last non-empty shard takes the ragged tail.
+  const int64_t blocks = (total + align - 1) / align;
+  const int64_t base = blocks / world;
+  const int64_t extra = blocks % world;
+  const int64_t b0 = rank * base + (rank < extra ? rank : extra);
+  const int64_t nb = base + (rank < extra ? 1 : 0);
+  int64_t lo = b0 * align;
+  int64_t hi = (b0 + nb) * align;
+  if (lo > total) lo = total;
+  if (hi > total) hi = total;
+  *begin = lo;
+  *count = hi - lo;
+  return SGL_OK;
+}
+
+int sgl_device_status(uint32_t* words) {
+  unsigned int host[8];
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
+  e = cudaMemcpyFromSymbol(host, sgl::g_status, sizeof(host));
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyFromSymbol(status)");
+  if (words) std::memcpy(words, host, sizeof(host));
+  if (host[0] != 0 || host[3] != 0) {
+    unsigned int zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(sgl::g_status, zero, sizeof(zero));
+    if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyToSymbol(status)");
+    return fail(SGL_ERR_DEVICE_STATUS,
+                "kernel wait timed out: code=0x%x block=%u detail=%u occurrences=%u", host[0],
+                host[1], host[2], host[3]);
+  }
+  return SGL_OK;
+}
+
+int sgl_set_wait_limit_ns(uint64_t ns) {
+  if (ns == 0) return fail(SGL_ERR_BAD_ARGUMENT, "wait limit must be > 0");
+  g_wait_limit_ns.store(ns);
+  return SGL_OK;
+}
+
+const char* sgl_last_error(void) { return t_last_error.c_str(); }
+
+int sgl_version(void) { return 100; }
+
+}  // extern "C"

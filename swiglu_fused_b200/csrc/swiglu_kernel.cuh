@@ -1,0 +1,493 @@
+// Persistent, warp-specialised fused SwiGLU gate/up kernel for sm_100a.
+//
+// Two forms share one skeleton:
+//   FORM_SILU_MUL  h = silu(x @ W_gate) * up              (up is an input)
+//       replaces matmul_silu_mul_impl, swiglu/_matmul_silu_mul.cu:323-652
+//   FORM_FUSED     h = silu(x @ W[:, gate cols]) * (x @ W[:, up cols])
+//       replaces matmul_fused_swiglu_impl, swiglu/_matmul_fused_swiglu.cu:193-508
+//
+// Design (not the reference's):
+//   * persistent grid, one CTA (or CTA pair) per SM, static GROUP_SIZE_M-swizzled
+//     tile schedule;
+//   * warp 0 = TMA producer, warp 1 = tcgen05 MMA issuer, warps 2-5 = epilogue;
+//   * one wide 256-column fp32 accumulator per tile.  In the fused form columns
+//     [0,128) hold `up` and [128,256) hold `gate` for the same 128 output
+//     columns, produced by ONE K loop (x is streamed once, not twice);
+//   * two accumulator stages fill the 512 TMEM columns, so the epilogue of tile
+//     t (TMEM -> registers -> silu*up in fp32 -> bf16 -> swizzled smem -> TMA
+//     store) overlaps the mainloop of tile t+1;
+//   * in the silu_mul form each epilogue warp prefetches its own `up` rows with
+//     TMA into private shared-memory buffers (coalesced and asynchronous);
+//   * with kCtaGroup == 2 a CTA pair computes a 256-row tile with
+//     tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of x and its own
+//     half of the B operand (no multicast loads anywhere);
+//   * every wait is bounded; a timeout raises a CTA-wide abort flag, records an
+//     error word in g_status and the kernel drains and exits.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "ptx_sm100.cuh"
+
+namespace sgl {
+
+enum : int { FORM_SILU_MUL = 0, FORM_FUSED = 1 };
+
+constexpr int kBlockM = 128;        // rows of x per CTA
+constexpr int kAccCols = 256;       // accumulator columns per tile (MMA N)
+constexpr int kAccStages = 2;       // TMEM accumulator stages
+constexpr int kTmemCols = 512;      // kAccCols * kAccStages
+constexpr int kMaxStages = 8;       // shared-memory ring depth limit
+constexpr int kNumThreads = 192;    // 6 warps
+constexpr int kEpiWarps = 4;
+constexpr int kChunkCols = 64;      // epilogue works on 64 output columns (128 B rows)
+constexpr int kChunkBytes = 32 * kChunkCols * 2;  // one warp's 32 rows x 128 B
+constexpr int kOutBufs = 2;         // staging buffers per epilogue warp
+constexpr int kUpBufs = 2;          // `up` prefetch buffers per epilogue warp
+
+// Error words written to g_status[0] (first error wins); g_status[1] = block,
+// g_status[2] = detail (role-specific: k-block, stage or chunk index).
+enum : unsigned {
+  kErrProducerEmptyWait = 0x101,
+  kErrMmaFullWait = 0x102,
+  kErrMmaTmemEmptyWait = 0x103,
+  kErrEpiTmemFullWait = 0x104,
+  kErrEpiUpWait = 0x105,
+};
+
+// First-error record, readable from the host with cudaMemcpyFromSymbol.
+__device__ unsigned int g_status[8];
+
+struct KernelParams {
+  int M, N, K;          // N = output columns of h
+  int b_col0;           // first B column: gate (silu_mul form) / up (fused form)
+  int b_col1;           // fused form: first gate column of the packed weight
+  int tiles_m, tiles_n; // tile grid in cluster-tile units
+  int group_m;          // GROUP_SIZE_M
+  int stages;           // shared-memory ring depth actually used
+  unsigned long long wait_limit_ns;
+};
+
+template <int kForm, int kCtaGroup, int kBlockK>
+struct KernelTraits {
+  static constexpr int kOutCols = (kForm == FORM_SILU_MUL) ? 256 : 128;
+  static constexpr int kChunksPerTile = kOutCols / kChunkCols;
+  static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
+  static constexpr int kBSlabs = kBColsPerCta / 64;           // 64-column slabs this CTA loads
+  static constexpr int kAStageBytes = kBlockM * kBlockK * 2;
+  static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
+  static constexpr int kBStageBytes = kBSlabs * kBSlabBytes;
+  static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+  static constexpr int kOutStagingBytes = kEpiWarps * kOutBufs * kChunkBytes;
+  static constexpr int kUpStagingBytes =
+      (kForm == FORM_SILU_MUL) ? kEpiWarps * kUpBufs * kChunkBytes : 0;
+  static constexpr int kBarrierBytes = 512;
+  static constexpr int kAlignSlack = 1024;
+  static constexpr int kMaxSmem = 227 * 1024;
+
+  __host__ __device__ static constexpr int smem_bytes(int stages) {
+    return kAlignSlack + stages * kStageBytes + kOutStagingBytes + kUpStagingBytes +
+           kBarrierBytes;
+  }
+  __host__ __device__ static constexpr int max_stages() {
+    int s = (kMaxSmem - kAlignSlack - kOutStagingBytes - kUpStagingBytes - kBarrierBytes) /
+            kStageBytes;
+    return s > kMaxStages ? kMaxStages : s;
+  }
+};
+
+struct TileCoord {
+  int m;  // cluster-tile row index
+  int n;  // cluster-tile column index
+};
+
+// GROUP_SIZE_M swizzle: tiles are walked in bands of `group_m` tile rows, rows
+// fastest inside a band, so concurrently running tiles share x rows and weight
+// columns in L2.  Equivalent in purpose to swiglu/_matmul_silu_mul.cu:357-384,
+// applied to the persistent schedule's linear tile index.
+__host__ __device__ inline TileCoord tile_coord(int t, int tiles_m, int tiles_n, int group_m) {
+  const int per_band = group_m * tiles_n;
+  const int band = t / per_band;
+  const int first_m = band * group_m;
+  const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+  const int in_band = t - band * per_band;
+  TileCoord c;
+  c.m = first_m + in_band % rows;
+  c.n = in_band / rows;
+  return c;
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// silu(g) * u in fp32 with one MUFU.EX2 and one MUFU.RCP:
+//   silu(g) = g / (1 + e^-g) = g * rcp(1 + 2^(-g * log2 e)).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float e = ex2_approx(g * -1.4426950408889634f);
+  const float s = g * rcp_approx(1.0f + e);
+  return s * u;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void report_error(unsigned code, unsigned detail, int* abort_flag) {
+  if (atomicCAS(&g_status[0], 0u, code) == 0u) {
+    g_status[1] = blockIdx.x;
+    g_status[2] = detail;
+  }
+  atomicAdd(&g_status[3], 1u);
+  *reinterpret_cast<volatile int*>(abort_flag) = 1;
+}
+
+template <int kForm, int kCtaGroup, int kBlockK>
+__global__ void __launch_bounds__(kNumThreads, 1)
+swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
+              const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_h,
+              const KernelParams p) {
+  using T = KernelTraits<kForm, kCtaGroup, kBlockK>;
+  static_assert(kBlockK == 64 || kBlockK == 128, "BLOCK_K is 64 or 128");
+  static_assert(kCtaGroup == 1 || kCtaGroup == 2, "CTA group is 1 or 2");
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
+  const int cluster_id = blockIdx.x / kCtaGroup;
+  const int num_clusters = gridDim.x / kCtaGroup;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  const int stages = p.stages;
+
+  // ---- shared memory carve-up (offsets identical in both CTAs of a pair) ----
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA = smem_base;
+  const uint32_t sB = sA + stages * T::kAStageBytes;
+  const uint32_t sOut = sB + stages * T::kBStageBytes;
+  const uint32_t sUp = sOut + T::kOutStagingBytes;
+  const uint32_t sBar = sUp + T::kUpStagingBytes;
+  const uint32_t bar_full = sBar;                       // [kMaxStages]
+  const uint32_t bar_empty = bar_full + 8 * kMaxStages; // [kMaxStages]
+  const uint32_t bar_tfull = bar_empty + 8 * kMaxStages;  // [kAccStages]
+  const uint32_t bar_tempty = bar_tfull + 8 * kAccStages; // [kAccStages]
+  const uint32_t bar_up = bar_tempty + 8 * kAccStages;    // [kEpiWarps][kUpBufs]
+  const uint32_t tmem_slot = bar_up + 8 * kEpiWarps * kUpBufs;
+  const uint32_t abort_slot = tmem_slot + 8;
+  // Generic pointers to the two scalar slots.
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+  // abort_flag[0] = CTA-wide abort flag, abort_flag[1] stays zero.
+  int* abort_flag = reinterpret_cast<int*>(smem_gen + (abort_slot - smem_base));
+
+  // ---- one-time setup ----
+  if (threadIdx.x == 0) {
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    for (int s = 0; s < kMaxStages; ++s) {
+      ptx::mbar_init(bar_full + 8 * s, kCtaGroup);  // one arrive.expect_tx per CTA
+      ptx::mbar_init(bar_empty + 8 * s, 1);         // one tcgen05.commit
+    }
+    for (int s = 0; s < kAccStages; ++s) {
+      ptx::mbar_init(bar_tfull + 8 * s, 1);                     // one tcgen05.commit
+      ptx::mbar_init(bar_tempty + 8 * s, kEpiWarps * kCtaGroup);  // one arrive per epilogue warp
+    }
+    for (int i = 0; i < kEpiWarps * kUpBufs; ++i) ptx::mbar_init(bar_up + 8 * i, 1);
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tm_x);
+    ptx::prefetch_tensormap(&tm_w);
+    ptx::prefetch_tensormap(&tm_h);
+    if constexpr (kForm == FORM_SILU_MUL) ptx::prefetch_tensormap(&tm_up);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<kCtaGroup>(tmem_slot, kTmemCols);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) ptx::cluster_sync();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  const uint64_t limit = p.wait_limit_ns;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) {
+      // Barrier that collects this stage's bytes: the leader CTA's.
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < total_tiles && ok; t += num_clusters) {
+        const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+        const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
+        const int n0 = tc.n * T::kOutCols;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(bar_empty + 8 * s, ph ^ 1u, limit, abort_flag)) {
+            report_error(kErrProducerEmptyWait, kb, abort_flag);
+            ok = false;
+            break;
+          }
+          const uint32_t full_local = bar_full + 8 * s;
+          const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
+          ptx::mbar_arrive_expect_tx_cluster(full, T::kStageBytes);
+          const int k0 = kb * kBlockK;
+          const uint32_t a_dst = sA + s * T::kAStageBytes;
+#pragma unroll
+          for (int j = 0; j < kBlockK / 64; ++j) {
+            ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64, m0,
+                                             full);
+          }
+          const uint32_t b_dst = sB + s * T::kBStageBytes;
+#pragma unroll
+          for (int j = 0; j < T::kBSlabs; ++j) {
+            // Slab index inside the 256 accumulator columns of the cluster tile.
+            const int g = static_cast<int>(rank) * T::kBSlabs + j;
+            int col;
+            if constexpr (kForm == FORM_SILU_MUL) {
+              col = p.b_col0 + n0 + g * 64;
+            } else {
+              col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
+            }
+            ptx::tma_load_2d<kCtaGroup == 2>(b_dst + j * T::kBSlabBytes, &tm_w, col, k0, full);
+          }
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Give loads that are still in flight time to land before the CTA exits.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols, true);
+      constexpr uint16_t mask = (kCtaGroup == 2) ? 0x3 : 0x1;
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int i = 0;
+      for (int t = cluster_id; t < total_tiles && ok; t += num_clusters, ++i) {
+        const int as = i & 1;
+        const uint32_t aph = (i >> 1) & 1u;
+        if (!ptx::mbar_wait(bar_tempty + 8 * as, aph ^ 1u, limit, abort_flag)) {
+          report_error(kErrMmaTmemEmptyWait, i, abort_flag);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + as * kAccCols;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(bar_full + 8 * s, ph, limit, abort_flag)) {
+            report_error(kErrMmaFullWait, kb, abort_flag);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_base = sA + s * T::kAStageBytes;
+          const uint32_t b_base = sB + s * T::kBStageBytes;
+#pragma unroll
+          for (int kk = 0; kk < kBlockK / 16; ++kk) {
+            // x tile: K-major, one 128-row x 64-col swizzled box per 64 k;
+            // 16 k = 32 bytes inside the 128-byte swizzle row.
+            const uint64_t a_desc = ptx::smem_desc_sw128(
+                a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
+            // weight tile: N-major slabs [kBlockK rows][64 cols]; 16 k = 16 rows.
+            const uint64_t b_desc =
+                ptx::smem_desc_sw128(b_base + kk * 16 * 128, T::kBSlabBytes, 1024);
+            ptx::umma_bf16<kCtaGroup>(d_tmem, a_desc, b_desc, idesc,
+                                      (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          ptx::umma_commit<kCtaGroup>(bar_empty + 8 * s, mask);
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (ok) ptx::umma_commit<kCtaGroup>(bar_tfull + 8 * as, mask);
+      }
+    }
+  } else {
+    // =========================== epilogue ===========================
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t out_buf0 = sOut + q * (kOutBufs * kChunkBytes);
+    const uint32_t up_buf0 = sUp + q * (kUpBufs * kChunkBytes);
+    const uint32_t my_bar_up = bar_up + 8 * (q * kUpBufs);
+    const uint32_t tempty_leader_base = (kCtaGroup == 2) ? ptx::mapa(bar_tempty, 0) : bar_tempty;
+    const uint32_t row_sw = static_cast<uint32_t>(lane & 7);  // 128B-swizzle row phase
+    const uint32_t row_off = static_cast<uint32_t>(lane) * 128u;
+
+    // Number of tiles this cluster owns.
+    const int my_tiles =
+        (cluster_id < total_tiles) ? (total_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+    const int total_chunks = my_tiles * T::kChunksPerTile;
+
+    // Coordinates of output chunk g (global over this CTA's tile sequence).
+    auto chunk_xy = [&](int g, int& x, int& y) {
+      const int i = g / T::kChunksPerTile;
+      const int c = g - i * T::kChunksPerTile;
+      const TileCoord tc =
+          tile_coord(cluster_id + i * num_clusters, p.tiles_m, p.tiles_n, p.group_m);
+      x = tc.n * T::kOutCols + c * kChunkCols;
+      y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
+    };
+
+    int up_issued = 0;  // `up` chunk loads issued so far (lane 0 only)
+    auto issue_up = [&](int g) {
+      int x, y;
+      chunk_xy(g, x, y);
+      const int b = g % kUpBufs;
+      ptx::mbar_arrive_expect_tx_cluster(my_bar_up + 8 * b, kChunkBytes);
+      ptx::tma_load_2d<false>(up_buf0 + b * kChunkBytes, &tm_up, x, y, my_bar_up + 8 * b);
+    };
+    if constexpr (kForm == FORM_SILU_MUL) {
+      if (lane == 0) {
+        for (; up_issued < kUpBufs && up_issued < total_chunks; ++up_issued) issue_up(up_issued);
+      }
+    }
+
+    bool ok = true;
+    int g = 0;  // running chunk index
+    for (int i = 0; i < my_tiles && ok; ++i) {
+      const int as = i & 1;
+      const uint32_t aph = (i >> 1) & 1u;
+      {
+        const bool w = ptx::mbar_wait(bar_tfull + 8 * as, aph, limit, abort_flag);
+        if (!__all_sync(0xffffffffu, w)) {
+          if (lane == 0) report_error(kErrEpiTmemFullWait, i, abort_flag);
+          ok = false;
+          break;
+        }
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
+
+#pragma unroll 1
+      for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
+        int x, y;
+        chunk_xy(g, x, y);
+        const uint32_t obuf = out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
+        const uint32_t ubuf = up_buf0 + (g % kUpBufs) * kChunkBytes;
+
+        if constexpr (kForm == FORM_SILU_MUL) {
+          const bool w = ptx::mbar_wait(my_bar_up + 8 * (g % kUpBufs), (g / kUpBufs) & 1u, limit,
+                                        abort_flag);
+          if (!__all_sync(0xffffffffu, w)) {
+            if (lane == 0) report_error(kErrEpiUpWait, g, abort_flag);
+            ok = false;
+            break;
+          }
+        }
+        // The staging buffer is free once the store issued two chunks ago has
+        // finished reading it.
+        if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
+        __syncwarp();
+
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int col = c * kChunkCols + half * 32;
+          float gate[32];
+          float upv[32];
+          if constexpr (kForm == FORM_SILU_MUL) {
+            ptx::tmem_ld_32x32b_x32(t_row + col, gate);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr =
+                  ubuf + row_off + ((static_cast<uint32_t>(half * 4 + j) ^ row_sw) << 4);
+              uint32_t r0, r1, r2, r3;
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                           : "r"(addr));
+              const uint32_t rr[4] = {r0, r1, r2, r3};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                upv[j * 8 + 2 * e] = __uint_as_float(rr[e] << 16);
+                upv[j * 8 + 2 * e + 1] = __uint_as_float(rr[e] & 0xffff0000u);
+              }
+            }
+          } else {
+            ptx::tmem_ld_32x32b_x32(t_row + col, upv);
+            ptx::tmem_ld_32x32b_x32(t_row + 128 + col, gate);
+          }
+          ptx::tmem_ld_wait();
+          if (c == T::kChunksPerTile - 1 && half == 1) {
+            // Last TMEM read of this tile: hand the accumulator stage back to
+            // the MMA issuer before finishing the math and the stores.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int idx = j * 8 + 2 * e;
+              w[e] = pack_bf16x2(silu_mul(gate[idx], upv[idx]),
+                                 silu_mul(gate[idx + 1], upv[idx + 1]));
+            }
+            const uint32_t addr =
+                obuf + row_off + ((static_cast<uint32_t>(half * 4 + j) ^ row_sw) << 4);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(w[0]),
+                         "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (x < p.N && y < p.M) ptx::tma_store_2d(&tm_h, x, y, obuf);
+          ptx::bulk_commit_group();
+          if constexpr (kForm == FORM_SILU_MUL) {
+            // This chunk's `up` buffer has been read by every lane: refill it.
+            if (up_issued < total_chunks) {
+              issue_up(up_issued);
+              ++up_issued;
+            }
+          }
+        }
+      }
+    }
+    if (lane == 0) {
+      ptx::bulk_wait_group<0>();
+      if constexpr (kForm == FORM_SILU_MUL) {
+        if (!ok) {
+          // Drain `up` loads that were issued but never consumed.
+          for (int gg = g; gg < up_issued; ++gg) {
+            ptx::mbar_wait(my_bar_up + 8 * (gg % kUpBufs), (gg / kUpBufs) & 1u, 1000000ull,
+                           abort_flag + 1 /* stays zero */);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----
+  __syncwarp();
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if constexpr (kCtaGroup == 2) ptx::cluster_sync();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace sgl

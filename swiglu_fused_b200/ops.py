@@ -1,0 +1,202 @@
+"""The two operators, on the reference's Python surface.
+
+``matmul_silu_mul(A, B_gate, up)``      mirrors ``swiglu/matmul_silu_mul.py:142-161``
+``matmul_fused_swiglu(A, W)``           mirrors ``swiglu/matmul_fused_swiglu.py:152-172``
+
+Same positional arguments, same result (a new ``[M, N]`` bf16 CUDA tensor).
+Differences, all on purpose:
+
+* inputs are validated (dtype, device, layout, alignment) and a bad call raises
+  before anything is launched; the reference only asserts shapes;
+* the launch goes to torch's current stream (or ``stream=``), not the null stream;
+* ``out=`` lets the caller own the output (no allocation inside the call);
+* ``config=`` pins a tile configuration; otherwise the persisted tile table,
+  then the library default, decides;
+* any ``M >= 1`` and any ``N``, ``K`` that are multiples of 8 are accepted;
+* there is no CPU or eager fallback: without the CUDA library and a B200 the
+  call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+from . import _lib, tile_table
+from ._lib import TileConfig
+
+DTYPE = torch.bfloat16
+
+
+def _check_matrix(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if t.dim() != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    if t.dtype != DTYPE:
+        raise TypeError(f"{name} must be torch.bfloat16, got {t.dtype}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (this operator has no CPU path)")
+    if t.shape[0] < 1 or t.shape[1] < 1:
+        raise ValueError(f"{name} must not be empty, got shape {tuple(t.shape)}")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must be row-major with unit column stride, "
+                         f"got strides {t.stride()}")
+    if t.shape[0] > 1 and t.stride(0) < t.shape[1]:
+        raise ValueError(f"{name} has overlapping rows: strides {t.stride()}")
+    if t.stride(0) % 8 != 0 and t.shape[0] > 1:
+        raise ValueError(f"{name}: row stride {t.stride(0)} must be a multiple of 8 elements")
+    if t.data_ptr() % 16 != 0:
+        raise ValueError(f"{name} must be 16-byte aligned")
+
+
+def _ld(t: torch.Tensor) -> int:
+    # A single-row tensor may report any stride; use the dense pitch (rounded to 8).
+    if t.shape[0] == 1:
+        return (t.shape[1] + 7) // 8 * 8
+    return t.stride(0)
+
+
+def _same_device(*named: tuple[str, torch.Tensor]) -> torch.device:
+    dev = named[0][1].device
+    for name, t in named[1:]:
+        if t.device != dev:
+            raise ValueError(f"{name} is on {t.device}, expected {dev}")
+    return dev
+
+
+def _stream_handle(stream, device) -> int:
+    if stream is None:
+        return torch.cuda.current_stream(device).cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+def _pick_config(form: int, config: TileConfig | None, M: int, N: int, K: int):
+    if config is not None:
+        return config
+    return tile_table.lookup(form, M, N, K)
+
+
+def _prep_out(out, M, N, device, name="out"):
+    if out is None:
+        return torch.empty((M, N), dtype=DTYPE, device=device)
+    _check_matrix(out, name)
+    if tuple(out.shape) != (M, N):
+        raise ValueError(f"{name} shape {tuple(out.shape)} != {(M, N)}")
+    if out.device != device:
+        raise ValueError(f"{name} is on {out.device}, expected {device}")
+    return out
+
+
+def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig | None = None):
+    """h = silu(A @ B_gate) * up.
+
+    A      : [M, K] bf16
+    B_gate : [K, N] bf16
+    up     : [M, N] bf16  (precomputed x @ W_up)
+    returns: [M, N] bf16
+    """
+    _check_matrix(A, "A")
+    _check_matrix(B_gate, "B_gate")
+    _check_matrix(up, "up")
+    M, K = A.shape
+    K2, N = B_gate.shape
+    if K2 != K:
+        raise ValueError(f"K mismatch: A.K={K} vs B_gate.K={K2}")
+    if tuple(up.shape) != (M, N):
+        raise ValueError(f"up shape {tuple(up.shape)} != {(M, N)}")
+    if K % 8 or N % 8:
+        raise ValueError(f"K={K} and N={N} must be multiples of 8")
+    dev = _same_device(("A", A), ("B_gate", B_gate), ("up", up))
+    h = _prep_out(out, M, N, dev)
+    if os.environ.get("SWIGLU_B200_AUTOTUNE") == "1" and config is None \
+            and tile_table.lookup(_lib.FORM_SILU_MUL, M, N, K) is None:
+        tune_matmul_silu_mul(A, B_gate, up)
+    cfg = _pick_config(_lib.FORM_SILU_MUL, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.sgl_matmul_silu_mul(
+            A.data_ptr(), B_gate.data_ptr(), up.data_ptr(), h.data_ptr(), M, N, K,
+            _ld(A), _ld(B_gate), _ld(up), _ld(h),
+            C.byref(cfg_c) if cfg_c is not None else None, _stream_handle(stream, dev))
+    _lib.check(rc)
+    return h
+
+
+def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | None = None,
+                        up_col0: int | None = None, gate_col0: int | None = None,
+                        n_out: int | None = None):
+    """Single-kernel SwiGLU.  C = silu(gate) * up  where [up|gate] = A @ W.
+
+    A : [M, K]  bf16
+    W : [K, 2N] bf16 - left half = W_up, right half = W_gate
+    returns: [M, N] bf16
+
+    ``up_col0``/``gate_col0``/``n_out`` (all three together) select two column
+    windows of a wider W instead: ``h = silu(A @ W[:, gate_col0:gate_col0+n_out])
+    * (A @ W[:, up_col0:up_col0+n_out])`` - how a column-parallel shard addresses
+    the unsplit packed weight.
+    """
+    _check_matrix(A, "A")
+    _check_matrix(W, "W")
+    M, K = A.shape
+    K2, N2 = W.shape
+    if K != K2:
+        raise ValueError(f"K mismatch: A.K={K} vs W.K={K2}")
+    windowed = (up_col0 is not None, gate_col0 is not None, n_out is not None)
+    if any(windowed) and not all(windowed):
+        raise ValueError("up_col0, gate_col0 and n_out must be given together")
+    if all(windowed):
+        N = int(n_out)
+        c_up, c_gate = int(up_col0), int(gate_col0)
+        if N < 1 or c_up < 0 or c_gate < 0 or max(c_up, c_gate) + N > N2:
+            raise ValueError(f"column windows [{c_up},+{N}) / [{c_gate},+{N}) outside W's {N2} columns")
+    else:
+        if N2 % 2 != 0:
+            raise ValueError(f"W's 2nd dim ({N2}) must be even")
+        N = N2 // 2
+        c_up, c_gate = 0, N
+    if K % 8 or N % 8 or c_up % 8 or c_gate % 8:
+        raise ValueError(f"K={K}, N={N} and the column offsets must be multiples of 8")
+    dev = _same_device(("A", A), ("W", W))
+    h = _prep_out(out, M, N, dev)
+    if os.environ.get("SWIGLU_B200_AUTOTUNE") == "1" and config is None and not any(windowed) \
+            and tile_table.lookup(_lib.FORM_FUSED_SWIGLU, M, N, K) is None:
+        tune_matmul_fused_swiglu(A, W)
+    cfg = _pick_config(_lib.FORM_FUSED_SWIGLU, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    lib = _lib.load()
+    ldw = _ld(W) if W.shape[0] > 1 else max(_ld(W), (N2 + 7) // 8 * 8)
+    with torch.cuda.device(dev):
+        rc = lib.sgl_matmul_fused_swiglu(
+            A.data_ptr(), W.data_ptr(), h.data_ptr(), M, N, K, _ld(A), ldw, _ld(h),
+            c_up, c_gate, C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+    return h
+
+
+def tune_matmul_silu_mul(A, B_gate, up, *, verbose=False, persist=False) -> TileConfig:
+    """Sweep the tile table for this problem (reference: ``_tune``,
+    ``swiglu/matmul_silu_mul.py:114-139``) and remember the winner."""
+    M, K = A.shape
+    N = B_gate.shape[1]
+    out = torch.empty((M, N), dtype=DTYPE, device=A.device)
+    return tile_table.autotune(
+        _lib.FORM_SILU_MUL, lambda cfg: matmul_silu_mul(A, B_gate, up, out=out, config=cfg),
+        M, N, K, verbose=verbose, persist=persist)
+
+
+def tune_matmul_fused_swiglu(A, W, *, verbose=False, persist=False) -> TileConfig:
+    """Sweep the tile table for this problem (reference: ``_tune``,
+    ``swiglu/matmul_fused_swiglu.py:122-149``) and remember the winner."""
+    M, K = A.shape
+    N = W.shape[1] // 2
+    out = torch.empty((M, N), dtype=DTYPE, device=A.device)
+    return tile_table.autotune(
+        _lib.FORM_FUSED_SWIGLU, lambda cfg: matmul_fused_swiglu(A, W, out=out, config=cfg),
+        M, N, K, verbose=verbose, persist=persist)
