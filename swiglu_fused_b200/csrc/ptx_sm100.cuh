@@ -69,16 +69,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  Polls the barrier until the phase with the given parity has
-// completed, the CTA-wide abort flag is raised, or `limit_ns` elapses.
+// completed, the CTA-wide abort flag is raised, or `limit_ns` elapses.  The
+// clock is only consulted every 256 failed polls (reading %globaltimer costs
+// far more than a poll, and each try_wait already suspends for a while), so a
+// wait that completes promptly never touches it.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns,
                                           const volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 31u) == 0u) {
+    if ((it & 255u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (globaltimer_ns() - t0 > limit_ns) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        return false;
+      }
     }
   }
 }

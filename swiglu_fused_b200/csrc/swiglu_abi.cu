@@ -143,6 +143,15 @@ const sgl_config kTable[] = {
 };
 constexpr int kTableSize = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 
+// Entries of kTable a form can run: at least a two-stage ring must fit.
+int form_entries(int form, int* idx) {
+  int n = 0;
+  for (int i = 0; i < kTableSize; ++i) {
+    if (variant(form, kTable[i].cta_group, kTable[i].block_k).max_stages >= 2) idx[n++] = i;
+  }
+  return n;
+}
+
 // ---------------------------------------------------------------- per-device state
 
 struct DeviceInfo {
@@ -413,16 +422,19 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
 int sgl_config_count(int form) {
   if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
-  return kTableSize;
+  int idx[kTableSize];
+  return form_entries(form, idx);
 }
 
 int sgl_config_get(int form, int index, sgl_config* out) {
   if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
   if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
-  if (index < 0 || index >= kTableSize)
-    return fail(SGL_ERR_BAD_ARGUMENT, "config index %d outside [0, %d)", index, kTableSize);
-  *out = kTable[index];
+  int idx[kTableSize];
+  const int n = form_entries(form, idx);
+  if (index < 0 || index >= n)
+    return fail(SGL_ERR_BAD_ARGUMENT, "config index %d outside [0, %d)", index, n);
+  *out = kTable[idx[index]];
   out->stages = variant(form, out->cta_group, out->block_k).max_stages;
   return SGL_OK;
 }

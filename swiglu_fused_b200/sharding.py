@@ -1,0 +1,150 @@
+"""Multi-GPU launchers: one process per GPU (``torch.distributed``), no collective
+unless the caller asks for the gathered output.
+
+The reference is single-GPU (every launch goes to one device's null stream,
+``swiglu/matmul_silu_mul.py:91-94``); these launchers are the multi-GPU form of
+its two operators:
+
+* **M-sharded** (tokens): rank r owns rows ``[r0, r0+rows)`` of ``x`` and ``h``,
+  the weight is replicated, nothing is exchanged.  ``h`` stays row-sharded, which
+  is what the row-independent down-projection that follows wants.
+* **N-sharded** (column-parallel): rank r owns output columns ``[c0, c0+cols)``
+  and reads the matching ``up`` and ``gate`` column windows of the packed weight
+  in place.  ``gather=True`` additionally all-gathers ``h`` over NCCL so every
+  rank ends with the full ``[M, N]``.
+
+All functions work with any initialised process group; the host-side logic is
+exercised on CPU with the gloo backend (the kernels themselves need a B200).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+ROW_ALIGN = 256   # a CTA pair's tile height: shard boundaries never split a pair tile
+COL_ALIGN = 128   # the fused form's tile width
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Half-open range ``[begin, begin + count)`` owned by one rank."""
+
+    begin: int
+    count: int
+
+    @property
+    def end(self) -> int:
+        return self.begin + self.count
+
+
+def row_shard(M: int, world: int, rank: int, align: int = ROW_ALIGN) -> Shard:
+    return Shard(*_lib.shard_range(M, align, world, rank))
+
+
+def col_shard(N: int, world: int, rank: int, align: int = COL_ALIGN) -> Shard:
+    return Shard(*_lib.shard_range(N, align, world, rank))
+
+
+def init_from_env(backend: str | None = None) -> tuple[int, int, int]:
+    """Join the process group described by RANK / WORLD_SIZE / MASTER_* (torchrun).
+
+    Returns ``(rank, world, local_rank)``; with WORLD_SIZE unset or 1 nothing is
+    initialised and ``(0, 1, 0)`` is returned.
+    """
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1:
+        return 0, 1, local_rank
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        if backend is None:
+            backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kw = {}
+        if backend == "nccl":
+            torch.cuda.set_device(local_rank)
+            kw["device_id"] = torch.device("cuda", local_rank)
+        dist.init_process_group(backend, rank=rank, world_size=world, **kw)
+    return rank, world, local_rank
+
+
+def fused_swiglu_m_sharded(x_local: torch.Tensor, w: torch.Tensor, *, out=None, stream=None,
+                           config=None, op=None) -> torch.Tensor:
+    """This rank's rows of ``h``: ``silu(x_local @ W_gate) * (x_local @ W_up)``.
+
+    ``x_local`` is the rank's row block of x (see ``row_shard``), ``w`` the full
+    packed weight, replicated on every rank.  No communication.
+    """
+    if op is None:
+        from .ops import matmul_fused_swiglu as op
+    return op(x_local, w, out=out, stream=stream, config=config)
+
+
+def fused_swiglu_n_sharded(x: torch.Tensor, w: torch.Tensor, *, rank: int, world: int,
+                           n_total: int | None = None, gather: bool = False,
+                           group=None, out=None, stream=None, config=None,
+                           op=None) -> torch.Tensor:
+    """Column-parallel fused SwiGLU.
+
+    ``x`` is replicated.  ``w`` is the unsplit packed weight ``[K, 2N]``; the rank
+    computes its column block ``[c0, c0+cols)`` from the windows ``w[:, c0:...]``
+    (up) and ``w[:, N+c0:...]`` (gate) without copying them.
+
+    gather=False: returns the local block ``[M, cols]``.
+    gather=True : returns the full ``[M, N]`` on every rank.  Each rank's kernel
+                  writes its block into place in the full buffer, and the other
+                  blocks arrive through one NCCL all-gather of column blocks.
+    """
+    if op is None:
+        from .ops import matmul_fused_swiglu as op
+    N = n_total if n_total is not None else w.shape[1] // 2
+    M = x.shape[0]
+    mine = col_shard(N, world, rank)
+    if not gather:
+        if mine.count == 0:
+            return x.new_empty((M, 0))
+        return op(x, w, up_col0=mine.begin, gate_col0=N + mine.begin, n_out=mine.count,
+                  out=out, stream=stream, config=config)
+
+    full = out if out is not None else x.new_empty((M, N))
+    if mine.count > 0:
+        op(x, w, up_col0=mine.begin, gate_col0=N + mine.begin, n_out=mine.count,
+           out=full[:, mine.begin:mine.end], stream=stream, config=config)
+    if world == 1:
+        return full
+    gather_column_blocks(full, N, rank, world, group=group)
+    return full
+
+
+def gather_column_blocks(full: torch.Tensor, N: int, rank: int, world: int, group=None) -> None:
+    """In-place all-gather of column blocks of ``full`` ([M, N], row-major).
+
+    Column blocks are strided in memory, so each block is broadcast from its
+    owner through a contiguous staging copy; shards are equal-sized except for
+    the ragged tail, which this handles too.
+    """
+    M = full.shape[0]
+    shards = [col_shard(N, world, r) for r in range(world)]
+    equal = len({s.count for s in shards}) == 1 and shards[0].count > 0
+    if equal:
+        cols = shards[0].count
+        send = full[:, shards[rank].begin:shards[rank].end].contiguous()
+        recv = full.new_empty((world, M, cols))
+        dist.all_gather_into_tensor(recv.view(world * M, cols), send, group=group)
+        for r, s in enumerate(shards):
+            if r != rank:
+                full[:, s.begin:s.end].copy_(recv[r])
+        return
+    for r, s in enumerate(shards):
+        if s.count == 0:
+            continue
+        buf = full[:, s.begin:s.end].contiguous() if r == rank else full.new_empty((M, s.count))
+        dist.broadcast(buf, src=r, group=group)
+        if r != rank:
+            full[:, s.begin:s.end].copy_(buf)

@@ -1,0 +1,178 @@
+"""Host-side checks of the C ABI that need no GPU: the library loads, exports
+every symbol the header declares, validates arguments before touching a device,
+and its host logic (tile table, tile order, shard ranges) is right."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from swiglu_fused_b200 import _lib
+from swiglu_fused_b200._lib import SglConfig, TileConfig
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "swiglu_b200.h")
+
+
+def declared_functions():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sgl_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = declared_functions()
+    assert len(names) >= 13
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert sorted(_lib.EXPORTED_SYMBOLS) == names
+    assert lib.sgl_version() >= 100
+
+
+def test_missing_library_is_a_loud_error(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("SWIGLU_B200_LIB", str(tmp_path / "nope.so"))
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.load()
+    monkeypatch.delenv("SWIGLU_B200_LIB")
+    monkeypatch.setattr(_lib, "_lib", None)
+    _lib.load()
+
+
+# Arguments are validated before any CUDA call, so these work without a device.
+BUF = (C.c_uint8 * 4096)()
+P = (C.addressof(BUF) + 15) // 16 * 16
+
+
+@pytest.mark.parametrize("kwargs,code,needle", [
+    (dict(x=0), -1, "x is NULL"),
+    (dict(h=P + 2), -4, "16-byte"),
+    (dict(M=0), -2, ">= 1"),
+    (dict(K=12), -2, "multiples of 8"),
+    (dict(ldx=8), -3, "smaller"),
+    (dict(ldh=68), -3, "multiple of 8"),
+    (dict(gate_col0=60), -4, "multiples of 8"),
+    (dict(up_col0=-8), -10, ">= 0"),
+    (dict(ldw=64), -3, "smaller"),
+    (dict(cfg=SglConfig(3, 64, 0, 8, 0)), -5, "unsupported"),
+    (dict(cfg=SglConfig(2, 64, 7, 8, 0)), -5, "stages"),
+    (dict(cfg=SglConfig(2, 64, 0, 0, 0)), -5, "unsupported"),
+])
+def test_fused_argument_validation(kwargs, code, needle):
+    lib = _lib.load()
+    a = dict(x=P, w=P, h=P, M=64, N=64, K=64, ldx=64, ldw=128, ldh=64, up_col0=0, gate_col0=64,
+             cfg=None, stream=None)
+    a.update(kwargs)
+    cfg = C.byref(a["cfg"]) if a["cfg"] is not None else None
+    rc = lib.sgl_matmul_fused_swiglu(a["x"], a["w"], a["h"], a["M"], a["N"], a["K"], a["ldx"],
+                                     a["ldw"], a["ldh"], a["up_col0"], a["gate_col0"], cfg,
+                                     a["stream"])
+    assert rc == code, lib.sgl_last_error()
+    assert needle in lib.sgl_last_error().decode()
+    with pytest.raises((ValueError, _lib.SglError)):
+        _lib.check(rc)
+
+
+@pytest.mark.parametrize("kwargs,code", [
+    (dict(up=0), -1), (dict(w=P + 8), -4), (dict(N=0), -2), (dict(ldup=32), -3),
+    (dict(ldw=60), -3),
+])
+def test_silu_mul_argument_validation(kwargs, code):
+    lib = _lib.load()
+    a = dict(x=P, w=P, up=P, h=P, M=64, N=64, K=64, ldx=64, ldw=64, ldup=64, ldh=64)
+    a.update(kwargs)
+    rc = lib.sgl_matmul_silu_mul(a["x"], a["w"], a["up"], a["h"], a["M"], a["N"], a["K"],
+                                 a["ldx"], a["ldw"], a["ldup"], a["ldh"], None, None)
+    assert rc == code, lib.sgl_last_error()
+
+
+def test_tile_table_fits_shared_memory():
+    for form in (_lib.FORM_SILU_MUL, _lib.FORM_FUSED_SWIGLU):
+        cfgs = _lib.builtin_configs(form)
+        assert len(cfgs) >= 8
+        for c in cfgs:
+            assert c.stages >= 2
+            smem = _lib.config_smem_bytes(form, c)
+            assert 0 < smem <= 227 * 1024, (form, c, smem)
+            # one more stage must not fit, i.e. `stages` is the deepest ring
+            if c.stages < 8:
+                too_deep = TileConfig(c.cta_group, c.block_k, c.stages + 1, c.group_m)
+                with pytest.raises(ValueError):
+                    _lib.config_smem_bytes(form, too_deep)
+    # the pair kernels at BLOCK_K=64 keep at least 5 stages in flight
+    assert _lib.builtin_configs(_lib.FORM_FUSED_SWIGLU)[0].stages >= 5
+    assert _lib.builtin_configs(_lib.FORM_SILU_MUL)[0].stages >= 5
+
+
+def test_default_config_uses_pairs_only_when_there_are_two_row_tiles():
+    assert _lib.default_config(_lib.FORM_FUSED_SWIGLU, 64, 14336, 4096).cta_group == 1
+    assert _lib.default_config(_lib.FORM_FUSED_SWIGLU, 128, 14336, 4096).cta_group == 1
+    assert _lib.default_config(_lib.FORM_FUSED_SWIGLU, 32768, 12288, 3072).cta_group == 2
+    with pytest.raises(ValueError):
+        _lib.default_config(_lib.FORM_FUSED_SWIGLU, 32768, 12290, 3072)
+
+
+def model_tile_coord(t, tiles_m, tiles_n, group_m):
+    """Independent Python model of the GROUP_SIZE_M order."""
+    per_band = group_m * tiles_n
+    band = t // per_band
+    first = band * group_m
+    rows = min(group_m, tiles_m - first)
+    r = t % per_band
+    return first + r % rows, r // rows
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,group_m", [
+    (1, 1, 8), (1, 112, 8), (128, 96, 8), (7, 5, 4), (9, 3, 16), (10, 7, 3), (64, 48, 1),
+    (33, 2, 32), (5, 1, 2),
+])
+def test_tile_order_is_a_bijection_and_matches_the_model(tiles_m, tiles_n, group_m):
+    seen = set()
+    for t in range(tiles_m * tiles_n):
+        mn = _lib.tile_coord(t, tiles_m, tiles_n, group_m)
+        assert mn == model_tile_coord(t, tiles_m, tiles_n, group_m)
+        assert 0 <= mn[0] < tiles_m and 0 <= mn[1] < tiles_n
+        seen.add(mn)
+    assert len(seen) == tiles_m * tiles_n
+    with pytest.raises(ValueError):
+        _lib.tile_coord(tiles_m * tiles_n, tiles_m, tiles_n, group_m)
+
+
+def test_tile_order_keeps_a_band_of_rows_together():
+    # the first group_m*tiles_n tiles touch only the first group_m tile rows
+    tiles_m, tiles_n, g = 128, 96, 8
+    rows = {_lib.tile_coord(t, tiles_m, tiles_n, g)[0] for t in range(g * tiles_n)}
+    assert rows == set(range(g))
+
+
+@pytest.mark.parametrize("total,align,world", [
+    (32768, 256, 8), (32768, 256, 1), (28672, 128, 8), (1000, 256, 4), (64, 256, 8),
+    (14336, 128, 3), (0, 8, 2), (4104, 8, 5),
+])
+def test_shard_ranges_partition_the_items(total, align, world):
+    pos = 0
+    sizes = []
+    for r in range(world):
+        b, c = _lib.shard_range(total, align, world, r)
+        assert b == pos and c >= 0
+        if b + c < total:
+            assert (b + c) % align == 0
+        pos = b + c
+        sizes.append(c)
+    assert pos == total
+    whole = [s for s in sizes if s % align == 0 and s > 0]
+    if whole:
+        assert max(whole) - min(whole) <= align
+    with pytest.raises(ValueError):
+        _lib.shard_range(total, align, world, world)
+
+
+def test_query_without_device_reports_cuda_error_not_crash():
+    import torch
+    if torch.cuda.is_available():
+        assert _lib.query(_lib.QUERY_SM_COUNT) > 0
+    else:
+        with pytest.raises(_lib.SglError):
+            _lib.query(_lib.QUERY_SM_COUNT)
+    assert _lib.kernel_launches() >= 0

@@ -1,0 +1,275 @@
+"""Parity of the CUDA kernels (called through the C ABI) with the CPU oracle.
+
+Tolerance (stated by the task, checked by ``swiglu_oracle.compare``): at least
+99.9 % of the elements within 1 bf16 ulp of the oracle and a floored relative
+error <= 1e-2, the floor being ``max(|ref|, 2**-7 * mean|ref|)``.
+Where two kernel results must be identical (determinism, row/column shards,
+schedules that only reorder tiles) the comparison is bit-exact.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import swiglu_oracle as orc
+from swiglu_fused_b200 import TileConfig, _lib, matmul_fused_swiglu, matmul_silu_mul
+from swiglu_fused_b200.workloads import make_inputs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# Every kernel variant: (cta_group, block_k).
+VARIANTS_FUSED = [(1, 64), (1, 128), (2, 64), (2, 128)]
+VARIANTS_SILU_MUL = [(1, 64), (2, 64), (2, 128)]   # (1, 128) does not fit shared memory
+
+
+def bits(t):
+    return t.contiguous().view(torch.int16)
+
+
+def bf16(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    _lib.device_status()   # raises if any kernel wait timed out
+
+
+def silu_mul_problem(M, K, N, seed):
+    inp = make_inputs(M, K, N, form="silu_mul", seed=seed)
+    up = (inp["x"].float() @ inp["w_up"].float()).to(torch.bfloat16)
+    return inp["x"], inp["w_gate"], up
+
+
+# ---------------------------------------------------------------- golden fixtures
+
+@pytest.mark.parametrize("name", ["fused_64x128x64", "fused_ragged_200x136x264"])
+def test_fused_matches_golden_vectors(golden_dir, name):
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    x, w, gold = bf16(g["x"]), bf16(g["w"]), bf16(g["h"])
+    for cg, bk in VARIANTS_FUSED:
+        h = matmul_fused_swiglu(x.to(DEV), w.to(DEV), config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(h.cpu(), gold)
+        assert rep.ok, f"cta_group={cg} block_k={bk}: {rep}"
+
+
+@pytest.mark.parametrize("name", ["silu_mul_64x128x64", "silu_mul_ragged_130x72x328"])
+def test_silu_mul_matches_golden_vectors(golden_dir, name):
+    g = np.load(os.path.join(golden_dir, name + ".npz"))
+    x, wg, up, gold = bf16(g["x"]), bf16(g["w_gate"]), bf16(g["up"]), bf16(g["h"])
+    for cg, bk in VARIANTS_SILU_MUL:
+        h = matmul_silu_mul(x.to(DEV), wg.to(DEV), up.to(DEV), config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(h.cpu(), gold)
+        assert rep.ok, f"cta_group={cg} block_k={bk}: {rep}"
+
+
+def test_config1_both_forms_match_oracle_and_golden_sample(golden_dir):
+    g = np.load(os.path.join(golden_dir, "c1_512x1024x2048.npz"))
+    M, K, N, stride = 512, 1024, 2048, int(g["sample_stride"])
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=0)
+    x, w = inp["x"], inp["w"]
+    ref32 = orc.fused_swiglu_f32(x, w)
+    h = matmul_fused_swiglu(x.to(DEV), w.to(DEV)).cpu()
+    rep = orc.compare(h, ref32.to(torch.bfloat16), ref32)
+    assert rep.ok, str(rep)
+    rep_g = orc.compare(h.reshape(-1)[::stride].contiguous(), bf16(g["h_fused_sample"]))
+    assert rep_g.ok, str(rep_g)
+
+    w_up, w_gate = w[:, :N].contiguous(), w[:, N:].contiguous()
+    up = (x.float() @ w_up.float()).to(torch.bfloat16)
+    ref32 = orc.silu_mul_f32(x, w_gate, up)
+    h3 = matmul_silu_mul(x.to(DEV), w_gate.to(DEV), up.to(DEV)).cpu()
+    rep3 = orc.compare(h3, ref32.to(torch.bfloat16), ref32)
+    assert rep3.ok, str(rep3)
+
+
+# ---------------------------------------------------------------- shape ladder
+
+LADDER = [(M, K, N) for M in (64, 128, 192, 256, 1024) for N in (128, 256, 384)
+          for K in (64, 128, 1024)]
+ODD = [(1, 8, 8), (7, 72, 40), (129, 200, 136), (257, 64, 520), (300, 1032, 264), (513, 136, 8)]
+
+
+@pytest.mark.parametrize("M,K,N", LADDER + ODD)
+def test_fused_shape_ladder(M, K, N):
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=M * 7 + K * 3 + N)
+    x, w = inp["x"], inp["w"]
+    ref32 = orc.fused_swiglu_f32(x, w)
+    ref = ref32.to(torch.bfloat16)
+    xd, wd = x.to(DEV), w.to(DEV)
+    # guard band: one row above/below and 8 columns left/right stay NaN
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for cg, bk in VARIANTS_FUSED:
+        out = big[1:M + 1, 8:8 + N]
+        matmul_fused_swiglu(xd, wd, out=out, config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(out.cpu(), ref, ref32)
+        assert rep.ok, f"{(M, K, N)} cta_group={cg} block_k={bk}: {rep}"
+        guard = big.clone()
+        guard[1:M + 1, 8:8 + N] = float("nan")
+        assert torch.isnan(guard).all(), f"{(M, K, N)} cg={cg} bk={bk}: wrote outside h"
+        big.fill_(float("nan"))
+
+
+@pytest.mark.parametrize("M,K,N", LADDER + ODD)
+def test_silu_mul_shape_ladder(M, K, N):
+    x, wg, up = silu_mul_problem(M, K, N, seed=M * 5 + K * 11 + N)
+    ref32 = orc.silu_mul_f32(x, wg, up)
+    ref = ref32.to(torch.bfloat16)
+    xd, wd, ud = x.to(DEV), wg.to(DEV), up.to(DEV)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for cg, bk in VARIANTS_SILU_MUL:
+        out = big[1:M + 1, 8:8 + N]
+        matmul_silu_mul(xd, wd, ud, out=out, config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(out.cpu(), ref, ref32)
+        assert rep.ok, f"{(M, K, N)} cta_group={cg} block_k={bk}: {rep}"
+        guard = big.clone()
+        guard[1:M + 1, 8:8 + N] = float("nan")
+        assert torch.isnan(guard).all(), f"{(M, K, N)} cg={cg} bk={bk}: wrote outside h"
+        big.fill_(float("nan"))
+
+
+# ---------------------------------------------------------------- layouts and schedules
+
+def test_strided_inputs_equal_dense_inputs():
+    M, K, N = 384, 264, 392
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=11)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    dense = matmul_fused_swiglu(x, w)
+    xs = torch.zeros((M, K + 24), dtype=torch.bfloat16, device=DEV)[:, :K]
+    ws = torch.zeros((K, 2 * N + 40), dtype=torch.bfloat16, device=DEV)[:, :2 * N]
+    xs.copy_(x)
+    ws.copy_(w)
+    assert torch.equal(bits(matmul_fused_swiglu(xs, ws)), bits(dense))
+
+    x3, wg, up = (t.to(DEV) for t in silu_mul_problem(M, K, N, seed=12))
+    dense3 = matmul_silu_mul(x3, wg, up)
+    ups = torch.zeros((M, N + 8), dtype=torch.bfloat16, device=DEV)[:, :N]
+    ups.copy_(up)
+    assert torch.equal(bits(matmul_silu_mul(x3, wg, ups)), bits(dense3))
+
+
+def test_results_do_not_depend_on_schedule_or_ring_depth():
+    M, K, N = 1024, 512, 1024
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=21)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    base = matmul_fused_swiglu(x, w, config=TileConfig(2, 64, 0, 8))
+    for cfg in (TileConfig(2, 64, 2, 1, max_ctas=4),    # 32 tiles on 2 CTA pairs, shallow ring
+                TileConfig(2, 64, 3, 3, max_ctas=6),
+                TileConfig(2, 64, 0, 32),
+                TileConfig(1, 64, 2, 5, max_ctas=3)):
+        assert torch.equal(bits(matmul_fused_swiglu(x, w, config=cfg)), bits(base)), cfg
+    x3, wg, up = (t.to(DEV) for t in silu_mul_problem(M, K, N, seed=22))
+    base3 = matmul_silu_mul(x3, wg, up, config=TileConfig(2, 64, 0, 8))
+    for cfg in (TileConfig(2, 64, 2, 1, max_ctas=2), TileConfig(1, 64, 2, 4, max_ctas=5),
+                TileConfig(2, 64, 0, 16)):
+        assert torch.equal(bits(matmul_silu_mul(x3, wg, up, config=cfg)), bits(base3)), cfg
+
+
+def test_run_to_run_determinism():
+    inp = make_inputs(768, 1024, 640, form="fused_swiglu", seed=31)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    a = matmul_fused_swiglu(x, w)
+    for _ in range(5):
+        assert torch.equal(bits(matmul_fused_swiglu(x, w)), bits(a))
+
+
+def test_row_shards_and_column_windows_equal_slices_of_the_full_result():
+    M, K, N = 1024, 256, 768
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=41)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    full = matmul_fused_swiglu(x, w)
+    world = 4
+    for r in range(world):
+        r0, rows = _lib.shard_range(M, 256, world, r)
+        part = matmul_fused_swiglu(x[r0:r0 + rows], w)
+        assert torch.equal(bits(part), bits(full[r0:r0 + rows]))
+        c0, cols = _lib.shard_range(N, 128, world, r)
+        win = matmul_fused_swiglu(x, w, up_col0=c0, gate_col0=N + c0, n_out=cols)
+        assert torch.equal(bits(win), bits(full[:, c0:c0 + cols]))
+        # shard writing straight into its column block of the full output
+        dst = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+        matmul_fused_swiglu(x, w, up_col0=c0, gate_col0=N + c0, n_out=cols,
+                            out=dst[:, c0:c0 + cols])
+        assert torch.equal(bits(dst[:, c0:c0 + cols]), bits(full[:, c0:c0 + cols]))
+
+
+def test_both_forms_agree_when_up_is_exact():
+    # With up = fp32-exact small integers the silu_mul form (bf16 `up` input) and the
+    # fused form (fp32 `up` accumulator) see the same factors.
+    M, K, N = 256, 64, 256
+    g = torch.Generator().manual_seed(5)
+    x = torch.randint(-2, 3, (M, K), generator=g).to(torch.bfloat16)
+    w_up = torch.randint(-1, 2, (K, N), generator=g).to(torch.bfloat16)
+    w_gate = (torch.randn((K, N), generator=g) * 0.125).to(torch.bfloat16)
+    up = (x.float() @ w_up.float())
+    assert up.abs().max() <= 256           # exactly representable in bf16
+    up = up.to(torch.bfloat16)
+    w = torch.cat([w_up, w_gate], dim=1).contiguous()
+    a = matmul_fused_swiglu(x.to(DEV), w.to(DEV))
+    b = matmul_silu_mul(x.to(DEV), w_gate.to(DEV), up.to(DEV))
+    assert torch.equal(bits(a), bits(b))
+
+
+def test_out_and_stream_arguments_and_no_hidden_allocation():
+    M, K, N = 512, 256, 512
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=51)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    ref = matmul_fused_swiglu(x, w)
+    out = torch.empty_like(ref)
+    side = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    before = torch.cuda.memory_allocated()
+    n0 = _lib.kernel_launches()
+    with torch.cuda.stream(side):
+        got = matmul_fused_swiglu(x, w, out=out)
+    side.synchronize()
+    assert got is out
+    assert _lib.kernel_launches() - n0 == 1
+    assert torch.cuda.max_memory_allocated() == before, "the call allocated device memory"
+    assert torch.equal(bits(out), bits(ref))
+    out.zero_()
+    matmul_fused_swiglu(x, w, out=out, stream=side)
+    side.synchronize()
+    assert torch.equal(bits(out), bits(ref))
+
+
+def test_bad_calls_raise_before_launch():
+    x = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((64, 128), dtype=torch.bfloat16, device=DEV)
+    n0 = _lib.kernel_launches()
+    with pytest.raises(ValueError):
+        matmul_fused_swiglu(x, w[:32])                      # K mismatch
+    with pytest.raises(ValueError):
+        matmul_fused_swiglu(x, w, out=torch.empty((64, 32), dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ValueError):
+        matmul_fused_swiglu(x.t(), w)                       # not row-major
+    with pytest.raises(TypeError):
+        matmul_fused_swiglu(x.float(), w)
+    with pytest.raises(ValueError):
+        matmul_fused_swiglu(x, w, config=TileConfig(2, 64, 9, 8))
+    with pytest.raises(ValueError):
+        matmul_silu_mul(x, w[:, :64].contiguous(),
+                        torch.zeros((32, 64), dtype=torch.bfloat16, device=DEV))
+    with pytest.raises(ValueError):
+        matmul_fused_swiglu(x, w, up_col0=0, gate_col0=100, n_out=32)   # window outside W
+    assert _lib.kernel_launches() == n0
+
+
+def test_extreme_gate_values_saturate_cleanly():
+    # silu(+big) = big, silu(-big) = -0: no NaN/Inf from the exp/rcp path.
+    M, K, N = 128, 64, 128
+    x = torch.zeros((M, K), dtype=torch.bfloat16)
+    x[:, 0] = 1.0
+    w_gate = torch.zeros((K, N), dtype=torch.bfloat16)
+    w_gate[0, :] = torch.linspace(-300, 300, N).to(torch.bfloat16)
+    up = torch.ones((M, N), dtype=torch.bfloat16)
+    h = matmul_silu_mul(x.to(DEV), w_gate.to(DEV), up.to(DEV)).cpu()
+    ref32 = orc.silu_mul_f32(x, w_gate, up)
+    assert torch.isfinite(h.float()).all()
+    rep = orc.compare(h, ref32.to(torch.bfloat16), ref32)
+    assert rep.ok, str(rep)
