@@ -99,14 +99,14 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 // Arrive on a barrier anywhere in the cluster (address from mapa, or a local
 // address, which is also a valid cluster address of the executing CTA).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar,
                                                               uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(
-                   cluster_bar),
+  // Default semantics (release at CTA scope): a cluster-scope release here costs a
+  // full memory fence per ring slot, which serialises the producer.
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
                "r"(bytes)
                : "memory");
 }

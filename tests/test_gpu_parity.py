@@ -261,7 +261,9 @@ def test_bad_calls_raise_before_launch():
 
 
 def test_extreme_gate_values_saturate_cleanly():
-    # silu(+big) = big, silu(-big) = -0: no NaN/Inf from the exp/rcp path.
+    # silu(+big) = big, silu(-big) = -0: no NaN/Inf from the exp/rcp path.  Results whose
+    # magnitude is below 2**-100 may flush to zero (the approximate reciprocal flushes
+    # subnormals), so those are compared by absolute value only.
     M, K, N = 128, 64, 128
     x = torch.zeros((M, K), dtype=torch.bfloat16)
     x[:, 0] = 1.0
@@ -271,5 +273,13 @@ def test_extreme_gate_values_saturate_cleanly():
     h = matmul_silu_mul(x.to(DEV), w_gate.to(DEV), up.to(DEV)).cpu()
     ref32 = orc.silu_mul_f32(x, w_gate, up)
     assert torch.isfinite(h.float()).all()
-    rep = orc.compare(h, ref32.to(torch.bfloat16), ref32)
+    tiny = ref32.abs() < 2.0 ** -100
+    assert (h.float()[tiny].abs() < 2.0 ** -99).all()
+    keep = ~tiny[0]
+    rep = orc.compare(h[:, keep].contiguous(), ref32[:, keep].to(torch.bfloat16).contiguous(),
+                      ref32[:, keep].contiguous())
     assert rep.ok, str(rep)
+    xd = x.to(DEV)
+    w = torch.cat([torch.ones((K, N), dtype=torch.bfloat16) * x[0:1, :].t(), w_gate], dim=1)
+    hf = matmul_fused_swiglu(xd, w.contiguous().to(DEV)).cpu()   # up = 1 through the GEMM
+    assert torch.equal(bits(hf), bits(h))
