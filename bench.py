@@ -135,6 +135,40 @@ def cpu_reference_rate(target_s: float, threads: int) -> dict:
                       f"torch fp32 CPU, {dt:.2f} s", "rows": rows_target, "seconds": dt}
 
 
+def gpu_baselines(x, w, n_out: int, iters: int) -> dict:
+    """Library baselines on the same GPU, same tensors: cuBLAS [M,2N] GEMM alone, plus eager
+    and torch.compile'd ``silu(gu[:, N:]) * gu[:, :N]`` (the reference's B1/B2,
+    ``bench_fused.py:52-62``).  Reported beside the kernel, never used by it."""
+    import torch.nn.functional as F
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    out = {"cublas_gemm_ms": timed(lambda: x @ w)}
+
+    def eager():
+        gu = x @ w
+        return F.silu(gu[:, n_out:]) * gu[:, :n_out]
+
+    out["cublas_plus_eager_act_ms"] = timed(eager)
+    try:
+        act = torch.compile(lambda gu: F.silu(gu[:, n_out:]) * gu[:, :n_out])
+        out["cublas_plus_compiled_act_ms"] = timed(lambda: act(x @ w))
+    except Exception as e:  # inductor unavailable on this box
+        out["cublas_plus_compiled_act_ms"] = None
+        out["compile_error"] = repr(e)[:200]
+    return out
+
+
 def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -190,15 +224,16 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     import torch.distributed as dist
 
-    rows = sharding.row_shard(M_TOTAL, world, rank)
+    m_total = args.rows or M_TOTAL
+    rows = sharding.row_shard(m_total, world, rank)
     # Same global tensors on every rank (seeded CUDA generator); each keeps its rows.
-    inp = make_inputs(M_TOTAL, K_DIM, N_OUT, form="fused_swiglu", seed=0, device=dev,
+    inp = make_inputs(m_total, K_DIM, N_OUT, form="fused_swiglu", seed=0, device=dev,
                       gen_device=str(dev))
     x_full, w = inp["x"], inp["w"]
     x = x_full[rows.begin:rows.end].clone() if world > 1 else x_full
     del x_full, inp
     h = torch.empty((rows.count, N_OUT), dtype=torch.bfloat16, device=dev)
-    flops_total = 2.0 * M_TOTAL * K_DIM * 2 * N_OUT
+    flops_total = 2.0 * m_total * K_DIM * 2 * N_OUT
     flops_local = 2.0 * rows.count * K_DIM * 2 * N_OUT
 
     def barrier():
@@ -237,29 +272,38 @@ def run_ours(args) -> None:
     value = flops_total / (ms_per_step * 1e-3) / 1e12
 
     # ---- end to end: host buffers in, host buffer out, every step ----
-    e2e_steps = max(2, min(args.steps, 8))
-    pipe = HostPipeline(rows.count, K_DIM, N_OUT, device=dev, blocks=8 if rows.count >= 2048 else 1)
-    x_host = torch.empty((rows.count, K_DIM), dtype=torch.bfloat16).pin_memory()
-    w_host = torch.empty((K_DIM, 2 * N_OUT), dtype=torch.bfloat16).pin_memory()
-    h_host = torch.empty((rows.count, N_OUT), dtype=torch.bfloat16).pin_memory()
-    x_host.copy_(x)
-    w_host.copy_(w)
-    for _ in range(2):
-        pipe.run(x_host, w_host, h_host)
-    e2e_launch0 = _lib.kernel_launches()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        pipe.run(x_host, w_host, h_host)
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    e2e_launches = _lib.kernel_launches() - e2e_launch0
-    te = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = flops_total / te.item() / 1e12
-    e2e_same = bool(torch.equal(h_host.to(dev).view(torch.int16), h.view(torch.int16)))
-    del pipe
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(2, min(args.steps, 8))
+        pipe = HostPipeline(rows.count, K_DIM, N_OUT, device=dev,
+                            blocks=8 if rows.count >= 2048 else 1)
+        x_host = torch.empty((rows.count, K_DIM), dtype=torch.bfloat16).pin_memory()
+        w_host = torch.empty((K_DIM, 2 * N_OUT), dtype=torch.bfloat16).pin_memory()
+        h_host = torch.empty((rows.count, N_OUT), dtype=torch.bfloat16).pin_memory()
+        x_host.copy_(x)
+        w_host.copy_(w)
+        for _ in range(2):
+            pipe.run(x_host, w_host, h_host)
+        e2e_launch0 = _lib.kernel_launches()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            pipe.run(x_host, w_host, h_host)
+        torch.cuda.synchronize()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        e2e_launches = _lib.kernel_launches() - e2e_launch0
+        te = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_same = bool(torch.equal(h_host.to(dev).view(torch.int16), h.view(torch.int16)))
+        e2e = {"value": flops_total / te.item() / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": 2 * (x.numel() + w.numel()),
+               "d2h_bytes_per_step": 2 * h.numel(), "ms_per_step": te.item() * 1e3,
+               "steps": e2e_steps, "launches": e2e_launches, "matches_device_run": e2e_same,
+               "note": "per rank: pinned host x and W copied in, h copied out, every step; "
+                       "row blocks pipelined on 3 streams; timed on the host clock around "
+                       "the calls, max over ranks"}
+        del pipe, x_host, w_host, h_host
 
     peaks = load_peaks()
     achieved = flops_local / (elapsed_ms / args.steps * 1e-3) / 1e12   # this rank's kernel
@@ -267,9 +311,11 @@ def run_ours(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong",
-        "vs_baseline": (value / PUBLISHED_V4_TFLOPS) if world == 1 else None,
+        "vs_baseline": (value / PUBLISHED_V4_TFLOPS) if world == 1 and m_total == M_TOTAL else None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "M": M_TOTAL, "K": K_DIM, "N": N_OUT,
+        "config": {"workload": WORKLOAD if m_total == M_TOTAL else
+                   f"reduced-M case of c3 ({m_total} rows) for profiling, not a headline number",
+                   "M": m_total, "K": K_DIM, "N": N_OUT,
                    "rows_per_gpu": rows.count, "parallelism": f"M-sharded x{world}, weights replicated, no collective",
                    "l2": "inputs+output larger than L2 (x+W+h per GPU = "
                          f"{(x.numel() + w.numel() + h.numel()) * 2 / 1e6:.0f} MB > 126 MB), no flush"},
@@ -279,14 +325,11 @@ def run_ours(args) -> None:
                      "frac_of_burst_peak": achieved / peaks["tflops_burst"],
                      "frac_of_nominal_2250": achieved / 2250.0},
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 2 * (x.numel() + w.numel()) * 1,
-                "d2h_bytes_per_step": 2 * h.numel(), "ms_per_step": te.item() * 1e3,
-                "steps": e2e_steps, "launches": e2e_launches, "matches_device_run": e2e_same,
-                "note": "pinned host x and W copied in, h copied out, every step; row blocks pipelined on 3 streams"},
+        "e2e": e2e,
         "gpu_launches": launches,
     }
 
-    if world == 1:
+    if world == 1 and m_total == M_TOTAL:
         # The reference's other operator on the same shape, device-resident.
         inp3 = make_inputs(M_TOTAL, K_DIM, N_OUT, form="silu_mul", seed=0, device=dev,
                            gen_device=str(dev))
@@ -308,6 +351,11 @@ def run_ours(args) -> None:
                             "published_ms": 2.281}
         del inp3, up, h3
         _lib.device_status()
+        if not args.no_gpu_baselines:
+            line["gpu_baselines"] = gpu_baselines(x, w, N_OUT, max(5, args.steps // 2))
+            b = line["gpu_baselines"].get("cublas_plus_compiled_act_ms") or \
+                line["gpu_baselines"].get("cublas_plus_eager_act_ms")
+            line["gpu_baselines"]["speedup_vs_cublas_plus_act"] = b / ms_per_step if b else None
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = {k: v for k, v in cpu_reference_rate(12.0, os.cpu_count() or 1).items()
                                     if k in ("value", "unit", "cores", "kind", "sample")}
@@ -327,6 +375,11 @@ def main() -> None:
     ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU-baseline leg (it takes about 15 s)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override M (profiling a reduced case under ncu); 0 = the full 32768")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-gpu-baselines", action="store_true",
+                    help="skip the cuBLAS (+ eager / compiled activation) legs")
     args = ap.parse_args()
     if args.steps < 1:
         raise SystemExit("--steps must be >= 1")
