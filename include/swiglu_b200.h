@@ -55,7 +55,10 @@ typedef struct sgl_config {
   int32_t stages;    /* shared-memory ring depth; 0 = deepest that fits */
   int32_t group_m;   /* GROUP_SIZE_M of the tile order, in cluster-tile rows; >= 1 */
   int32_t max_ctas;  /* cap on the persistent grid (0 = all SMs); for tests and sweeps */
-  int32_t reserved[3];
+  int32_t l2_hints;  /* L2 eviction priorities, 2 bits each: bits 0-1 x loads, 2-3 weight
+                        loads, 4-5 h stores, 6-7 `up` loads; 0 normal, 1 evict-first,
+                        2 evict-last.  0 = all normal. */
+  int32_t reserved[2];
 } sgl_config;
 
 /*

@@ -47,7 +47,8 @@ class SglConfig(C.Structure):
         ("stages", C.c_int32),
         ("group_m", C.c_int32),
         ("max_ctas", C.c_int32),
-        ("reserved", C.c_int32 * 3),
+        ("l2_hints", C.c_int32),
+        ("reserved", C.c_int32 * 2),
     ]
 
 
@@ -64,14 +65,15 @@ class TileConfig:
     stages: int = 0
     group_m: int = 8
     max_ctas: int = 0
+    l2_hints: int = 0   # see sgl_config.l2_hints: 2 bits each for x, weight, h, up
 
     def to_c(self) -> SglConfig:
         return SglConfig(self.cta_group, self.block_k, self.stages, self.group_m, self.max_ctas,
-                         (C.c_int32 * 3)(0, 0, 0))
+                         self.l2_hints, (C.c_int32 * 2)(0, 0))
 
     @staticmethod
     def from_c(c: SglConfig) -> "TileConfig":
-        return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas)
+        return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas, c.l2_hints)
 
 
 class SglError(RuntimeError):

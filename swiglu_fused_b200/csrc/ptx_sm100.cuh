@@ -117,6 +117,20 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
 
+// L2 eviction-priority policy for the .L2::cache_hint forms below.
+// kind: 0 = evict_normal, 1 = evict_first, 2 = evict_last.
+__device__ __forceinline__ uint64_t make_l2_policy(int kind) {
+  uint64_t p;
+  if (kind == 1) {
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  } else if (kind == 2) {
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  } else {
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  }
+  return p;
+}
+
 // 2-D tiled load, global -> this CTA's shared memory, completion reported on
 // `bar` as transaction bytes.  x is the innermost (contiguous) coordinate and
 // x * sizeof(element) must be a multiple of 16 bytes.
@@ -124,18 +138,18 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
 // peer CTA of a CTA pair (no multicast: each CTA loads only its own tile).
 template <bool kPeerBarrier>
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x,
-                                            int y, uint32_t bar) {
+                                            int y, uint32_t bar, uint64_t policy) {
   if constexpr (kPeerBarrier) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.cta_group::2"
-        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
         : "memory");
   } else {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-        " [%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        ".L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar), "l"(policy)
         : "memory");
   }
 }
@@ -143,11 +157,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
 // 2-D tiled store, shared memory -> global; rows/columns outside the tensor
 // are clipped by the hardware.  Part of the executing thread's bulk group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y,
-                                             uint32_t smem_src) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
-                   reinterpret_cast<uint64_t>(map)),
-               "r"(x), "r"(y), "r"(smem_src)
-               : "memory");
+                                             uint32_t smem_src, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint"
+      " [%0, {%1, %2}], [%3], %4;" ::"l"(reinterpret_cast<uint64_t>(map)),
+      "r"(x), "r"(y), "r"(smem_src), "l"(policy)
+      : "memory");
 }
 
 __device__ __forceinline__ void bulk_commit_group() {

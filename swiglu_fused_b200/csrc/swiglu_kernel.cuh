@@ -68,6 +68,7 @@ struct KernelParams {
   int tiles_m, tiles_n; // tile grid in cluster-tile units
   int group_m;          // GROUP_SIZE_M
   int stages;           // shared-memory ring depth actually used
+  int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
   unsigned long long wait_limit_ns;
 };
 
@@ -227,6 +228,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     // =========================== TMA producer ===========================
     if (lane == 0) {
       // Barrier that collects this stage's bytes: the leader CTA's.
+      const uint64_t pol_x = ptx::make_l2_policy(p.l2_hints & 3);
+      const uint64_t pol_w = ptx::make_l2_policy((p.l2_hints >> 2) & 3);
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
@@ -248,7 +251,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < kBlockK / 64; ++j) {
             ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64, m0,
-                                             full);
+                                             full, pol_x);
           }
           const uint32_t b_dst = sB + s * T::kBStageBytes;
 #pragma unroll
@@ -261,7 +264,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             } else {
               col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
             }
-            ptx::tma_load_2d<kCtaGroup == 2>(b_dst + j * T::kBSlabBytes, &tm_w, col, k0, full);
+            ptx::tma_load_2d<kCtaGroup == 2>(b_dst + j * T::kBSlabBytes, &tm_w, col, k0, full,
+                                             pol_w);
           }
           if (++s == stages) {
             s = 0;
@@ -349,13 +353,16 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
     };
 
+    const uint64_t pol_h = ptx::make_l2_policy((p.l2_hints >> 4) & 3);
+    const uint64_t pol_up = ptx::make_l2_policy((p.l2_hints >> 6) & 3);
     int up_issued = 0;  // `up` chunk loads issued so far (lane 0 only)
     auto issue_up = [&](int g) {
       int x, y;
       chunk_xy(g, x, y);
       const int b = g % kUpBufs;
       ptx::mbar_arrive_expect_tx_cluster(my_bar_up + 8 * b, kChunkBytes);
-      ptx::tma_load_2d<false>(up_buf0 + b * kChunkBytes, &tm_up, x, y, my_bar_up + 8 * b);
+      ptx::tma_load_2d<false>(up_buf0 + b * kChunkBytes, &tm_up, x, y, my_bar_up + 8 * b,
+                              pol_up);
     };
     if constexpr (kForm == FORM_SILU_MUL) {
       if (lane == 0) {
@@ -453,7 +460,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (x < p.N && y < p.M) ptx::tma_store_2d(&tm_h, x, y, obuf);
+          if (x < p.N && y < p.M) ptx::tma_store_2d(&tm_h, x, y, obuf, pol_h);
           ptx::bulk_commit_group();
           if constexpr (kForm == FORM_SILU_MUL) {
             // This chunk's `up` buffer has been read by every lane: refill it.

@@ -39,7 +39,8 @@ def _load() -> dict[str, TileConfig]:
                     raw = json.load(f)
                 for k, v in raw.get("entries", {}).items():
                     _table[k] = TileConfig(int(v["cta_group"]), int(v["block_k"]),
-                                           int(v.get("stages", 0)), int(v["group_m"]))
+                                           int(v.get("stages", 0)), int(v["group_m"]), 0,
+                                           int(v.get("l2_hints", 0)))
         return _table
 
 
@@ -57,7 +58,7 @@ def save(path: str | None = None) -> str:
     path = path or os.environ.get("SWIGLU_B200_TILE_TABLE", TABLE_PATH)
     entries = {
         k: {"cta_group": c.cta_group, "block_k": c.block_k, "stages": c.stages,
-            "group_m": c.group_m}
+            "group_m": c.group_m, "l2_hints": c.l2_hints}
         for k, c in sorted(_load().items())
     }
     tmp = path + ".tmp"
