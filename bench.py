@@ -117,18 +117,19 @@ def cpu_reference_rate(target_s: float, threads: int) -> dict:
     from swiglu_fused_b200.workloads import make_inputs
 
     torch.set_num_threads(threads)
-    rows = 128
-    inp = make_inputs(rows, K_DIM, N_OUT, form="fused_swiglu", seed=0)
-    orc.fused_swiglu(inp["x"], inp["w"])               # warm-up (thread pool, pages)
-    t0 = time.perf_counter()
-    orc.fused_swiglu(inp["x"], inp["w"])
-    dt = max(time.perf_counter() - t0, 1e-4)
-    rows_target = int(min(M_TOTAL, max(128, rows * target_s / dt)))
-    rows_target = max(128, rows_target // 128 * 128)
-    x = make_inputs(rows_target, K_DIM, 8, form="fused_swiglu", seed=1)["x"]
-    t0 = time.perf_counter()
-    orc.fused_swiglu(x, inp["w"])
-    dt = time.perf_counter() - t0
+    w = make_inputs(8, K_DIM, N_OUT, form="fused_swiglu", seed=0)["w"]
+    x_all = make_inputs(M_TOTAL, K_DIM, 8, form="fused_swiglu", seed=1)["x"]
+    orc.fused_swiglu(x_all[:256], w)                   # warm-up (thread pool, pages)
+    # Grow the sample until it takes about target_s (or covers the whole workload).
+    rows_target, dt = 1024, 0.0
+    while True:
+        t0 = time.perf_counter()
+        orc.fused_swiglu(x_all[:rows_target], w)
+        dt = time.perf_counter() - t0
+        if rows_target >= M_TOTAL or dt >= 0.5 * target_s:
+            break
+        grow = max(2.0, min(16.0, 0.8 * target_s / max(dt, 1e-3)))
+        rows_target = int(min(M_TOTAL, rows_target * grow)) // 128 * 128
     flops = 2.0 * rows_target * K_DIM * 2 * N_OUT
     return {"value": flops / dt / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
             "sample": f"{rows_target} of {M_TOTAL} rows of the c3 workload, full K and N, "

@@ -53,8 +53,10 @@ def fused_swiglu_f32(x: torch.Tensor, w: torch.Tensor, up_col0: int | None = Non
     ``gate = x @ w[:, gate_col0:+n]`` for column-parallel shards.
     """
     if n_out is None:
-        n_out = w.shape[1] // 2
-        up_col0, gate_col0 = 0, n_out
+        # exactly the reference's expression: one [M, 2N] fp32 GEMM, then the two halves
+        n = w.shape[1] // 2
+        gate_up_f32 = x.float() @ w.float()
+        return F.silu(gate_up_f32[:, n:]) * gate_up_f32[:, :n]
     xf = x.float()
     up = xf @ w[:, up_col0:up_col0 + n_out].float()
     gate = xf @ w[:, gate_col0:gate_col0 + n_out].float()

@@ -56,3 +56,53 @@ def test_fused_swiglu_agrees_with_the_reference_kernel(M, K, N):
     assert r_ours.frac_exact >= r_theirs.frac_exact
     both = orc.compare(ours, theirs)
     assert both.frac_within_1ulp >= 0.99 and both.max_floored_rel <= 1e-2, str(both)
+
+
+def _median_ms(fn, iters=12):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    return sorted(ts)[len(ts) // 2]
+
+
+def test_full_size_results_agree_and_this_build_is_not_slower(capsys):
+    """Benchmark shape 32768 x 3072 x 12288: outputs agree with the reference's kernels and
+    the kernels of this build are at least as fast on the same GPU (interleaved timing)."""
+    M, K, N = 32768, 3072, 12288
+    g = torch.Generator(device=DEV).manual_seed(0)
+    x = torch.randn((M, K), device=DEV, dtype=torch.bfloat16, generator=g)
+    w = (torch.randn((K, 2 * N), device=DEV, dtype=torch.float32, generator=g)
+         * K ** -0.5).to(torch.bfloat16)
+    ours = matmul_fused_swiglu(x, w)
+    theirs = ref_kernels.matmul_fused_swiglu(x, w)
+    rep = orc.compare(ours, theirs)
+    assert rep.frac_within_1ulp >= 0.99 and rep.max_floored_rel <= 1e-2, str(rep)
+    t_ours = _median_ms(lambda: matmul_fused_swiglu(x, w, out=ours))
+    t_theirs = _median_ms(lambda: ref_kernels.matmul_fused_swiglu(x, w))
+    t_ours2 = _median_ms(lambda: matmul_fused_swiglu(x, w, out=ours))
+    del theirs
+
+    w_gate = w[:, N:].contiguous()
+    up = x @ w[:, :N].contiguous()
+    ours3 = matmul_silu_mul(x, w_gate, up)
+    theirs3 = ref_kernels.matmul_silu_mul(x, w_gate, up)
+    rep3 = orc.compare(ours3, theirs3)
+    assert rep3.ok and rep3.frac_exact >= 0.9999, str(rep3)
+    t3_ours = _median_ms(lambda: matmul_silu_mul(x, w_gate, up, out=ours3))
+    t3_theirs = _median_ms(lambda: ref_kernels.matmul_silu_mul(x, w_gate, up))
+    torch.cuda.synchronize()
+    _lib.device_status()
+    with capsys.disabled():
+        print(f"\n[same-GPU comparator] fused_swiglu: this build {min(t_ours, t_ours2):.3f} ms, "
+              f"reference V4 kernel {t_theirs:.3f} ms; silu_mul: this build {t3_ours:.3f} ms, "
+              f"reference V3 kernel {t3_theirs:.3f} ms")
+    assert min(t_ours, t_ours2) <= t_theirs * 1.02
+    assert t3_ours <= t3_theirs * 1.02
