@@ -43,9 +43,9 @@ WORKLOAD = "c3_fused: matmul_fused_swiglu 32768x3072x12288 bf16, W=[W_up|W_gate]
 METRIC = "fused_swiglu_tflops"
 UNIT = "TFLOP/s"
 PUBLISHED_V4_TFLOPS = 1257.0   # reference README, 1x B200, same shape
-# DRAM traffic of one full-size launch (dram__bytes_read.sum + dram__bytes_write.sum from an
-# ncu capture; see profiles/).  None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM traffic of one full-size launch on one GPU: dram__bytes_read.sum + dram__bytes_write.sum
+# from a one-pass ncu capture of this workload (profiles/swiglu_kernel_fused_c3_full_dram_traffic.md).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.27e9
 
 
 def load_peaks() -> dict:
@@ -322,7 +322,9 @@ def run_ours(args) -> None:
                          f"{(x.numel() + w.numel() + h.numel()) * 2 / 1e6:.0f} MB > 126 MB), no flush"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"],
                      "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "peak_source": peaks["source"],
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (world == 1 and m_total == M_TOTAL) else None,
+                     "algorithmic_bytes": 2.0 * (rows.count * K_DIM + 2 * K_DIM * N_OUT + rows.count * N_OUT),
+                     "peak_source": peaks["source"],
                      "frac_of_burst_peak": achieved / peaks["tflops_burst"],
                      "frac_of_nominal_2250": achieved / 2250.0},
         "clocks": clocks,
