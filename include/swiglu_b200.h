@@ -85,6 +85,21 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
                             int64_t gate_col0, const sgl_config* cfg, void* stream);
 
 /*
+ * Same computation, but every output tile is written to n_dsts (1..8) buffers:
+ * h_dsts[i] is the address of element (0, 0) of this launch's [M, N] block inside
+ * destination i (all with row pitch ldh).  Destinations may be peer-GPU memory
+ * mapped into this process (plain TMA stores over NVLink, no multicast).  This is
+ * the all-gather of the column-parallel launch fused into the kernel: rank r
+ * computes columns [c0, c0+N) and stores them into that column window of every
+ * rank's full-width h.  The caller synchronises the ranks before reading.
+ * The reference is single-GPU; no counterpart there.
+ */
+int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const* h_dsts,
+                                      int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                      int64_t ldw, int64_t ldh, int64_t up_col0,
+                                      int64_t gate_col0, const sgl_config* cfg, void* stream);
+
+/*
  * Tile table access.  Replaces the module-level config lists and _legal /
  * _legal_for_problem (swiglu/matmul_silu_mul.py:46-51,101-111).
  * sgl_config_count: number of built-in configurations for a form.

@@ -24,6 +24,7 @@ QUERY_KERNEL_LAUNCHES = 3
 EXPORTED_SYMBOLS = (
     "sgl_matmul_silu_mul",
     "sgl_matmul_fused_swiglu",
+    "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_config_count",
     "sgl_config_get",
     "sgl_config_default",
@@ -115,6 +116,9 @@ def load() -> C.CDLL:
         lib.sgl_matmul_fused_swiglu.restype = ip
         lib.sgl_matmul_fused_swiglu.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
                                                 i64, cfgp, vp]
+        lib.sgl_matmul_fused_swiglu_multi_dst.restype = ip
+        lib.sgl_matmul_fused_swiglu_multi_dst.argtypes = [vp, vp, C.POINTER(vp), ip, i64, i64,
+                                                          i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_config_count.restype = ip
         lib.sgl_config_count.argtypes = [ip]
         lib.sgl_config_get.restype = ip

@@ -91,7 +91,7 @@ int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int
 // ---------------------------------------------------------------- kernel variants
 
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                          const CUtensorMap, const sgl::KernelParams);
+                          const sgl::OutMaps, const sgl::KernelParams);
 
 struct Variant {
   KernelFn fn;
@@ -269,7 +269,7 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 }
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
-           const CUtensorMap& th, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           const sgl::OutMaps& th, int n_dst, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -341,6 +341,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.group_m = cfg.group_m;
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
+  p.n_dst = n_dst;
   p.wait_limit_ns = g_wait_limit_ns.load();
 
   cudaLaunchConfig_t lc = {};
@@ -392,23 +393,28 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
 
-  CUtensorMap tx, tw, tup, th;
+  CUtensorMap tx, tw, tup;
+  sgl::OutMaps th;
+  std::memset(&th, 0, sizeof(th));
   if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "x")) ||
       (rc = make_map(&tw, w_gate, K, N, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "w_gate")) ||
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
-      (rc = make_map(&th, h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
+      (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, M, N, K, 0, 0, c, info, stream);
 }
 
-int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
-                            int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
-                            int64_t gate_col0, const sgl_config* cfg, void* stream) {
+static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, int n_dsts,
+                            int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                            int64_t ldh, int64_t up_col0, int64_t gate_col0,
+                            const sgl_config* cfg, void* stream) {
   int rc;
-  if ((rc = validate_ptr(x, "x")) || (rc = validate_ptr(w, "w")) || (rc = validate_ptr(h, "h")))
-    return rc;
+  if ((rc = validate_ptr(x, "x")) || (rc = validate_ptr(w, "w"))) return rc;
+  for (int d = 0; d < n_dsts; ++d) {
+    if ((rc = validate_ptr(h_dsts[d], "h"))) return rc;
+  }
   if ((rc = validate_shape(M, N, K))) return rc;
   if (up_col0 < 0 || gate_col0 < 0)
     return fail(SGL_ERR_BAD_ARGUMENT, "up_col0=%lld and gate_col0=%lld must be >= 0",
@@ -426,15 +432,39 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
 
-  CUtensorMap tx, tw, th;
+  CUtensorMap tx, tw;
+  sgl::OutMaps th;
+  std::memset(&th, 0, sizeof(th));
   if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "x")) ||
       (rc = make_map(&tw, w, K, ldw, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     "w")) ||
-      (rc = make_map(&th, h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
+                     "w")))
     return rc;
-  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th, th, M, N, K, up_col0, gate_col0, c, info,
-                stream);
+  for (int d = 0; d < n_dsts; ++d) {
+    if ((rc = make_map(&th.m[d], h_dsts[d], M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       "h")))
+      return rc;
+  }
+  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, M, N, K, up_col0, gate_col0,
+                c, info, stream);
+}
+
+int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
+                            int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
+                            int64_t gate_col0, const sgl_config* cfg, void* stream) {
+  void* dst[1] = {h};
+  return fused_swiglu_impl(x, w, dst, 1, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg, stream);
+}
+
+int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const* h_dsts,
+                                      int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                      int64_t ldw, int64_t ldh, int64_t up_col0,
+                                      int64_t gate_col0, const sgl_config* cfg, void* stream) {
+  if (!h_dsts) return fail(SGL_ERR_NULL_POINTER, "h_dsts is NULL");
+  if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
+    return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
+  return fused_swiglu_impl(x, w, h_dsts, n_dsts, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg,
+                           stream);
 }
 
 int sgl_config_count(int form) {

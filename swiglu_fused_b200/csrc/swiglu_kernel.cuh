@@ -21,6 +21,9 @@
 //   * with kCtaGroup == 2 a CTA pair computes a 256-row tile with
 //     tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of x and its own
 //     half of the B operand (no multicast loads anywhere);
+//   * the epilogue can write each output tile to several destination buffers
+//     (this GPU's and its peers', plain TMA stores over NVLink): the all-gather
+//     of a column-parallel launch is fused into the kernel;
 //   * every wait is bounded; a timeout raises a CTA-wide abort flag, records an
 //     error word in g_status and the kernel drains and exits.
 #pragma once
@@ -61,6 +64,14 @@ enum : unsigned {
 // First-error record, readable from the host with cudaMemcpyFromSymbol.
 __device__ unsigned int g_status[8];
 
+constexpr int kMaxDst = 8;          // output copies one launch can write (this GPU + 7 peers)
+
+// Tensor maps of the output: one per destination buffer.  A plain call has one;
+// the column-parallel gather writes the same tile to every rank's buffer.
+struct OutMaps {
+  CUtensorMap m[kMaxDst];
+};
+
 struct KernelParams {
   int M, N, K;          // N = output columns of h
   int b_col0;           // first B column: gate (silu_mul form) / up (fused form)
@@ -69,6 +80,7 @@ struct KernelParams {
   int group_m;          // GROUP_SIZE_M
   int stages;           // shared-memory ring depth actually used
   int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
+  int n_dst;            // destinations in OutMaps actually used (>= 1)
   unsigned long long wait_limit_ns;
 };
 
@@ -157,7 +169,7 @@ __device__ __forceinline__ void report_error(unsigned code, unsigned detail, int
 template <int kForm, int kCtaGroup, int kBlockK>
 __global__ void __launch_bounds__(kNumThreads, 1)
 swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
-              const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ CUtensorMap tm_h,
+              const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ OutMaps tm_h,
               const KernelParams p) {
   using T = KernelTraits<kForm, kCtaGroup, kBlockK>;
   static_assert(kBlockK == 64 || kBlockK == 128, "BLOCK_K is 64 or 128");
@@ -210,7 +222,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_x);
     ptx::prefetch_tensormap(&tm_w);
-    ptx::prefetch_tensormap(&tm_h);
+    for (int d = 0; d < p.n_dst; ++d) ptx::prefetch_tensormap(&tm_h.m[d]);
     if constexpr (kForm == FORM_SILU_MUL) ptx::prefetch_tensormap(&tm_up);
   }
   if (warp == 1) {
@@ -460,7 +472,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (x < p.N && y < p.M) ptx::tma_store_2d(&tm_h, x, y, obuf, pol_h);
+          if (x < p.N && y < p.M) {
+            // One store per destination buffer (local, then peers over NVLink), all
+            // reading the same staging buffer; they form one bulk group.
+            for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&tm_h.m[d], x, y, obuf, pol_h);
+          }
           ptx::bulk_commit_group();
           if constexpr (kForm == FORM_SILU_MUL) {
             // This chunk's `up` buffer has been read by every lane: refill it.

@@ -180,6 +180,39 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     return h
 
 
+def matmul_fused_swiglu_multi_dst(A, W, dst_ptrs, ldh: int, *, up_col0: int, gate_col0: int,
+                                  n_out: int, stream=None, config: TileConfig | None = None):
+    """Fused SwiGLU whose output block is written to several buffers at once.
+
+    ``dst_ptrs[i]`` is the device address of element (0, 0) of this launch's
+    ``[M, n_out]`` block inside destination ``i`` (row pitch ``ldh`` elements, bf16);
+    destinations may be peer-GPU buffers mapped into this process.  Used by the
+    column-parallel launcher to fuse the all-gather of ``h`` into the kernel.  The
+    caller owns the buffers and the cross-rank synchronisation.
+    """
+    _check_matrix(A, "A")
+    _check_matrix(W, "W")
+    M, K = A.shape
+    if W.shape[0] != K:
+        raise ValueError(f"K mismatch: A.K={K} vs W.K={W.shape[0]}")
+    N = int(n_out)
+    if N < 1 or up_col0 < 0 or gate_col0 < 0 or max(up_col0, gate_col0) + N > W.shape[1]:
+        raise ValueError("column windows outside W")
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError(f"need 1..8 destinations, got {len(dst_ptrs)}")
+    dev = _same_device(("A", A), ("W", W))
+    cfg = _pick_config(_lib.FORM_FUSED_SWIGLU, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.sgl_matmul_fused_swiglu_multi_dst(
+            A.data_ptr(), W.data_ptr(), arr, len(dst_ptrs), M, N, K, _ld(A), _ld(W), int(ldh),
+            int(up_col0), int(gate_col0), C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+
+
 def tune_matmul_silu_mul(A, B_gate, up, *, verbose=False, persist=False) -> TileConfig:
     """Sweep the tile table for this problem (reference: ``_tune``,
     ``swiglu/matmul_silu_mul.py:114-139``) and remember the winner."""

@@ -74,6 +74,56 @@ def init_from_env(backend: str | None = None) -> tuple[int, int, int]:
     return rank, world, local_rank
 
 
+class SymmetricOutput:
+    """A full-width ``[M, N]`` bf16 output buffer on every rank, each mapped into every
+    other rank's address space (``torch.distributed._symmetric_memory``; multicast
+    objects are not requested - peers are reached with plain stores).  Collective:
+    every rank of ``group`` constructs it with the same shape."""
+
+    def __init__(self, M: int, N: int, device, group=None):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.M, self.N = M, N
+        self.group = group if group is not None else dist.group.WORLD
+        self.tensor = symm_mem.empty((M, N), dtype=torch.bfloat16, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+
+    def barrier(self) -> None:
+        """Device-side barrier across the ranks on the current stream."""
+        self.handle.barrier(channel=0)
+
+
+def fused_swiglu_n_sharded_fused_gather(x: torch.Tensor, w: torch.Tensor, out: SymmetricOutput, *,
+                                        n_total: int | None = None, stream=None, config=None):
+    """Column-parallel fused SwiGLU with the all-gather of ``h`` inside the kernel.
+
+    Every rank computes its column block and its epilogue stores each finished tile into
+    that column window of EVERY rank's ``out`` buffer (its own, then the peers' over
+    NVLink), so the transfer overlaps the remaining tiles.  Two device-side barriers
+    bracket the launch: nobody overwrites a buffer a peer may still be reading, and
+    nobody reads before every peer's stores have landed.  Returns ``out.tensor``
+    (the full ``[M, N]``) on every rank.
+    """
+    from .ops import matmul_fused_swiglu_multi_dst
+
+    N = n_total if n_total is not None else w.shape[1] // 2
+    rank, world = out.rank, out.world
+    mine = col_shard(N, world, rank)
+    out.barrier()
+    if mine.count > 0:
+        order = [rank] + [r for r in range(world) if r != rank]
+        dsts = [out.ptrs[r] + 2 * mine.begin for r in order]
+        matmul_fused_swiglu_multi_dst(x, w, dsts, out.tensor.stride(0), up_col0=mine.begin,
+                                      gate_col0=N + mine.begin, n_out=mine.count,
+                                      stream=stream, config=config)
+    out.barrier()
+    return out.tensor
+
+
 def fused_swiglu_m_sharded(x_local: torch.Tensor, w: torch.Tensor, *, out=None, stream=None,
                            config=None, op=None) -> torch.Tensor:
     """This rank's rows of ``h``: ``silu(x_local @ W_gate) * (x_local @ W_up)``.

@@ -45,6 +45,15 @@ def _worker(rank, world, port, M, K, N, results):
 
     full = sharding.fused_swiglu_n_sharded(x, w, rank=rank, world=world, gather=True)
     ok_g = same(full, full_ref)
+    # all-gather fused into the kernel: tiles stored straight into every rank's buffer
+    sym = sharding.SymmetricOutput(M, N, dev)
+    ok_f = True
+    for _ in range(2):                      # twice: the buffer is reused
+        sym.tensor.zero_()
+        got = sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym)
+        torch.cuda.synchronize()
+        ok_f = ok_f and same(got, full_ref)
+    ok_g = ok_g and ok_f
     torch.cuda.synchronize()
     _lib.device_status()
     flags = torch.tensor([int(ok_m), int(ok_n), int(ok_g)], dtype=torch.int64, device=dev)
