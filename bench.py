@@ -207,7 +207,7 @@ def run_reference(args) -> None:
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_ours(args) -> None:
@@ -364,13 +364,25 @@ def run_ours(args) -> None:
                                     if k in ("value", "unit", "cores", "kind", "sample")}
 
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
 
 
+def emit(line: dict) -> None:
+    """Write the one JSON line to the process's real stdout."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+# Libraries (NCCL prints its version banner) write to stdout too; keep fd 1 for the JSON
+# line alone and send everything else to stderr.
+_REAL_STDOUT = os.dup(1)
+
+
 def main() -> None:
+    sys.stdout.flush()
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
