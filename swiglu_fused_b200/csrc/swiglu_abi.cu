@@ -228,9 +228,9 @@ int validate_shape(int64_t M, int64_t N, int64_t K) {
 
 // Built-in choice when the caller passes no configuration.  Measured on B200
 // under a sustained (power-capped) load: the fused form runs best with CTA
-// pairs, BLOCK_K = 128 (3-stage ring) and bands of 16 tile rows; the silu_mul
-// form with BLOCK_K = 64 (5 stages) and bands of 8.  A single 128-row tile
-// cannot use a pair.
+// pairs, BLOCK_K = 128 (3-stage ring) and bands of 16 tile rows once there are
+// at least 2048 rows; shorter problems and the silu_mul form with BLOCK_K = 64
+// (6 / 5 stages) and bands of 8.  A single 128-row tile cannot use a pair.
 void default_config(int form, int64_t M, sgl_config* c) {
   std::memset(c, 0, sizeof(*c));
   c->stages = 0;
@@ -238,7 +238,7 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 1;
     c->block_k = 64;
     c->group_m = 8;
-  } else if (form == SGL_FORM_FUSED_SWIGLU) {
+  } else if (form == SGL_FORM_FUSED_SWIGLU && M >= 2048) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;
