@@ -12,6 +12,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -101,25 +102,39 @@ struct Variant {
   int (*smem_bytes)(int);
 };
 
-template <int F, int G, int BK>
+template <int F, int G, int BK, bool IP>
 int smem_bytes_of(int stages) {
-  return sgl::KernelTraits<F, G, BK>::smem_bytes(stages);
+  return sgl::KernelTraits<F, G, BK, IP>::smem_bytes(stages);
 }
 
-template <int F, int G, int BK>
+template <int F, int G, int BK, bool IP = false>
 Variant make_variant() {
-  using T = sgl::KernelTraits<F, G, BK>;
+  using T = sgl::KernelTraits<F, G, BK, IP>;
   Variant v;
-  v.fn = sgl::swiglu_kernel<F, G, BK>;
+  v.fn = sgl::swiglu_kernel<F, G, BK, IP>;
   v.out_cols = T::kOutCols;
   v.stage_bytes = T::kStageBytes;
   v.max_stages = T::max_stages();
-  v.smem_bytes = smem_bytes_of<F, G, BK>;
+  v.smem_bytes = smem_bytes_of<F, G, BK, IP>;
   return v;
 }
 
 // Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
+bool experiment_inplace() {
+  static const bool on = [] {
+    const char* e = std::getenv("SGL_EXPERIMENT_INPLACE");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
 const Variant& variant(int form, int cta_group, int block_k) {
+  static const Variant inplace[4] = {
+      make_variant<sgl::FORM_SILU_MUL, 1, 64, true>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128, true>(),
+      make_variant<sgl::FORM_SILU_MUL, 2, 64, true>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128, true>(),
+  };
+  if (form == 0 && experiment_inplace())
+    return inplace[(cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
   static const Variant table[8] = {
       make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
       make_variant<sgl::FORM_SILU_MUL, 2, 64>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128>(),
@@ -582,6 +597,17 @@ int sgl_set_wait_limit_ns(uint64_t ns) {
   g_wait_limit_ns.store(ns);
   return SGL_OK;
 }
+
+#ifdef SGL_PROFILE
+// Profiling builds only: copy the per-CTA cycle counters (512 x 8 words).
+int sgl_debug_profile(unsigned long long* out) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
+  e = cudaMemcpyFromSymbol(out, sgl::g_prof, sizeof(unsigned long long) * 512 * 8);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyFromSymbol(prof)");
+  return SGL_OK;
+}
+#endif
 
 const char* sgl_last_error(void) { return t_last_error.c_str(); }
 

@@ -72,6 +72,23 @@ struct OutMaps {
   CUtensorMap m[kMaxDst];
 };
 
+// Optional cycle accounting (build with -DSGL_PROFILE): per CTA, cycles each role spent
+// waiting.  [0] MMA waits for a free accumulator, [1] MMA waits for operands, [2] MMA loop
+// total, [3] producer waits for a free ring slot, [4] epilogue waits for an accumulator,
+// [5] epilogue waits for `up`, [6] epilogue busy, [7] tiles.
+#ifdef SGL_PROFILE
+__device__ unsigned long long g_prof[512][8];
+#define SGL_PROF_DECL(name) long long name = 0
+#define SGL_PROF_BEGIN(t) const long long t = clock64()
+#define SGL_PROF_END(acc, t) acc += clock64() - t
+#define SGL_PROF_STORE(slot, v) g_prof[blockIdx.x & 511][slot] = static_cast<unsigned long long>(v)
+#else
+#define SGL_PROF_DECL(name)
+#define SGL_PROF_BEGIN(t)
+#define SGL_PROF_END(acc, t)
+#define SGL_PROF_STORE(slot, v)
+#endif
+
 struct KernelParams {
   int M, N, K;          // N = output columns of h
   int b_col0;           // first B column: gate (silu_mul form) / up (fused form)
@@ -84,7 +101,7 @@ struct KernelParams {
   unsigned long long wait_limit_ns;
 };
 
-template <int kForm, int kCtaGroup, int kBlockK>
+template <int kForm, int kCtaGroup, int kBlockK, bool kInPlace = false>
 struct KernelTraits {
   static constexpr int kOutCols = (kForm == FORM_SILU_MUL) ? 256 : 128;
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
@@ -94,7 +111,9 @@ struct KernelTraits {
   static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
   static constexpr int kBStageBytes = kBSlabs * kBSlabBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kOutStagingBytes = kEpiWarps * kOutBufs * kChunkBytes;
+  // kInPlace (silu_mul form only): the `up` chunk is overwritten with the result and
+  // stored from the same buffer, so no separate output staging is needed.
+  static constexpr int kOutStagingBytes = kInPlace ? 0 : kEpiWarps * kOutBufs * kChunkBytes;
   static constexpr int kUpStagingBytes =
       (kForm == FORM_SILU_MUL) ? kEpiWarps * kUpBufs * kChunkBytes : 0;
   static constexpr int kBarrierBytes = 512;
@@ -166,12 +185,13 @@ __device__ __forceinline__ void report_error(unsigned code, unsigned detail, int
   *reinterpret_cast<volatile int*>(abort_flag) = 1;
 }
 
-template <int kForm, int kCtaGroup, int kBlockK>
+template <int kForm, int kCtaGroup, int kBlockK, bool kInPlace = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
               const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ OutMaps tm_h,
               const KernelParams p) {
-  using T = KernelTraits<kForm, kCtaGroup, kBlockK>;
+  using T = KernelTraits<kForm, kCtaGroup, kBlockK, kInPlace>;
+  static_assert(!kInPlace || kForm == FORM_SILU_MUL, "in-place staging needs an `up` input");
   static_assert(kBlockK == 64 || kBlockK == 128, "BLOCK_K is 64 or 128");
   static_assert(kCtaGroup == 1 || kCtaGroup == 2, "CTA group is 1 or 2");
 
@@ -240,6 +260,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     // =========================== TMA producer ===========================
     if (lane == 0) {
       // Barrier that collects this stage's bytes: the leader CTA's.
+      SGL_PROF_DECL(prof_pe);
       const uint64_t pol_x = ptx::make_l2_policy(p.l2_hints & 3);
       const uint64_t pol_w = ptx::make_l2_policy((p.l2_hints >> 2) & 3);
       int s = 0;
@@ -250,11 +271,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
         const int n0 = tc.n * T::kOutCols;
         for (int kb = 0; kb < num_kb; ++kb) {
+          SGL_PROF_BEGIN(tp0);
           if (!ptx::mbar_wait(bar_empty + 8 * s, ph ^ 1u, limit, abort_flag)) {
             report_error(kErrProducerEmptyWait, kb, abort_flag);
             ok = false;
             break;
           }
+          SGL_PROF_END(prof_pe, tp0);
           const uint32_t full_local = bar_full + 8 * s;
           const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
           ptx::mbar_arrive_expect_tx_cluster(full, T::kStageBytes);
@@ -285,6 +308,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
         }
       }
+      SGL_PROF_STORE(3, prof_pe);
       if (!ok) {
         // Give loads that are still in flight time to land before the CTA exits.
         const uint64_t t0 = ptx::globaltimer_ns();
@@ -300,22 +324,30 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       int i = 0;
+      SGL_PROF_DECL(prof_te);
+      SGL_PROF_DECL(prof_fu);
+      SGL_PROF_DECL(prof_tot);
+      SGL_PROF_BEGIN(tm_all);
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters, ++i) {
         const int as = i & 1;
         const uint32_t aph = (i >> 1) & 1u;
+        SGL_PROF_BEGIN(tm0);
         if (!ptx::mbar_wait(bar_tempty + 8 * as, aph ^ 1u, limit, abort_flag)) {
           report_error(kErrMmaTmemEmptyWait, i, abort_flag);
           ok = false;
           break;
         }
+        SGL_PROF_END(prof_te, tm0);
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + as * kAccCols;
         for (int kb = 0; kb < num_kb; ++kb) {
+          SGL_PROF_BEGIN(tm1);
           if (!ptx::mbar_wait(bar_full + 8 * s, ph, limit, abort_flag)) {
             report_error(kErrMmaFullWait, kb, abort_flag);
             ok = false;
             break;
           }
+          SGL_PROF_END(prof_fu, tm1);
           ptx::tc_fence_after_sync();
           const uint32_t a_base = sA + s * T::kAStageBytes;
           const uint32_t b_base = sB + s * T::kBStageBytes;
@@ -339,6 +371,10 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
         if (ok) ptx::umma_commit<kCtaGroup>(bar_tfull + 8 * as, mask);
       }
+      SGL_PROF_END(prof_tot, tm_all);
+      SGL_PROF_STORE(0, prof_te);
+      SGL_PROF_STORE(1, prof_fu);
+      SGL_PROF_STORE(2, prof_tot);
     }
   } else {
     // =========================== epilogue ===========================
@@ -378,17 +414,25 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     };
     if constexpr (kForm == FORM_SILU_MUL) {
       if (lane == 0) {
-        for (; up_issued < kUpBufs && up_issued < total_chunks; ++up_issued) issue_up(up_issued);
+        // In-place staging refills a buffer only after its store has drained, so it runs
+        // one chunk ahead; separate staging runs kUpBufs chunks ahead.
+        const int ahead = kInPlace ? 1 : kUpBufs;
+        for (; up_issued < ahead && up_issued < total_chunks; ++up_issued) issue_up(up_issued);
       }
     }
 
     bool ok = true;
     int g = 0;  // running chunk index
+    SGL_PROF_DECL(prof_tf);
+    SGL_PROF_DECL(prof_up);
+    SGL_PROF_DECL(prof_busy);
     for (int i = 0; i < my_tiles && ok; ++i) {
       const int as = i & 1;
       const uint32_t aph = (i >> 1) & 1u;
       {
+        SGL_PROF_BEGIN(te0);
         const bool w = ptx::mbar_wait(bar_tfull + 8 * as, aph, limit, abort_flag);
+        SGL_PROF_END(prof_tf, te0);
         if (!__all_sync(0xffffffffu, w)) {
           if (lane == 0) report_error(kErrEpiTmemFullWait, i, abort_flag);
           ok = false;
@@ -396,18 +440,33 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
       }
       ptx::tc_fence_after_sync();
+      SGL_PROF_BEGIN(te_busy);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
 
 #pragma unroll 1
       for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
         int x, y;
         chunk_xy(g, x, y);
-        const uint32_t obuf = out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
         const uint32_t ubuf = up_buf0 + (g % kUpBufs) * kChunkBytes;
+        const uint32_t obuf = kInPlace ? ubuf : out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
+
+        if constexpr (kInPlace) {
+          // The other buffer is free once the previous chunk's store has read it:
+          // fetch the next `up` chunk into it while this chunk is processed.
+          if (lane == 0) {
+            ptx::bulk_wait_group_read<0>();
+            if (up_issued < total_chunks) {
+              issue_up(up_issued);
+              ++up_issued;
+            }
+          }
+        }
 
         if constexpr (kForm == FORM_SILU_MUL) {
+          SGL_PROF_BEGIN(te1);
           const bool w = ptx::mbar_wait(my_bar_up + 8 * (g % kUpBufs), (g / kUpBufs) & 1u, limit,
                                         abort_flag);
+          SGL_PROF_END(prof_up, te1);
           if (!__all_sync(0xffffffffu, w)) {
             if (lane == 0) report_error(kErrEpiUpWait, g, abort_flag);
             ok = false;
@@ -416,7 +475,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
         // The staging buffer is free once the store issued two chunks ago has
         // finished reading it.
-        if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
+        if constexpr (!kInPlace) {
+          if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
+        }
         __syncwarp();
 
 #pragma unroll
@@ -478,7 +539,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&tm_h.m[d], x, y, obuf, pol_h);
           }
           ptx::bulk_commit_group();
-          if constexpr (kForm == FORM_SILU_MUL) {
+          if constexpr (kForm == FORM_SILU_MUL && !kInPlace) {
             // This chunk's `up` buffer has been read by every lane: refill it.
             if (up_issued < total_chunks) {
               issue_up(up_issued);
@@ -487,6 +548,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
         }
       }
+      SGL_PROF_END(prof_busy, te_busy);
+    }
+    if (lane == 0 && q == 0) {
+      SGL_PROF_STORE(4, prof_tf);
+      SGL_PROF_STORE(5, prof_up);
+      SGL_PROF_STORE(6, prof_busy);
+      SGL_PROF_STORE(7, my_tiles);
     }
     if (lane == 0) {
       ptx::bulk_wait_group<0>();
