@@ -12,7 +12,6 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -102,39 +101,25 @@ struct Variant {
   int (*smem_bytes)(int);
 };
 
-template <int F, int G, int BK, bool IP>
+template <int F, int G, int BK>
 int smem_bytes_of(int stages) {
-  return sgl::KernelTraits<F, G, BK, IP>::smem_bytes(stages);
+  return sgl::KernelTraits<F, G, BK>::smem_bytes(stages);
 }
 
-template <int F, int G, int BK, bool IP = false>
+template <int F, int G, int BK>
 Variant make_variant() {
-  using T = sgl::KernelTraits<F, G, BK, IP>;
+  using T = sgl::KernelTraits<F, G, BK>;
   Variant v;
-  v.fn = sgl::swiglu_kernel<F, G, BK, IP>;
+  v.fn = sgl::swiglu_kernel<F, G, BK>;
   v.out_cols = T::kOutCols;
   v.stage_bytes = T::kStageBytes;
   v.max_stages = T::max_stages();
-  v.smem_bytes = smem_bytes_of<F, G, BK, IP>;
+  v.smem_bytes = smem_bytes_of<F, G, BK>;
   return v;
 }
 
 // Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
-bool experiment_inplace() {
-  static const bool on = [] {
-    const char* e = std::getenv("SGL_EXPERIMENT_INPLACE");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 const Variant& variant(int form, int cta_group, int block_k) {
-  static const Variant inplace[4] = {
-      make_variant<sgl::FORM_SILU_MUL, 1, 64, true>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128, true>(),
-      make_variant<sgl::FORM_SILU_MUL, 2, 64, true>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128, true>(),
-  };
-  if (form == 0 && experiment_inplace())
-    return inplace[(cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
   static const Variant table[8] = {
       make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
       make_variant<sgl::FORM_SILU_MUL, 2, 64>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128>(),
@@ -244,8 +229,8 @@ int validate_shape(int64_t M, int64_t N, int64_t K) {
 // Built-in choice when the caller passes no configuration.  Measured on B200
 // under a sustained (power-capped) load: the fused form runs best with CTA
 // pairs, BLOCK_K = 128 (3-stage ring) and bands of 16 tile rows once there are
-// at least 2048 rows; shorter problems and the silu_mul form with BLOCK_K = 64
-// (6 / 5 stages) and bands of 8.  A single 128-row tile cannot use a pair.
+// at least 2048 rows (the silu_mul form with bands of 8); shorter problems with
+// BLOCK_K = 64 (6 stages) and bands of 8.  A single 128-row tile cannot use a pair.
 void default_config(int form, int64_t M, sgl_config* c) {
   std::memset(c, 0, sizeof(*c));
   c->stages = 0;
@@ -257,6 +242,10 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;
+  } else if (M >= 2048) {
+    c->cta_group = 2;
+    c->block_k = 128;
+    c->group_m = 8;
   } else {
     c->cta_group = 2;
     c->block_k = 64;

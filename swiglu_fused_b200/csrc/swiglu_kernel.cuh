@@ -17,7 +17,8 @@
 //     t (TMEM -> registers -> silu*up in fp32 -> bf16 -> swizzled smem -> TMA
 //     store) overlaps the mainloop of tile t+1;
 //   * in the silu_mul form each epilogue warp prefetches its own `up` rows with
-//     TMA into private shared-memory buffers (coalesced and asynchronous);
+//     TMA into private shared-memory buffers (coalesced and asynchronous), overwrites
+//     them in place with the result and TMA-stores from the same buffer;
 //   * with kCtaGroup == 2 a CTA pair computes a 256-row tile with
 //     tcgen05.mma.cta_group::2: each CTA loads its own 128 rows of x and its own
 //     half of the B operand (no multicast loads anywhere);
@@ -101,8 +102,11 @@ struct KernelParams {
   unsigned long long wait_limit_ns;
 };
 
-template <int kForm, int kCtaGroup, int kBlockK, bool kInPlace = false>
+template <int kForm, int kCtaGroup, int kBlockK>
 struct KernelTraits {
+  // silu_mul form: the `up` chunk is overwritten with the result and stored from the same
+  // buffer (no separate output staging), which leaves room for one more ring stage.
+  static constexpr bool kInPlace = (kForm == FORM_SILU_MUL);
   static constexpr int kOutCols = (kForm == FORM_SILU_MUL) ? 256 : 128;
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
   static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
@@ -111,8 +115,6 @@ struct KernelTraits {
   static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
   static constexpr int kBStageBytes = kBSlabs * kBSlabBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  // kInPlace (silu_mul form only): the `up` chunk is overwritten with the result and
-  // stored from the same buffer, so no separate output staging is needed.
   static constexpr int kOutStagingBytes = kInPlace ? 0 : kEpiWarps * kOutBufs * kChunkBytes;
   static constexpr int kUpStagingBytes =
       (kForm == FORM_SILU_MUL) ? kEpiWarps * kUpBufs * kChunkBytes : 0;
@@ -185,13 +187,13 @@ __device__ __forceinline__ void report_error(unsigned code, unsigned detail, int
   *reinterpret_cast<volatile int*>(abort_flag) = 1;
 }
 
-template <int kForm, int kCtaGroup, int kBlockK, bool kInPlace = false>
+template <int kForm, int kCtaGroup, int kBlockK>
 __global__ void __launch_bounds__(kNumThreads, 1)
 swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
               const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ OutMaps tm_h,
               const KernelParams p) {
-  using T = KernelTraits<kForm, kCtaGroup, kBlockK, kInPlace>;
-  static_assert(!kInPlace || kForm == FORM_SILU_MUL, "in-place staging needs an `up` input");
+  using T = KernelTraits<kForm, kCtaGroup, kBlockK>;
+  constexpr bool kInPlace = T::kInPlace;
   static_assert(kBlockK == 64 || kBlockK == 128, "BLOCK_K is 64 or 128");
   static_assert(kCtaGroup == 1 || kCtaGroup == 2, "CTA group is 1 or 2");
 

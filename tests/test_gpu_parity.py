@@ -21,7 +21,7 @@ DEV = "cuda:0"
 
 # Every kernel variant: (cta_group, block_k).
 VARIANTS_FUSED = [(1, 64), (1, 128), (2, 64), (2, 128)]
-VARIANTS_SILU_MUL = [(1, 64), (2, 64), (2, 128)]   # (1, 128) does not fit shared memory
+VARIANTS_SILU_MUL = [(1, 64), (1, 128), (2, 64), (2, 128)]
 
 
 def bits(t):
