@@ -29,7 +29,7 @@ from ._lib import TileConfig
 DTYPE = torch.bfloat16
 
 
-def _check_matrix(t: torch.Tensor, name: str) -> None:
+def _check_matrix(t: torch.Tensor, name: str, allow_empty_rows: bool = False) -> None:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
     if t.dim() != 2:
@@ -38,8 +38,10 @@ def _check_matrix(t: torch.Tensor, name: str) -> None:
         raise TypeError(f"{name} must be torch.bfloat16, got {t.dtype}")
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor (this operator has no CPU path)")
-    if t.shape[0] < 1 or t.shape[1] < 1:
+    if t.shape[1] < 1 or (t.shape[0] < 1 and not allow_empty_rows):
         raise ValueError(f"{name} must not be empty, got shape {tuple(t.shape)}")
+    if t.shape[0] == 0:
+        return
     if t.stride(1) != 1:
         raise ValueError(f"{name} must be row-major with unit column stride, "
                          f"got strides {t.stride()}")
@@ -99,9 +101,9 @@ def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig 
     up     : [M, N] bf16  (precomputed x @ W_up)
     returns: [M, N] bf16
     """
-    _check_matrix(A, "A")
+    _check_matrix(A, "A", allow_empty_rows=True)
     _check_matrix(B_gate, "B_gate")
-    _check_matrix(up, "up")
+    _check_matrix(up, "up", allow_empty_rows=True)
     M, K = A.shape
     K2, N = B_gate.shape
     if K2 != K:
@@ -111,6 +113,8 @@ def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig 
     if K % 8 or N % 8:
         raise ValueError(f"K={K} and N={N} must be multiples of 8")
     dev = _same_device(("A", A), ("B_gate", B_gate), ("up", up))
+    if M == 0:   # no tokens: nothing to launch
+        return out if out is not None else torch.empty((0, N), dtype=DTYPE, device=dev)
     h = _prep_out(out, M, N, dev)
     if os.environ.get("SWIGLU_B200_AUTOTUNE") == "1" and config is None \
             and tile_table.lookup(_lib.FORM_SILU_MUL, M, N, K) is None:
@@ -141,7 +145,7 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     * (A @ W[:, up_col0:up_col0+n_out])`` - how a column-parallel shard addresses
     the unsplit packed weight.
     """
-    _check_matrix(A, "A")
+    _check_matrix(A, "A", allow_empty_rows=True)
     _check_matrix(W, "W")
     M, K = A.shape
     K2, N2 = W.shape
@@ -163,6 +167,8 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     if K % 8 or N % 8 or c_up % 8 or c_gate % 8:
         raise ValueError(f"K={K}, N={N} and the column offsets must be multiples of 8")
     dev = _same_device(("A", A), ("W", W))
+    if M == 0:   # no tokens: nothing to launch
+        return out if out is not None else torch.empty((0, N), dtype=DTYPE, device=dev)
     h = _prep_out(out, M, N, dev)
     if os.environ.get("SWIGLU_B200_AUTOTUNE") == "1" and config is None and not any(windowed) \
             and tile_table.lookup(_lib.FORM_FUSED_SWIGLU, M, N, K) is None:

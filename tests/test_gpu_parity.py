@@ -283,3 +283,39 @@ def test_extreme_gate_values_saturate_cleanly():
     w = torch.cat([torch.ones((K, N), dtype=torch.bfloat16) * x[0:1, :].t(), w_gate], dim=1)
     hf = matmul_fused_swiglu(xd, w.contiguous().to(DEV)).cpu()   # up = 1 through the GEMM
     assert torch.equal(bits(hf), bits(h))
+
+
+def test_empty_batch_returns_empty_without_launching():
+    n0 = _lib.kernel_launches()
+    x = torch.empty((0, 64), dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros((64, 256), dtype=torch.bfloat16, device=DEV)
+    h = matmul_fused_swiglu(x, w)
+    assert h.shape == (0, 128) and h.dtype == torch.bfloat16
+    h3 = matmul_silu_mul(x, w[:, :128].contiguous(),
+                         torch.empty((0, 128), dtype=torch.bfloat16, device=DEV))
+    assert h3.shape == (0, 128)
+    assert _lib.kernel_launches() == n0
+
+
+def test_autotune_picks_a_working_entry_and_remembers_it(monkeypatch, tmp_path):
+    from swiglu_fused_b200 import tile_table, tune_matmul_fused_swiglu, tune_matmul_silu_mul
+
+    monkeypatch.setattr(tile_table, "_table", None)
+    monkeypatch.setenv("SWIGLU_B200_TILE_TABLE", str(tmp_path / "tuned.json"))
+    M, K, N = 1024, 512, 768
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=61)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    best = tune_matmul_fused_swiglu(x, w, persist=True)
+    assert best in tile_table.legal_configs(_lib.FORM_FUSED_SWIGLU, M, N, K)
+    assert tile_table.lookup(_lib.FORM_FUSED_SWIGLU, M, N, K) == best
+    monkeypatch.setattr(tile_table, "_table", None)          # reload from the file
+    again = tile_table.lookup(_lib.FORM_FUSED_SWIGLU, M, N, K)
+    assert (again.cta_group, again.block_k, again.group_m) == \
+        (best.cta_group, best.block_k, best.group_m)
+    ref32 = orc.fused_swiglu_f32(inp["x"], inp["w"])
+    assert orc.compare(matmul_fused_swiglu(x, w).cpu(), ref32.to(torch.bfloat16), ref32).ok
+
+    x3, wg, up = (t.to(DEV) for t in silu_mul_problem(M, K, N, seed=62))
+    best3 = tune_matmul_silu_mul(x3, wg, up)
+    assert best3 in tile_table.legal_configs(_lib.FORM_SILU_MUL, M, N, K)
+    monkeypatch.setattr(tile_table, "_table", None)
