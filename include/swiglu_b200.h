@@ -42,7 +42,7 @@ typedef enum sgl_status {
 } sgl_status;
 
 /* Operator forms. */
-enum { SGL_FORM_SILU_MUL = 0, SGL_FORM_FUSED_SWIGLU = 1 };
+enum { SGL_FORM_SILU_MUL = 0, SGL_FORM_FUSED_SWIGLU = 1, SGL_FORM_MATMUL = 2 };
 
 /*
  * One entry of the tile table.  Replaces the reference's (BN, BK, NS, GSM)
@@ -98,6 +98,31 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
                                       int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx,
                                       int64_t ldw, int64_t ldh, int64_t up_col0,
                                       int64_t gate_col0, const sgl_config* cfg, void* stream);
+
+/*
+ * c[M,N] = a[M,K] @ b[K,N], bf16 in, fp32 accumulate, bf16 out: the down projection
+ * y = h @ W_down that consumes the stage's output, on the same TMA/tcgen05 pipeline.
+ * The reference stops at h; no counterpart there.
+ */
+int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream);
+
+/*
+ * Row-parallel form of the same product with the reduce-scatter fused in: this rank's
+ * partial product a @ b is ADDED (TMA reduce, atomic per element) into the buffer of the
+ * rank that owns each row block.  Destination d owns rows [d*rows_per_dst, (d+1)*rows_per_dst)
+ * of the [M, N] result and dsts[d] is the address of its [rows_per_dst, N] buffer (row pitch
+ * ldc, element type fp32 if dst_is_f32 else bf16), which may be peer-GPU memory mapped into
+ * this process.  rows_per_dst must be a multiple of 32.  The buffers must hold their initial
+ * value (normally zero) before any rank launches; the caller synchronises the ranks before
+ * and after.  Additions into fp32 are exact enough to be order independent at bf16 output
+ * precision; additions into bf16 round after every rank's contribution.
+ * No counterpart in the reference (single GPU, no down projection).
+ */
+int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
+                                   int64_t rows_per_dst, int dst_is_f32, int64_t M, int64_t N,
+                                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                   const sgl_config* cfg, void* stream);
 
 /*
  * Tile table access.  Replaces the module-level config lists and _legal /

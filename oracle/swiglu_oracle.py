@@ -63,6 +63,12 @@ def fused_swiglu_f32(x: torch.Tensor, w: torch.Tensor, up_col0: int | None = Non
     return F.silu(gate) * up
 
 
+def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """fp32 ``a @ b`` of bf16 operands: the plain torch fp32 reference of the down projection
+    (the reference project has no such product; this follows its fp32-check convention)."""
+    return a.float() @ b.float()
+
+
 def silu_mul(x, w_gate, up) -> torch.Tensor:
     """bf16 result of the silu_mul form."""
     return silu_mul_f32(x, w_gate, up).to(torch.bfloat16)

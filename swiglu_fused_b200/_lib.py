@@ -14,6 +14,7 @@ from . import build as _build
 
 FORM_SILU_MUL = 0
 FORM_FUSED_SWIGLU = 1
+FORM_MATMUL = 2
 
 QUERY_SM_COUNT = 0
 QUERY_MAX_SMEM_OPTIN = 1
@@ -25,6 +26,8 @@ EXPORTED_SYMBOLS = (
     "sgl_matmul_silu_mul",
     "sgl_matmul_fused_swiglu",
     "sgl_matmul_fused_swiglu_multi_dst",
+    "sgl_matmul_bf16",
+    "sgl_matmul_bf16_reduce_scatter",
     "sgl_config_count",
     "sgl_config_get",
     "sgl_config_default",
@@ -119,6 +122,11 @@ def load() -> C.CDLL:
         lib.sgl_matmul_fused_swiglu_multi_dst.restype = ip
         lib.sgl_matmul_fused_swiglu_multi_dst.argtypes = [vp, vp, C.POINTER(vp), ip, i64, i64,
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_bf16.restype = ip
+        lib.sgl_matmul_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_bf16_reduce_scatter.restype = ip
+        lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, i64,
+                                                       i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_config_count.restype = ip
         lib.sgl_config_count.argtypes = [ip]
         lib.sgl_config_get.restype = ip

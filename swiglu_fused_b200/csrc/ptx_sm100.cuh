@@ -165,6 +165,18 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int 
       : "memory");
 }
 
+// 2-D tiled reduction, shared memory -> global: every element of the box is ADDED to the
+// tensor in global memory (element type from the tensor map: bf16 or f32), atomically per
+// element at the L2 / memory that owns the address, which may be a peer GPU's.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y,
+                                                  uint32_t smem_src) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group"
+      " [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(map)),
+      "r"(x), "r"(y), "r"(smem_src)
+      : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

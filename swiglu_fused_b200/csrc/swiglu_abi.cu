@@ -69,14 +69,16 @@ EncodeTiledFn encode_tiled_fn() {
 // Rank-2 bf16 map over a row-major [rows, cols] tensor with row pitch `ld`
 // elements; box = box_cols (<= 64, one 128-byte swizzle row) x box_rows.
 int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld,
-             int box_rows, int box_cols, CUtensorMapL2promotion promo, const char* name) {
+             int box_rows, int box_cols, CUtensorMapL2promotion promo, const char* name,
+             bool f32 = false) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(SGL_ERR_NO_DRIVER, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * (f32 ? 4 : 2)};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+  CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -119,12 +121,15 @@ Variant make_variant() {
 }
 
 // Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
+constexpr int kNumVariants = 12;
 const Variant& variant(int form, int cta_group, int block_k) {
-  static const Variant table[8] = {
+  static const Variant table[kNumVariants] = {
       make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
       make_variant<sgl::FORM_SILU_MUL, 2, 64>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128>(),
       make_variant<sgl::FORM_FUSED, 1, 64>(),     make_variant<sgl::FORM_FUSED, 1, 128>(),
       make_variant<sgl::FORM_FUSED, 2, 64>(),     make_variant<sgl::FORM_FUSED, 2, 128>(),
+      make_variant<sgl::FORM_GEMM, 1, 64>(),      make_variant<sgl::FORM_GEMM, 1, 128>(),
+      make_variant<sgl::FORM_GEMM, 2, 64>(),      make_variant<sgl::FORM_GEMM, 2, 128>(),
   };
   return table[form * 4 + (cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
 }
@@ -160,8 +165,8 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc = 0;
   int max_smem_optin = 0;
-  int max_clusters[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per variant, 0 = not yet queried
-  int smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};      // dynamic smem attribute already raised to
+  int max_clusters[12] = {};  // per variant, 0 = not yet queried
+  int smem_set[12] = {};      // dynamic smem attribute already raised to
 };
 
 std::mutex g_dev_mutex;
@@ -238,7 +243,7 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 1;
     c->block_k = 64;
     c->group_m = 8;
-  } else if (form == SGL_FORM_FUSED_SWIGLU && M >= 2048) {
+  } else if (form != SGL_FORM_SILU_MUL && M >= 2048) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;
@@ -273,7 +278,7 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 }
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
-           const sgl::OutMaps& th, int n_dst, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -346,6 +351,8 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
   p.n_dst = n_dst;
+  p.reduce_rows = reduce_rows;
+  p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
 
   cudaLaunchConfig_t lc = {};
@@ -407,7 +414,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, int n_dsts,
@@ -449,7 +456,7 @@ static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, 
                        "h")))
       return rc;
   }
-  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, M, N, K, up_col0, gate_col0,
+  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, 0, 0, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -471,8 +478,73 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
                            stream);
 }
 
+static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_dsts,
+                       int64_t reduce_rows, int dst_is_f32, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg,
+                       void* stream) {
+  int rc;
+  if ((rc = validate_ptr(a, "a")) || (rc = validate_ptr(b, "b"))) return rc;
+  for (int d = 0; d < n_dsts; ++d) {
+    if ((rc = validate_ptr(dsts[d], "c"))) return rc;
+  }
+  if ((rc = validate_shape(M, N, K))) return rc;
+  if ((rc = validate_ld(lda, K, "lda")) || (rc = validate_ld(ldb, N, "ldb")) ||
+      (rc = validate_ld(ldc, N, "ldc")))
+    return rc;
+  if (reduce_rows < 0 || (reduce_rows > 0 && reduce_rows % 32 != 0))
+    return fail(SGL_ERR_BAD_ARGUMENT, "rows_per_dst=%lld must be a positive multiple of 32",
+                static_cast<long long>(reduce_rows));
+  if (reduce_rows > 0 && reduce_rows * n_dsts < M)
+    return fail(SGL_ERR_BAD_ARGUMENT, "%d destinations of %lld rows do not cover M=%lld", n_dsts,
+                static_cast<long long>(reduce_rows), static_cast<long long>(M));
+  sgl_config c;
+  if ((rc = resolve_config(SGL_FORM_MATMUL, cfg, M, &c))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+
+  CUtensorMap ta, tb;
+  sgl::OutMaps tc;
+  std::memset(&tc, 0, sizeof(tc));
+  if ((rc = make_map(&ta, a, M, K, lda, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "a")) ||
+      (rc = make_map(&tb, b, K, N, ldb, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")))
+    return rc;
+  const bool f32 = dst_is_f32 != 0;
+  for (int d = 0; d < n_dsts; ++d) {
+    int64_t rows = M;
+    if (reduce_rows > 0) {
+      rows = M - d * reduce_rows;
+      if (rows > reduce_rows) rows = reduce_rows;
+      if (rows < 1) rows = 1;   // a destination past the end is never addressed
+    }
+    if ((rc = make_map(&tc.m[d], dsts[d], rows, N, ldc, 32, f32 ? 32 : 64,
+                       CU_TENSOR_MAP_L2_PROMOTION_NONE, "c", f32)))
+      return rc;
+  }
+  return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
+                f32 ? 1 : 0, M, N, K, 0, 0, c, info, stream);
+}
+
+int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream) {
+  void* dst[1] = {c};
+  return matmul_impl(a, b, dst, 1, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
+}
+
+int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
+                                   int64_t rows_per_dst, int dst_is_f32, int64_t M, int64_t N,
+                                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                   const sgl_config* cfg, void* stream) {
+  if (!dsts) return fail(SGL_ERR_NULL_POINTER, "dsts is NULL");
+  if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
+    return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
+  if (rows_per_dst < 1) return fail(SGL_ERR_BAD_ARGUMENT, "rows_per_dst must be >= 1");
+  return matmul_impl(a, b, dsts, n_dsts, rows_per_dst, dst_is_f32, M, N, K, lda, ldb, ldc, cfg,
+                     stream);
+}
+
 int sgl_config_count(int form) {
-  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int idx[kTableSize];
   return form_entries(form, idx);
@@ -480,7 +552,7 @@ int sgl_config_count(int form) {
 
 int sgl_config_get(int form, int index, sgl_config* out) {
   if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
-  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int idx[kTableSize];
   const int n = form_entries(form, idx);
@@ -493,7 +565,7 @@ int sgl_config_get(int form, int index, sgl_config* out) {
 
 int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* out) {
   if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
-  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int rc = validate_shape(M, N, K);
   if (rc) return rc;
@@ -502,7 +574,7 @@ int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* ou
 
 int sgl_config_smem_bytes(int form, const sgl_config* cfg) {
   if (!cfg) return fail(SGL_ERR_NULL_POINTER, "cfg is NULL");
-  if (form != SGL_FORM_SILU_MUL && form != SGL_FORM_FUSED_SWIGLU)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   sgl_config c;
   int rc = resolve_config(form, cfg, 1 << 20, &c);

@@ -5,6 +5,10 @@
 //       replaces matmul_silu_mul_impl, swiglu/_matmul_silu_mul.cu:323-652
 //   FORM_FUSED     h = silu(x @ W[:, gate cols]) * (x @ W[:, up cols])
 //       replaces matmul_fused_swiglu_impl, swiglu/_matmul_fused_swiglu.cu:193-508
+//   FORM_GEMM      y = a @ b, no activation: the down projection that consumes h.  Its
+//       epilogue can ADD each tile into the buffer of the rank that owns those rows
+//       (TMA reduce over NVLink): GEMM + reduce-scatter in one kernel.  No counterpart in
+//       the reference, which stops at h.
 //
 // Design (not the reference's):
 //   * persistent grid, one CTA (or CTA pair) per SM, static GROUP_SIZE_M-swizzled
@@ -38,7 +42,7 @@
 
 namespace sgl {
 
-enum : int { FORM_SILU_MUL = 0, FORM_FUSED = 1 };
+enum : int { FORM_SILU_MUL = 0, FORM_FUSED = 1, FORM_GEMM = 2 };
 
 constexpr int kBlockM = 128;        // rows of x per CTA
 constexpr int kAccCols = 256;       // accumulator columns per tile (MMA N)
@@ -99,6 +103,9 @@ struct KernelParams {
   int stages;           // shared-memory ring depth actually used
   int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
   int n_dst;            // destinations in OutMaps actually used (>= 1)
+  int reduce_rows;      // FORM_GEMM: > 0 = add into the destination that owns the row block
+                        // (destination d owns rows [d * reduce_rows, (d+1) * reduce_rows))
+  int out_f32;          // FORM_GEMM: destination element type is fp32 (else bf16)
   unsigned long long wait_limit_ns;
 };
 
@@ -107,7 +114,7 @@ struct KernelTraits {
   // silu_mul form: the `up` chunk is overwritten with the result and stored from the same
   // buffer (no separate output staging), which leaves room for one more ring stage.
   static constexpr bool kInPlace = (kForm == FORM_SILU_MUL);
-  static constexpr int kOutCols = (kForm == FORM_SILU_MUL) ? 256 : 128;
+  static constexpr int kOutCols = (kForm == FORM_FUSED) ? 128 : 256;
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
   static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
   static constexpr int kBSlabs = kBColsPerCta / 64;           // 64-column slabs this CTA loads
@@ -296,7 +303,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             // Slab index inside the 256 accumulator columns of the cluster tile.
             const int g = static_cast<int>(rank) * T::kBSlabs + j;
             int col;
-            if constexpr (kForm == FORM_SILU_MUL) {
+            if constexpr (kForm != FORM_FUSED) {
               col = p.b_col0 + n0 + g * 64;
             } else {
               col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
@@ -424,7 +431,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     }
 
     bool ok = true;
-    int g = 0;  // running chunk index
+    int g = 0;            // running chunk index
+    int gemm_stores = 0;  // FORM_GEMM: staging buffers filled so far
     SGL_PROF_DECL(prof_tf);
     SGL_PROF_DECL(prof_up);
     SGL_PROF_DECL(prof_busy);
@@ -445,6 +453,76 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_BEGIN(te_busy);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
 
+      if constexpr (kForm == FORM_GEMM) {
+        // Plain GEMM epilogue: fp32 accumulator -> bf16 (or fp32) -> staging -> TMA store, or
+        // TMA reduce-add into the buffer of the rank that owns this row block.
+        int x0, y;
+        chunk_xy(g, x0, y);
+        g += T::kChunksPerTile;
+        const bool f32 = p.out_f32 != 0;
+        int dst = 0, yy = y;
+        if (p.reduce_rows > 0) {
+          dst = y / p.reduce_rows;
+          yy = y - dst * p.reduce_rows;
+        }
+        uint32_t nbuf = out_buf0;
+#pragma unroll 1
+        for (int u = 0; u < kAccCols / 32; ++u) {
+          const bool first = f32 || (u & 1) == 0;   // first 32-column unit of a staging buffer
+          const bool last = f32 || (u & 1) == 1;    // buffer complete after this unit
+          if (first) {
+            if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
+            __syncwarp();
+            nbuf = out_buf0 + (gemm_stores & (kOutBufs - 1)) * kChunkBytes;
+          }
+          float acc[32];
+          ptx::tmem_ld_32x32b_x32(t_row + u * 32, acc);
+          ptx::tmem_ld_wait();
+          if (u == kAccCols / 32 - 1) {
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+          }
+          if (f32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t addr = nbuf + row_off + ((static_cast<uint32_t>(j) ^ row_sw) << 4);
+              asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "f"(acc[4 * j]),
+                           "f"(acc[4 * j + 1]), "f"(acc[4 * j + 2]), "f"(acc[4 * j + 3])
+                           : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t addr =
+                  nbuf + row_off + ((static_cast<uint32_t>((u & 1) * 4 + j) ^ row_sw) << 4);
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr),
+                           "r"(pack_bf16x2(acc[8 * j], acc[8 * j + 1])),
+                           "r"(pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3])),
+                           "r"(pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5])),
+                           "r"(pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]))
+                           : "memory");
+            }
+          }
+          if (last) {
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int x = x0 + (f32 ? u * 32 : (u >> 1) * 64);
+              if (x < p.N && y < p.M) {
+                if (p.reduce_rows > 0) {
+                  ptx::tma_reduce_add_2d(&tm_h.m[dst], x, yy, nbuf);
+                } else {
+                  for (int d = 0; d < p.n_dst; ++d)
+                    ptx::tma_store_2d(&tm_h.m[d], x, y, nbuf, pol_h);
+                }
+              }
+              ptx::bulk_commit_group();
+            }
+            ++gemm_stores;
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
         int x, y;
@@ -550,6 +628,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
         }
       }
+      }  // form
       SGL_PROF_END(prof_busy, te_busy);
     }
     if (lane == 0 && q == 0) {

@@ -219,6 +219,63 @@ def matmul_fused_swiglu_multi_dst(A, W, dst_ptrs, ldh: int, *, up_col0: int, gat
     _lib.check(rc)
 
 
+def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None):
+    """``A @ B`` (bf16 in, fp32 accumulate, bf16 out) on the same TMA/tcgen05 pipeline:
+    the down projection ``y = h @ W_down`` that consumes the stage's output.
+
+    A : [M, K] bf16, B : [K, N] bf16 (row-major), returns [M, N] bf16.
+    """
+    _check_matrix(A, "A", allow_empty_rows=True)
+    _check_matrix(B, "B")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"K mismatch: A.K={K} vs B.K={K2}")
+    if K % 8 or N % 8:
+        raise ValueError(f"K={K} and N={N} must be multiples of 8")
+    dev = _same_device(("A", A), ("B", B))
+    if M == 0:
+        return out if out is not None else torch.empty((0, N), dtype=DTYPE, device=dev)
+    c = _prep_out(out, M, N, dev)
+    cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_matmul_bf16(
+            A.data_ptr(), B.data_ptr(), c.data_ptr(), M, N, K, _ld(A), _ld(B), _ld(c),
+            C.byref(cfg_c) if cfg_c is not None else None, _stream_handle(stream, dev))
+    _lib.check(rc)
+    return c
+
+
+def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, dst_f32: bool,
+                               stream=None, config: TileConfig | None = None):
+    """Adds ``A @ B`` into the row-block owners' buffers (GEMM + reduce-scatter in one kernel).
+
+    ``dst_ptrs[d]`` is the device address of the ``[rows_per_dst, N]`` buffer (fp32 if
+    ``dst_f32`` else bf16, row pitch ``ldc`` elements) of the rank that owns rows
+    ``[d * rows_per_dst, (d+1) * rows_per_dst)``; peers' buffers are addressed through their
+    mapping in this process.  The caller zeroes the buffers and synchronises the ranks.
+    """
+    _check_matrix(A, "A")
+    _check_matrix(B, "B")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"K mismatch: A.K={K} vs B.K={K2}")
+    if not 1 <= len(dst_ptrs) <= 8:
+        raise ValueError(f"need 1..8 destinations, got {len(dst_ptrs)}")
+    dev = _same_device(("A", A), ("B", B))
+    cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_matmul_bf16_reduce_scatter(
+            A.data_ptr(), B.data_ptr(), arr, len(dst_ptrs), int(rows_per_dst), int(bool(dst_f32)),
+            M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+
+
 def tune_matmul_silu_mul(A, B_gate, up, *, verbose=False, persist=False) -> TileConfig:
     """Sweep the tile table for this problem (reference: ``_tune``,
     ``swiglu/matmul_silu_mul.py:114-139``) and remember the winner."""

@@ -124,6 +124,53 @@ def fused_swiglu_n_sharded_fused_gather(x: torch.Tensor, w: torch.Tensor, out: S
     return out.tensor
 
 
+class RowShardedOutput:
+    """Per-rank ``[rows_per_rank, N]`` accumulation buffer (fp32 by default) in symmetric
+    memory: rank r's buffer receives every rank's partial product for the rows r owns.
+    Collective constructor, like ``SymmetricOutput``."""
+
+    def __init__(self, M: int, N: int, device, group=None, dtype=torch.float32):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("accumulation buffer must be fp32 or bf16")
+        self.group = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(self.group)
+        self.M, self.N = M, N
+        # equal row blocks, a multiple of the pair-tile height, the last one possibly ragged
+        self.rows_per_rank = -(-(-(-M // world)) // ROW_ALIGN) * ROW_ALIGN
+        self.tensor = symm_mem.empty((self.rows_per_rank, N), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.my_rows = max(0, min(self.rows_per_rank, M - self.rank * self.rows_per_rank))
+
+    def barrier(self) -> None:
+        self.handle.barrier(channel=0)
+
+
+def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor,
+                           out: RowShardedOutput, *, stream=None, config=None) -> torch.Tensor:
+    """``y = h @ W_down`` for a column-sharded ``h``, reduce-scatter fused into the GEMM.
+
+    Rank r holds ``h_local = h[:, cols_r]`` (exactly what the column-parallel gate/up stage
+    leaves on it - no all-gather of ``h``) and ``w_down_local = W_down[cols_r, :]``.  Each
+    rank's kernel adds its partial product tile by tile into the buffer of the rank that
+    owns those rows (TMA reduce over NVLink), so every rank ends with the complete rows it
+    owns: ``out.tensor[:out.my_rows]``.  Barriers: zeroing -> launch -> completion.
+    """
+    from .ops import matmul_bf16_reduce_scatter
+
+    out.tensor.zero_()
+    out.barrier()                      # every buffer is zero before anybody adds into it
+    matmul_bf16_reduce_scatter(h_local, w_down_local, out.ptrs, out.rows_per_rank,
+                               out.tensor.stride(0), dst_f32=out.tensor.dtype == torch.float32,
+                               stream=stream, config=config)
+    out.barrier()                      # every rank's additions have landed
+    return out.tensor[:out.my_rows]
+
+
 def fused_swiglu_m_sharded(x_local: torch.Tensor, w: torch.Tensor, *, out=None, stream=None,
                            config=None, op=None) -> torch.Tensor:
     """This rank's rows of ``h``: ``silu(x_local @ W_gate) * (x_local @ W_up)``.

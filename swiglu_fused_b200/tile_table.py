@@ -18,7 +18,8 @@ from . import _lib
 from ._lib import TileConfig
 
 TABLE_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tile_table.json")
-FORM_NAMES = {_lib.FORM_SILU_MUL: "silu_mul", _lib.FORM_FUSED_SWIGLU: "fused_swiglu"}
+FORM_NAMES = {_lib.FORM_SILU_MUL: "silu_mul", _lib.FORM_FUSED_SWIGLU: "fused_swiglu",
+              _lib.FORM_MATMUL: "matmul"}
 
 _lock = threading.Lock()
 _table: dict[str, TileConfig] | None = None

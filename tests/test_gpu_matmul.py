@@ -1,0 +1,92 @@
+"""The plain bf16 GEMM form (down projection) and its fused reduce-scatter, against the torch
+fp32 reference (``swiglu_oracle.matmul_f32``).  Same tolerance as the activation kernels:
+>= 99.9 % of elements within 1 bf16 ulp, floored relative error <= 1e-2."""
+import pytest
+import torch
+
+import swiglu_oracle as orc
+from swiglu_fused_b200 import TileConfig, _lib, matmul_bf16
+from swiglu_fused_b200.ops import matmul_bf16_reduce_scatter
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+VARIANTS = [(1, 64), (1, 128), (2, 64), (2, 128)]
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
+def problem(M, K, N, seed):
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    b = (torch.randn((K, N), generator=g) * K ** -0.5).to(torch.bfloat16)
+    return a, b
+
+
+@pytest.mark.parametrize("M,K,N", [(128, 64, 256), (256, 256, 256), (512, 1024, 2048),
+                                    (200, 136, 264), (1024, 512, 1024), (1, 8, 8),
+                                    (300, 1032, 520), (64, 4096, 512)])
+def test_matmul_matches_fp32_reference(M, K, N):
+    a, b = problem(M, K, N, seed=M + K + N)
+    ref32 = orc.matmul_f32(a, b)
+    ref = ref32.to(torch.bfloat16)
+    ad, bd = a.to(DEV), b.to(DEV)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    for cg, bk in VARIANTS:
+        out = big[1:M + 1, 8:8 + N]
+        matmul_bf16(ad, bd, out=out, config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(out.cpu(), ref, ref32)
+        assert rep.ok, f"{(M, K, N)} cta_group={cg} block_k={bk}: {rep}"
+        guard = big.clone()
+        guard[1:M + 1, 8:8 + N] = float("nan")
+        assert torch.isnan(guard).all(), "wrote outside the output"
+        big.fill_(float("nan"))
+
+
+def test_matmul_equals_cublas_on_exact_data():
+    # small integers: every product and partial sum is exact, so any correct GEMM agrees bit for bit
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(-3, 4, (512, 256), generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randint(-2, 3, (256, 768), generator=g).to(torch.bfloat16).to(DEV)
+    assert torch.equal(matmul_bf16(a, b).view(torch.int16), (a @ b).view(torch.int16))
+
+
+@pytest.mark.parametrize("dst_f32", [True, False])
+def test_reduce_scatter_epilogue_on_one_gpu(dst_f32):
+    """Two row-block owners, both buffers on this GPU; two launches (two 'ranks') add their
+    partial products of a K-split problem.  The sum must equal the unsplit product."""
+    M, K, N = 1024, 512, 768
+    a, b = problem(M, K, N, seed=9)
+    ad, bd = a.to(DEV), b.to(DEV)
+    rows = 512
+    dt = torch.float32 if dst_f32 else torch.bfloat16
+    bufs = [torch.zeros((rows, N), dtype=dt, device=DEV) for _ in range(2)]
+    ptrs = [t.data_ptr() for t in bufs]
+    for r in range(2):                                   # rank r holds K-slice r
+        ks = slice(r * K // 2, (r + 1) * K // 2)
+        matmul_bf16_reduce_scatter(ad[:, ks], bd[ks].contiguous(), ptrs, rows, N, dst_f32=dst_f32)
+    torch.cuda.synchronize()
+    got = torch.cat(bufs, dim=0)
+    ref32 = orc.matmul_f32(a, b)
+    if dst_f32:
+        assert torch.allclose(got.cpu(), ref32, rtol=1e-5, atol=1e-4)
+        rep = orc.compare(got.to(torch.bfloat16).cpu(), ref32.to(torch.bfloat16), ref32)
+        assert rep.ok, str(rep)
+    else:
+        # bf16 accumulation rounds after each contribution: within 2 ulp of the fp32 result
+        rep = orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32)
+        assert rep.max_floored_rel <= 1e-2 and rep.frac_within_1ulp >= 0.95, str(rep)
+
+
+def test_reduce_scatter_rejects_bad_row_blocks():
+    a = torch.zeros((256, 64), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
+    buf = torch.zeros((256, 64), dtype=torch.float32, device=DEV)
+    with pytest.raises(ValueError):
+        matmul_bf16_reduce_scatter(a, b, [buf.data_ptr()], 100, 64, dst_f32=True)   # not % 32
+    with pytest.raises(ValueError):
+        matmul_bf16_reduce_scatter(a, b, [buf.data_ptr()], 128, 64, dst_f32=True)   # does not cover M

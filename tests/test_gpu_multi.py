@@ -54,6 +54,23 @@ def _worker(rank, world, port, M, K, N, results):
         torch.cuda.synchronize()
         ok_f = ok_f and same(got, full_ref)
     ok_g = ok_g and ok_f
+
+    # down projection with the reduce-scatter fused into the GEMM: y = h @ W_down from the
+    # column-sharded h, every rank ends with the complete rows it owns
+    Kd = 384
+    gw = torch.Generator().manual_seed(23)
+    w_down = (torch.randn((N, Kd), generator=gw) * N ** -0.5).to(torch.bfloat16).to(dev)
+    y_ref = full_ref.float() @ w_down.float()
+    rso = sharding.RowShardedOutput(M, Kd, dev)
+    for _ in range(2):
+        y_rows = sharding.down_proj_row_parallel(
+            full_ref[:, cols.begin:cols.end].contiguous(),
+            w_down[cols.begin:cols.end].contiguous(), rso)
+        torch.cuda.synchronize()
+        r0 = rank * rso.rows_per_rank
+        want = y_ref[r0:r0 + rso.my_rows]
+        ok_g = ok_g and y_rows.shape == want.shape and bool(
+            torch.allclose(y_rows, want, rtol=1e-4, atol=2e-3))
     torch.cuda.synchronize()
     _lib.device_status()
     flags = torch.tensor([int(ok_m), int(ok_n), int(ok_g)], dtype=torch.int64, device=dev)
