@@ -85,6 +85,18 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
                             int64_t gate_col0, const sgl_config* cfg, void* stream);
 
 /*
+ * Same computation with the weight in checkpoint (nn.Linear) layout: w_nk[2N, K], row f holds
+ * the K weights of output feature f; rows [up_row0, up_row0+N) are the up features and rows
+ * [gate_row0, gate_row0+N) the gate features (N and 0.. for the usual [up; gate] stack), ldw
+ * the row pitch (>= K).  No transpose or repack: the kernel reads the rows as a K-major B
+ * operand.  Counterpart of the reference's pack/unpack helpers
+ * (swiglu/triton/impls.py:1898-1917), which convert between the two layouts by copying.
+ */
+int sgl_matmul_fused_swiglu_nk(const void* x, const void* w_nk, void* h, int64_t M, int64_t N,
+                               int64_t K, int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_row0,
+                               int64_t gate_row0, const sgl_config* cfg, void* stream);
+
+/*
  * Same computation, but every output tile is written to n_dsts (1..8) buffers:
  * h_dsts[i] is the address of element (0, 0) of this launch's [M, N] block inside
  * destination i (all with row pitch ldh).  Destinations may be peer-GPU memory

@@ -25,6 +25,7 @@ QUERY_KERNEL_LAUNCHES = 3
 EXPORTED_SYMBOLS = (
     "sgl_matmul_silu_mul",
     "sgl_matmul_fused_swiglu",
+    "sgl_matmul_fused_swiglu_nk",
     "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_matmul_bf16",
     "sgl_matmul_bf16_reduce_scatter",
@@ -119,6 +120,9 @@ def load() -> C.CDLL:
         lib.sgl_matmul_fused_swiglu.restype = ip
         lib.sgl_matmul_fused_swiglu.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
                                                 i64, cfgp, vp]
+        lib.sgl_matmul_fused_swiglu_nk.restype = ip
+        lib.sgl_matmul_fused_swiglu_nk.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
+                                                   i64, cfgp, vp]
         lib.sgl_matmul_fused_swiglu_multi_dst.restype = ip
         lib.sgl_matmul_fused_swiglu_multi_dst.argtypes = [vp, vp, C.POINTER(vp), ip, i64, i64,
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]

@@ -278,7 +278,8 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 }
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
-           const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int b_kmajor,
+           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -351,6 +352,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
   p.n_dst = n_dst;
+  p.b_kmajor = b_kmajor;
   p.reduce_rows = reduce_rows;
   p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
@@ -414,11 +416,11 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
-static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, int n_dsts,
-                            int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
+                            int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
                             int64_t ldh, int64_t up_col0, int64_t gate_col0,
                             const sgl_config* cfg, void* stream) {
   int rc;
@@ -434,9 +436,11 @@ static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, 
     return fail(SGL_ERR_MISALIGNED,
                 "up_col0=%lld and gate_col0=%lld must be multiples of 8 columns (16 bytes)",
                 static_cast<long long>(up_col0), static_cast<long long>(gate_col0));
-  const int64_t w_cols = (up_col0 > gate_col0 ? up_col0 : gate_col0) + N;
-  if ((rc = validate_ld(ldx, K, "ldx")) || (rc = validate_ld(ldw, w_cols, "ldw")) ||
-      (rc = validate_ld(ldh, N, "ldh")))
+  // [k, n] storage: ldw is the pitch of a row of all columns; [n, k] storage: of one
+  // feature's K weights, and the tensor has (max offset + N) rows.
+  const int64_t w_span = (up_col0 > gate_col0 ? up_col0 : gate_col0) + N;
+  if ((rc = validate_ld(ldx, K, "ldx")) ||
+      (rc = validate_ld(ldw, w_is_nk ? K : w_span, "ldw")) || (rc = validate_ld(ldh, N, "ldh")))
     return rc;
   sgl_config c;
   if ((rc = resolve_config(SGL_FORM_FUSED_SWIGLU, cfg, M, &c))) return rc;
@@ -448,15 +452,17 @@ static int fused_swiglu_impl(const void* x, const void* w, void* const* h_dsts, 
   std::memset(&th, 0, sizeof(th));
   if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "x")) ||
-      (rc = make_map(&tw, w, K, ldw, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     "w")))
+      (rc = w_is_nk ? make_map(&tw, w, w_span, K, ldw, 128, 64,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "w")
+                    : make_map(&tw, w, K, ldw, ldw, c.block_k, 64,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "w")))
     return rc;
   for (int d = 0; d < n_dsts; ++d) {
     if ((rc = make_map(&th.m[d], h_dsts[d], M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                        "h")))
       return rc;
   }
-  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, 0, 0, M, N, K, up_col0, gate_col0,
+  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -464,7 +470,16 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
                             int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
                             int64_t gate_col0, const sgl_config* cfg, void* stream) {
   void* dst[1] = {h};
-  return fused_swiglu_impl(x, w, dst, 1, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg, stream);
+  return fused_swiglu_impl(x, w, 0, dst, 1, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg,
+                           stream);
+}
+
+int sgl_matmul_fused_swiglu_nk(const void* x, const void* w_nk, void* h, int64_t M, int64_t N,
+                               int64_t K, int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_row0,
+                               int64_t gate_row0, const sgl_config* cfg, void* stream) {
+  void* dst[1] = {h};
+  return fused_swiglu_impl(x, w_nk, 1, dst, 1, M, N, K, ldx, ldw, ldh, up_row0, gate_row0, cfg,
+                           stream);
 }
 
 int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const* h_dsts,
@@ -474,8 +489,8 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
   if (!h_dsts) return fail(SGL_ERR_NULL_POINTER, "h_dsts is NULL");
   if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
     return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
-  return fused_swiglu_impl(x, w, h_dsts, n_dsts, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg,
-                           stream);
+  return fused_swiglu_impl(x, w, 0, h_dsts, n_dsts, M, N, K, ldx, ldw, ldh, up_col0, gate_col0,
+                           cfg, stream);
 }
 
 static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_dsts,
@@ -522,7 +537,7 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
       return rc;
   }
   return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
-                f32 ? 1 : 0, M, N, K, 0, 0, c, info, stream);
+                f32 ? 1 : 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,

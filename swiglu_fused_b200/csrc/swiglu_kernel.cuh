@@ -103,6 +103,8 @@ struct KernelParams {
   int stages;           // shared-memory ring depth actually used
   int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
   int n_dst;            // destinations in OutMaps actually used (>= 1)
+  int b_kmajor;         // weight operand is stored [n, k] (nn.Linear layout) instead of [k, n];
+                        // b_col0 / b_col1 are then row offsets of that tensor
   int reduce_rows;      // FORM_GEMM: > 0 = add into the destination that owns the row block
                         // (destination d owns rows [d * reduce_rows, (d+1) * reduce_rows))
   int out_f32;          // FORM_GEMM: destination element type is fp32 (else bf16)
@@ -298,18 +300,40 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                                              full, pol_x);
           }
           const uint32_t b_dst = sB + s * T::kBStageBytes;
+          if (p.b_kmajor) {
+            // Weight stored [n, k]: boxes of 128 n-rows x 64 k, laid out [k box][rows][128 B]
+            // so that one 64-k slice of all this CTA's B rows is contiguous.
+            constexpr int kRowBoxes = T::kBColsPerCta / 128;
 #pragma unroll
-          for (int j = 0; j < T::kBSlabs; ++j) {
-            // Slab index inside the 256 accumulator columns of the cluster tile.
-            const int g = static_cast<int>(rank) * T::kBSlabs + j;
-            int col;
-            if constexpr (kForm != FORM_FUSED) {
-              col = p.b_col0 + n0 + g * 64;
-            } else {
-              col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
+            for (int j = 0; j < kBlockK / 64; ++j) {
+#pragma unroll
+              for (int rb = 0; rb < kRowBoxes; ++rb) {
+                const int wdx = static_cast<int>(rank) * kRowBoxes + rb;  // 128-column window
+                int row;
+                if constexpr (kForm != FORM_FUSED) {
+                  row = p.b_col0 + n0 + wdx * 128;
+                } else {
+                  row = (wdx == 0) ? (p.b_col0 + n0) : (p.b_col1 + n0);
+                }
+                ptx::tma_load_2d<kCtaGroup == 2>(
+                    b_dst + j * (T::kBColsPerCta * 128) + rb * (128 * 128), &tm_w, k0 + j * 64,
+                    row, full, pol_w);
+              }
             }
-            ptx::tma_load_2d<kCtaGroup == 2>(b_dst + j * T::kBSlabBytes, &tm_w, col, k0, full,
-                                             pol_w);
+          } else {
+#pragma unroll
+            for (int j = 0; j < T::kBSlabs; ++j) {
+              // Slab index inside the 256 accumulator columns of the cluster tile.
+              const int g = static_cast<int>(rank) * T::kBSlabs + j;
+              int col;
+              if constexpr (kForm != FORM_FUSED) {
+                col = p.b_col0 + n0 + g * 64;
+              } else {
+                col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
+              }
+              ptx::tma_load_2d<kCtaGroup == 2>(b_dst + j * T::kBSlabBytes, &tm_w, col, k0, full,
+                                               pol_w);
+            }
           }
           if (++s == stages) {
             s = 0;
@@ -327,7 +351,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (rank == 0 && lane == 0) {
-      constexpr uint32_t idesc = ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols, true);
+      const uint32_t idesc =
+          ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols, /*b_mn_major=*/p.b_kmajor == 0);
+      const bool b_kmajor = p.b_kmajor != 0;
       constexpr uint16_t mask = (kCtaGroup == 2) ? 0x3 : 0x1;
       int s = 0;
       uint32_t ph = 0;
@@ -366,9 +392,12 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             // 16 k = 32 bytes inside the 128-byte swizzle row.
             const uint64_t a_desc = ptx::smem_desc_sw128(
                 a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
-            // weight tile: N-major slabs [kBlockK rows][64 cols]; 16 k = 16 rows.
+            // weight tile, [k, n] storage: N-major slabs [kBlockK rows][64 cols], 16 k = 16
+            // rows; [n, k] storage: K-major like x, rows = n, 16 k = 32 bytes.
             const uint64_t b_desc =
-                ptx::smem_desc_sw128(b_base + kk * 16 * 128, T::kBSlabBytes, 1024);
+                b_kmajor ? ptx::smem_desc_sw128(b_base + (kk >> 2) * (T::kBColsPerCta * 128) +
+                                                    (kk & 3) * 32, 16, 1024)
+                         : ptx::smem_desc_sw128(b_base + kk * 16 * 128, T::kBSlabBytes, 1024);
             ptx::umma_bf16<kCtaGroup>(d_tmem, a_desc, b_desc, idesc,
                                       (kb > 0 || kk > 0) ? 1u : 0u);
           }

@@ -133,7 +133,7 @@ def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig 
 
 def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | None = None,
                         up_col0: int | None = None, gate_col0: int | None = None,
-                        n_out: int | None = None):
+                        n_out: int | None = None, w_layout: str = "kn"):
     """Single-kernel SwiGLU.  C = silu(gate) * up  where [up|gate] = A @ W.
 
     A : [M, K]  bf16
@@ -144,11 +144,16 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     windows of a wider W instead: ``h = silu(A @ W[:, gate_col0:gate_col0+n_out])
     * (A @ W[:, up_col0:up_col0+n_out])`` - how a column-parallel shard addresses
     the unsplit packed weight.
+
+    ``w_layout="nk"``: W is the checkpoint (``nn.Linear``) layout ``[2N, K]`` = ``[W_up^T ;
+    W_gate^T]`` and is consumed as is (no transpose); the window arguments then count rows.
     """
+    if w_layout not in ("kn", "nk"):
+        raise ValueError(f"w_layout must be 'kn' or 'nk', got {w_layout!r}")
     _check_matrix(A, "A", allow_empty_rows=True)
     _check_matrix(W, "W")
     M, K = A.shape
-    K2, N2 = W.shape
+    K2, N2 = W.shape if w_layout == "kn" else (W.shape[1], W.shape[0])
     if K != K2:
         raise ValueError(f"K mismatch: A.K={K} vs W.K={K2}")
     windowed = (up_col0 is not None, gate_col0 is not None, n_out is not None)
@@ -176,9 +181,10 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     cfg = _pick_config(_lib.FORM_FUSED_SWIGLU, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
     lib = _lib.load()
-    ldw = _ld(W) if W.shape[0] > 1 else max(_ld(W), (N2 + 7) // 8 * 8)
+    ldw = _ld(W) if W.shape[0] > 1 else max(_ld(W), (W.shape[1] + 7) // 8 * 8)
+    entry = lib.sgl_matmul_fused_swiglu if w_layout == "kn" else lib.sgl_matmul_fused_swiglu_nk
     with torch.cuda.device(dev):
-        rc = lib.sgl_matmul_fused_swiglu(
+        rc = entry(
             A.data_ptr(), W.data_ptr(), h.data_ptr(), M, N, K, _ld(A), ldw, _ld(h),
             c_up, c_gate, C.byref(cfg_c) if cfg_c is not None else None,
             _stream_handle(stream, dev))

