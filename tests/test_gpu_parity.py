@@ -319,3 +319,56 @@ def test_autotune_picks_a_working_entry_and_remembers_it(monkeypatch, tmp_path):
     best3 = tune_matmul_silu_mul(x3, wg, up)
     assert best3 in tile_table.legal_configs(_lib.FORM_SILU_MUL, M, N, K)
     monkeypatch.setattr(tile_table, "_table", None)
+
+
+def test_launch_is_capturable_in_a_cuda_graph():
+    M, K, N = 512, 256, 512
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=71)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    ref = matmul_fused_swiglu(x, w)
+    out = torch.zeros_like(ref)
+    matmul_fused_swiglu(x, w, out=out)            # first call sets function attributes
+    out.zero_()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            matmul_fused_swiglu(x, w, out=out)
+    torch.cuda.synchronize()
+    assert not torch.equal(bits(out), bits(ref))  # capture does not execute
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(bits(out), bits(ref))
+
+
+def test_concurrent_launches_from_two_host_threads():
+    import threading
+
+    M, K, N = 1024, 512, 512
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=81)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    ref = matmul_fused_swiglu(x, w)
+    outs = [torch.zeros_like(ref) for _ in range(2)]
+    errors = []
+
+    def worker(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(20):
+                    matmul_fused_swiglu(x, w, out=outs[i])
+            st.synchronize()
+        except Exception as e:  # surfaced below
+            errors.append(e)
+
+    torch.cuda.synchronize()
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for o in outs:
+        assert torch.equal(bits(o), bits(ref))
