@@ -42,7 +42,12 @@ typedef enum sgl_status {
 } sgl_status;
 
 /* Operator forms. */
-enum { SGL_FORM_SILU_MUL = 0, SGL_FORM_FUSED_SWIGLU = 1, SGL_FORM_MATMUL = 2 };
+enum {
+  SGL_FORM_SILU_MUL = 0,
+  SGL_FORM_FUSED_SWIGLU = 1,
+  SGL_FORM_MATMUL = 2,
+  SGL_FORM_FUSED_SWIGLU_SAVE = 3
+};
 
 /*
  * One entry of the tile table.  Replaces the reference's (BN, BK, NS, GSM)
@@ -95,6 +100,28 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
 int sgl_matmul_fused_swiglu_nk(const void* x, const void* w_nk, void* h, int64_t M, int64_t N,
                                int64_t K, int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_row0,
                                int64_t gate_row0, const sgl_config* cfg, void* stream);
+
+/*
+ * Training forward: h as above, and from the same epilogue the two factors the backward
+ * pass needs, factors[M, 2N] = [ silu(gate) | up * silu'(gate) ] (bf16, row pitch ldf).
+ * Counterpart of the reference's Triton side-store forward
+ * (_fused_swiglu_wide_packed_save_factors_kernel, swiglu/triton/impls.py:384-468); the
+ * factors are stored as two plain [M, N] halves, not chunk-interleaved.
+ */
+int sgl_matmul_fused_swiglu_save_factors(const void* x, const void* w, void* h, void* factors,
+                                         int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                         int64_t ldw, int64_t ldh, int64_t ldf, int64_t up_col0,
+                                         int64_t gate_col0, const sgl_config* cfg, void* stream);
+
+/*
+ * Backward elementwise step: grad_preact[M, 2N] = [ dy * factors[:, :N] | dy * factors[:, N:] ]
+ * = [ d/d(up) | d/d(gate) ], in the column order of the packed weight, so that
+ * grad_x = grad_preact @ W^T and grad_W = x^T @ grad_preact follow directly.  grad_preact may
+ * alias factors (in place).  HBM bound: 10 * M * N bytes.  Counterpart of
+ * _swiglu_grad_preact_normal_kernel (swiglu/triton/impls.py:3947-3993).
+ */
+int sgl_swiglu_grad_preact(const void* dy, const void* factors, void* grad_preact, int64_t M,
+                           int64_t N, int64_t lddy, int64_t ldf, int64_t ldo, void* stream);
 
 /*
  * Same computation, but every output tile is written to n_dsts (1..8) buffers:

@@ -69,6 +69,27 @@ def matmul_f32(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     return a.float() @ b.float()
 
 
+def swiglu_factors_f32(x: torch.Tensor, w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``(h, factors)`` of the side-store forward, with the reference's expressions
+    (``swiglu/triton/impls.py:455-468``): sig = sigmoid(gate); silu = gate * sig;
+    silu_prime = sig + silu * (1 - sig); factors = [silu | left * silu_prime]; h = left * silu."""
+    n = w.shape[1] // 2
+    gu = x.float() @ w.float()
+    left, gate = gu[:, :n], gu[:, n:]
+    sig = torch.sigmoid(gate)
+    silu = gate * sig
+    silu_prime = sig + silu * (1.0 - sig)
+    return left * silu, torch.cat([silu, left * silu_prime], dim=1)
+
+
+def grad_preact_f32(dy: torch.Tensor, factors: torch.Tensor) -> torch.Tensor:
+    """fp32 ``[dy * silu | dy * left * silu_prime]`` from the saved (bf16) factors."""
+    n = dy.shape[1]
+    f = factors.float()
+    d = dy.float()
+    return torch.cat([d * f[:, :n], d * f[:, n:]], dim=1)
+
+
 def silu_mul(x, w_gate, up) -> torch.Tensor:
     """bf16 result of the silu_mul form."""
     return silu_mul_f32(x, w_gate, up).to(torch.bfloat16)

@@ -15,6 +15,7 @@ from . import build as _build
 FORM_SILU_MUL = 0
 FORM_FUSED_SWIGLU = 1
 FORM_MATMUL = 2
+FORM_FUSED_SWIGLU_SAVE = 3
 
 QUERY_SM_COUNT = 0
 QUERY_MAX_SMEM_OPTIN = 1
@@ -26,6 +27,8 @@ EXPORTED_SYMBOLS = (
     "sgl_matmul_silu_mul",
     "sgl_matmul_fused_swiglu",
     "sgl_matmul_fused_swiglu_nk",
+    "sgl_matmul_fused_swiglu_save_factors",
+    "sgl_swiglu_grad_preact",
     "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_matmul_bf16",
     "sgl_matmul_bf16_reduce_scatter",
@@ -123,6 +126,11 @@ def load() -> C.CDLL:
         lib.sgl_matmul_fused_swiglu_nk.restype = ip
         lib.sgl_matmul_fused_swiglu_nk.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, i64,
                                                    i64, cfgp, vp]
+        lib.sgl_matmul_fused_swiglu_save_factors.restype = ip
+        lib.sgl_matmul_fused_swiglu_save_factors.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64,
+                                                             i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_swiglu_grad_preact.restype = ip
+        lib.sgl_swiglu_grad_preact.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, vp]
         lib.sgl_matmul_fused_swiglu_multi_dst.restype = ip
         lib.sgl_matmul_fused_swiglu_multi_dst.argtypes = [vp, vp, C.POINTER(vp), ip, i64, i64,
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]

@@ -1,0 +1,34 @@
+"""``torch.autograd`` wiring of the stage for training.
+
+Forward: the side-store kernel (h + factors in one launch).  Backward: the elementwise
+kernel of this library for ``grad_preact``, then two plain GEMMs
+(``grad_x = grad_preact @ W^T``, ``grad_W = x^T @ grad_preact``) through ``torch.matmul``
+(cuBLAS), which are library GEMMs and not part of the accelerated path.  The reference
+keeps its autograd Functions in its Triton module (``swiglu/triton/impls.py:2913-3369``).
+"""
+from __future__ import annotations
+
+import torch
+
+from .ops import matmul_fused_swiglu_save_factors, swiglu_grad_preact
+
+
+class FusedSwiGLUFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        h, factors = matmul_fused_swiglu_save_factors(x, w)
+        ctx.save_for_backward(x, w, factors)
+        return h
+
+    @staticmethod
+    def backward(ctx, grad_h: torch.Tensor):
+        x, w, factors = ctx.saved_tensors
+        grad_preact = swiglu_grad_preact(grad_h.contiguous(), factors, out=factors)  # in place
+        grad_x = grad_preact @ w.t() if ctx.needs_input_grad[0] else None
+        grad_w = x.t() @ grad_preact if ctx.needs_input_grad[1] else None
+        return grad_x, grad_w
+
+
+def fused_swiglu(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """Differentiable ``silu(x @ W_gate) * (x @ W_up)`` with ``w = [W_up | W_gate]``."""
+    return FusedSwiGLUFunction.apply(x, w)

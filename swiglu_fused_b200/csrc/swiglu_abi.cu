@@ -20,6 +20,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "swiglu_elementwise.cuh"
 #include "swiglu_kernel.cuh"
 
 namespace {
@@ -121,7 +122,7 @@ Variant make_variant() {
 }
 
 // Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
-constexpr int kNumVariants = 12;
+constexpr int kNumVariants = 16;
 const Variant& variant(int form, int cta_group, int block_k) {
   static const Variant table[kNumVariants] = {
       make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
@@ -130,6 +131,8 @@ const Variant& variant(int form, int cta_group, int block_k) {
       make_variant<sgl::FORM_FUSED, 2, 64>(),     make_variant<sgl::FORM_FUSED, 2, 128>(),
       make_variant<sgl::FORM_GEMM, 1, 64>(),      make_variant<sgl::FORM_GEMM, 1, 128>(),
       make_variant<sgl::FORM_GEMM, 2, 64>(),      make_variant<sgl::FORM_GEMM, 2, 128>(),
+      make_variant<sgl::FORM_FUSED_SAVE, 1, 64>(), make_variant<sgl::FORM_FUSED_SAVE, 1, 128>(),
+      make_variant<sgl::FORM_FUSED_SAVE, 2, 64>(), make_variant<sgl::FORM_FUSED_SAVE, 2, 128>(),
   };
   return table[form * 4 + (cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
 }
@@ -165,8 +168,8 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc = 0;
   int max_smem_optin = 0;
-  int max_clusters[12] = {};  // per variant, 0 = not yet queried
-  int smem_set[12] = {};      // dynamic smem attribute already raised to
+  int max_clusters[16] = {};  // per variant, 0 = not yet queried
+  int smem_set[16] = {};      // dynamic smem attribute already raised to
 };
 
 std::mutex g_dev_mutex;
@@ -243,6 +246,10 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 1;
     c->block_k = 64;
     c->group_m = 8;
+  } else if (form == SGL_FORM_FUSED_SWIGLU_SAVE) {
+    c->cta_group = 2;
+    c->block_k = 64;
+    c->group_m = 16;
   } else if (form != SGL_FORM_SILU_MUL && M >= 2048) {
     c->cta_group = 2;
     c->block_k = 128;
@@ -420,7 +427,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
-                            int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                            int n_dsts, void* factors, int64_t ldf, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
                             int64_t ldh, int64_t up_col0, int64_t gate_col0,
                             const sgl_config* cfg, void* stream) {
   int rc;
@@ -442,8 +449,13 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
   if ((rc = validate_ld(ldx, K, "ldx")) ||
       (rc = validate_ld(ldw, w_is_nk ? K : w_span, "ldw")) || (rc = validate_ld(ldh, N, "ldh")))
     return rc;
+  const int form = factors ? SGL_FORM_FUSED_SWIGLU_SAVE : SGL_FORM_FUSED_SWIGLU;
+  if (factors) {
+    if ((rc = validate_ptr(factors, "factors")) || (rc = validate_ld(ldf, 2 * N, "ldf")))
+      return rc;
+  }
   sgl_config c;
-  if ((rc = resolve_config(SGL_FORM_FUSED_SWIGLU, cfg, M, &c))) return rc;
+  if ((rc = resolve_config(form, cfg, M, &c))) return rc;
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
 
@@ -462,7 +474,18 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
                        "h")))
       return rc;
   }
-  return launch(SGL_FORM_FUSED_SWIGLU, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, M, N, K, up_col0, gate_col0,
+  if (factors) {
+    // m[1]: the silu block, columns [0, N); m[2]: the gate-factor block, columns [N, 2N).
+    // Separate maps so a ragged last tile is clipped at N, not at 2N.
+    char* f = static_cast<char*>(factors);
+    if ((rc = make_map(&th.m[1], f, M, N, ldf, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       "factors")) ||
+        (rc = make_map(&th.m[2], f + 2 * N, M, N, ldf, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       "factors")))
+      return rc;
+    n_dsts = 3;
+  }
+  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -470,7 +493,7 @@ int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, in
                             int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,
                             int64_t gate_col0, const sgl_config* cfg, void* stream) {
   void* dst[1] = {h};
-  return fused_swiglu_impl(x, w, 0, dst, 1, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg,
+  return fused_swiglu_impl(x, w, 0, dst, 1, nullptr, 0, M, N, K, ldx, ldw, ldh, up_col0, gate_col0, cfg,
                            stream);
 }
 
@@ -478,8 +501,46 @@ int sgl_matmul_fused_swiglu_nk(const void* x, const void* w_nk, void* h, int64_t
                                int64_t K, int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_row0,
                                int64_t gate_row0, const sgl_config* cfg, void* stream) {
   void* dst[1] = {h};
-  return fused_swiglu_impl(x, w_nk, 1, dst, 1, M, N, K, ldx, ldw, ldh, up_row0, gate_row0, cfg,
+  return fused_swiglu_impl(x, w_nk, 1, dst, 1, nullptr, 0, M, N, K, ldx, ldw, ldh, up_row0, gate_row0, cfg,
                            stream);
+}
+
+int sgl_matmul_fused_swiglu_save_factors(const void* x, const void* w, void* h, void* factors,
+                                         int64_t M, int64_t N, int64_t K, int64_t ldx,
+                                         int64_t ldw, int64_t ldh, int64_t ldf, int64_t up_col0,
+                                         int64_t gate_col0, const sgl_config* cfg,
+                                         void* stream) {
+  if (!factors) return fail(SGL_ERR_NULL_POINTER, "factors is NULL");
+  void* dst[1] = {h};
+  return fused_swiglu_impl(x, w, 0, dst, 1, factors, ldf, M, N, K, ldx, ldw, ldh, up_col0,
+                           gate_col0, cfg, stream);
+}
+
+int sgl_swiglu_grad_preact(const void* dy, const void* factors, void* grad_preact, int64_t M,
+                           int64_t N, int64_t lddy, int64_t ldf, int64_t ldo, void* stream) {
+  int rc;
+  if ((rc = validate_ptr(dy, "dy")) || (rc = validate_ptr(factors, "factors")) ||
+      (rc = validate_ptr(grad_preact, "grad_preact")))
+    return rc;
+  if ((rc = validate_shape(M, N, 8))) return rc;
+  if ((rc = validate_ld(lddy, N, "lddy")) || (rc = validate_ld(ldf, 2 * N, "ldf")) ||
+      (rc = validate_ld(ldo, 2 * N, "ldo")))
+    return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+  const int64_t vecs = M * (N / 8);
+  int64_t blocks = (vecs + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;   // 8 resident CTAs of 256 per SM
+  if (blocks > cap) blocks = cap;
+  sgl::grad_preact_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                            static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(dy), static_cast<const uint4*>(factors),
+      static_cast<uint4*>(grad_preact), static_cast<int>(M), static_cast<int>(N / 8), lddy / 8,
+      ldf / 8, ldo / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "grad_preact_kernel launch");
+  g_launches.fetch_add(1);
+  return SGL_OK;
 }
 
 int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const* h_dsts,
@@ -489,7 +550,7 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
   if (!h_dsts) return fail(SGL_ERR_NULL_POINTER, "h_dsts is NULL");
   if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
     return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
-  return fused_swiglu_impl(x, w, 0, h_dsts, n_dsts, M, N, K, ldx, ldw, ldh, up_col0, gate_col0,
+  return fused_swiglu_impl(x, w, 0, h_dsts, n_dsts, nullptr, 0, M, N, K, ldx, ldw, ldh, up_col0, gate_col0,
                            cfg, stream);
 }
 
@@ -559,7 +620,7 @@ int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* ds
 }
 
 int sgl_config_count(int form) {
-  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_FUSED_SWIGLU_SAVE)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int idx[kTableSize];
   return form_entries(form, idx);
@@ -567,7 +628,7 @@ int sgl_config_count(int form) {
 
 int sgl_config_get(int form, int index, sgl_config* out) {
   if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
-  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_FUSED_SWIGLU_SAVE)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int idx[kTableSize];
   const int n = form_entries(form, idx);
@@ -580,7 +641,7 @@ int sgl_config_get(int form, int index, sgl_config* out) {
 
 int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* out) {
   if (!out) return fail(SGL_ERR_NULL_POINTER, "out is NULL");
-  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_FUSED_SWIGLU_SAVE)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   int rc = validate_shape(M, N, K);
   if (rc) return rc;
@@ -589,7 +650,7 @@ int sgl_config_default(int form, int64_t M, int64_t N, int64_t K, sgl_config* ou
 
 int sgl_config_smem_bytes(int form, const sgl_config* cfg) {
   if (!cfg) return fail(SGL_ERR_NULL_POINTER, "cfg is NULL");
-  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_MATMUL)
+  if (form < SGL_FORM_SILU_MUL || form > SGL_FORM_FUSED_SWIGLU_SAVE)
     return fail(SGL_ERR_BAD_ARGUMENT, "unknown form %d", form);
   sgl_config c;
   int rc = resolve_config(form, cfg, 1 << 20, &c);

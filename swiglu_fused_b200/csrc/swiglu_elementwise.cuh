@@ -1,0 +1,55 @@
+// Backward elementwise step of the SwiGLU stage (HBM bound, no tensor cores):
+//   grad_preact[:, 0:N]  = dy * silu(gate)            (gradient w.r.t. up   = x @ W_up)
+//   grad_preact[:, N:2N] = dy * up * silu'(gate)      (gradient w.r.t. gate = x @ W_gate)
+// from the two factors the side-store forward saved, factors = [silu(gate) | up * silu'(gate)].
+// Column order matches the packed weight [W_up | W_gate], so grad_x = grad_preact @ W^T and
+// grad_W = x^T @ grad_preact need no reshuffle.  Counterpart of
+// _swiglu_grad_preact_normal_kernel (swiglu/triton/impls.py:3947-3993), which recomputes
+// the sigmoid from saved pre-activations instead.
+//
+// One thread moves 8 bf16 (16 bytes) per operand; the grid is a multiple of the SM count
+// and strides over the rows.  `out` may alias `factors` (each thread reads its elements
+// before it writes them).  Algorithmic bytes: 10 * M * N (three reads, two writes).
+#pragma once
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace sgl {
+
+__device__ __forceinline__ uint32_t mul_bf16x2_f32(uint32_t a, uint32_t b) {
+  const float a0 = __uint_as_float(a << 16), a1 = __uint_as_float(a & 0xffff0000u);
+  const float b0 = __uint_as_float(b << 16), b1 = __uint_as_float(b & 0xffff0000u);
+  __nv_bfloat162 r = __floats2bfloat162_rn(a0 * b0, a1 * b1);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+__global__ void __launch_bounds__(256)
+grad_preact_kernel(const uint4* __restrict__ dy, const uint4* factors, uint4* out, int M,
+                   int n_vec,            // N / 8
+                   int64_t lddy_vec, int64_t ldf_vec, int64_t ldo_vec) {
+  const int64_t total = static_cast<int64_t>(M) * n_vec;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t row = i / n_vec;
+    const int64_t v = i - row * n_vec;
+    const uint4 g = dy[row * lddy_vec + v];
+    const uint4 s = factors[row * ldf_vec + v];
+    const uint4 d = factors[row * ldf_vec + n_vec + v];
+    uint4 o0, o1;
+    o0.x = mul_bf16x2_f32(g.x, s.x);
+    o0.y = mul_bf16x2_f32(g.y, s.y);
+    o0.z = mul_bf16x2_f32(g.z, s.z);
+    o0.w = mul_bf16x2_f32(g.w, s.w);
+    o1.x = mul_bf16x2_f32(g.x, d.x);
+    o1.y = mul_bf16x2_f32(g.y, d.y);
+    o1.z = mul_bf16x2_f32(g.z, d.z);
+    o1.w = mul_bf16x2_f32(g.w, d.w);
+    out[row * ldo_vec + v] = o0;
+    out[row * ldo_vec + n_vec + v] = o1;
+  }
+}
+
+}  // namespace sgl

@@ -5,6 +5,10 @@
 //       replaces matmul_silu_mul_impl, swiglu/_matmul_silu_mul.cu:323-652
 //   FORM_FUSED     h = silu(x @ W[:, gate cols]) * (x @ W[:, up cols])
 //       replaces matmul_fused_swiglu_impl, swiglu/_matmul_fused_swiglu.cu:193-508
+//   FORM_FUSED_SAVE  FORM_FUSED that also stores the two factors training needs,
+//       silu(gate) and up * silu'(gate), from the same epilogue (the reference does this
+//       only in Triton: _fused_swiglu_wide_packed_save_factors_kernel,
+//       swiglu/triton/impls.py:384-468)
 //   FORM_GEMM      y = a @ b, no activation: the down projection that consumes h.  Its
 //       epilogue can ADD each tile into the buffer of the rank that owns those rows
 //       (TMA reduce over NVLink): GEMM + reduce-scatter in one kernel.  No counterpart in
@@ -42,7 +46,7 @@
 
 namespace sgl {
 
-enum : int { FORM_SILU_MUL = 0, FORM_FUSED = 1, FORM_GEMM = 2 };
+enum : int { FORM_SILU_MUL = 0, FORM_FUSED = 1, FORM_GEMM = 2, FORM_FUSED_SAVE = 3 };
 
 constexpr int kBlockM = 128;        // rows of x per CTA
 constexpr int kAccCols = 256;       // accumulator columns per tile (MMA N)
@@ -116,7 +120,11 @@ struct KernelTraits {
   // silu_mul form: the `up` chunk is overwritten with the result and stored from the same
   // buffer (no separate output staging), which leaves room for one more ring stage.
   static constexpr bool kInPlace = (kForm == FORM_SILU_MUL);
-  static constexpr int kOutCols = (kForm == FORM_FUSED) ? 128 : 256;
+  static constexpr bool kIsFused = (kForm == FORM_FUSED || kForm == FORM_FUSED_SAVE);
+  static constexpr int kOutCols = kIsFused ? 128 : 256;
+  // staging buffers per epilogue warp: the side-store form fills h, silu and the gate
+  // factor of a chunk at once
+  static constexpr int kNumOutBufs = (kForm == FORM_FUSED_SAVE) ? 3 : kOutBufs;
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
   static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
   static constexpr int kBSlabs = kBColsPerCta / 64;           // 64-column slabs this CTA loads
@@ -124,7 +132,7 @@ struct KernelTraits {
   static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
   static constexpr int kBStageBytes = kBSlabs * kBSlabBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kOutStagingBytes = kInPlace ? 0 : kEpiWarps * kOutBufs * kChunkBytes;
+  static constexpr int kOutStagingBytes = kInPlace ? 0 : kEpiWarps * kNumOutBufs * kChunkBytes;
   static constexpr int kUpStagingBytes =
       (kForm == FORM_SILU_MUL) ? kEpiWarps * kUpBufs * kChunkBytes : 0;
   static constexpr int kBarrierBytes = 512;
@@ -180,6 +188,18 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   const float e = ex2_approx(g * -1.4426950408889634f);
   const float s = g * rcp_approx(1.0f + e);
   return s * u;
+}
+
+// The three values the side-store forward writes for one element:
+//   h = silu(g) * u,  s = silu(g),  d = u * silu'(g)  with  silu' = sig + silu * (1 - sig)
+// (the same expressions as swiglu/triton/impls.py:455-461), from one ex2 and one rcp.
+__device__ __forceinline__ void silu_factors(float g, float u, float& h, float& s, float& d) {
+  const float e = ex2_approx(g * -1.4426950408889634f);
+  const float sig = rcp_approx(1.0f + e);
+  s = g * sig;
+  const float sp = sig + s * (1.0f - sig);
+  h = s * u;
+  d = u * sp;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
@@ -310,7 +330,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               for (int rb = 0; rb < kRowBoxes; ++rb) {
                 const int wdx = static_cast<int>(rank) * kRowBoxes + rb;  // 128-column window
                 int row;
-                if constexpr (kForm != FORM_FUSED) {
+                if constexpr (!T::kIsFused) {
                   row = p.b_col0 + n0 + wdx * 128;
                 } else {
                   row = (wdx == 0) ? (p.b_col0 + n0) : (p.b_col1 + n0);
@@ -326,7 +346,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               // Slab index inside the 256 accumulator columns of the cluster tile.
               const int g = static_cast<int>(rank) * T::kBSlabs + j;
               int col;
-              if constexpr (kForm != FORM_FUSED) {
+              if constexpr (!T::kIsFused) {
                 col = p.b_col0 + n0 + g * 64;
               } else {
                 col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
@@ -417,7 +437,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   } else {
     // =========================== epilogue ===========================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const uint32_t out_buf0 = sOut + q * (kOutBufs * kChunkBytes);
+    const uint32_t out_buf0 = sOut + q * (T::kNumOutBufs * kChunkBytes);
     const uint32_t up_buf0 = sUp + q * (kUpBufs * kChunkBytes);
     const uint32_t my_bar_up = bar_up + 8 * (q * kUpBufs);
     const uint32_t tempty_leader_base = (kCtaGroup == 2) ? ptx::mapa(bar_tempty, 0) : bar_tempty;
@@ -482,7 +502,63 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_BEGIN(te_busy);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
 
-      if constexpr (kForm == FORM_GEMM) {
+      if constexpr (kForm == FORM_FUSED_SAVE) {
+        // Side-store epilogue: per 64-column chunk fill three staging buffers (h, silu(gate),
+        // up * silu'(gate)) and store them with three TMA stores in one bulk group.
+        // tm_h.m[0] = h, m[1] = silu block of the factors, m[2] = gate-factor block.
+#pragma unroll 1
+        for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
+          int x, y;
+          chunk_xy(g, x, y);
+          if (lane == 0) ptx::bulk_wait_group_read<0>();
+          __syncwarp();
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            const int col = c * kChunkCols + half * 32;
+            float gate[32];
+            float upv[32];
+            ptx::tmem_ld_32x32b_x32(t_row + col, upv);
+            ptx::tmem_ld_32x32b_x32(t_row + 128 + col, gate);
+            ptx::tmem_ld_wait();
+            if (c == T::kChunksPerTile - 1 && half == 1) {
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t wh[4], ws[4], wd[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int idx = j * 8 + 2 * e;
+                float h0, s0, d0, h1, s1, d1;
+                silu_factors(gate[idx], upv[idx], h0, s0, d0);
+                silu_factors(gate[idx + 1], upv[idx + 1], h1, s1, d1);
+                wh[e] = pack_bf16x2(h0, h1);
+                ws[e] = pack_bf16x2(s0, s1);
+                wd[e] = pack_bf16x2(d0, d1);
+              }
+              const uint32_t off = row_off + ((static_cast<uint32_t>(half * 4 + j) ^ row_sw) << 4);
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + off),
+                           "r"(wh[0]), "r"(wh[1]), "r"(wh[2]), "r"(wh[3]) : "memory");
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + kChunkBytes + off),
+                           "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]) : "memory");
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + 2 * kChunkBytes + off),
+                           "r"(wd[0]), "r"(wd[1]), "r"(wd[2]), "r"(wd[3]) : "memory");
+            }
+          }
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (x < p.N && y < p.M) {
+              ptx::tma_store_2d(&tm_h.m[0], x, y, out_buf0, pol_h);
+              ptx::tma_store_2d(&tm_h.m[1], x, y, out_buf0 + kChunkBytes, pol_h);
+              ptx::tma_store_2d(&tm_h.m[2], x, y, out_buf0 + 2 * kChunkBytes, pol_h);
+            }
+            ptx::bulk_commit_group();
+          }
+        }
+      } else if constexpr (kForm == FORM_GEMM) {
         // Plain GEMM epilogue: fp32 accumulator -> bf16 (or fp32) -> staging -> TMA store, or
         // TMA reduce-add into the buffer of the rank that owns this row block.
         int x0, y;

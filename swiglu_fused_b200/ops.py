@@ -225,6 +225,57 @@ def matmul_fused_swiglu_multi_dst(A, W, dst_ptrs, ldh: int, *, up_col0: int, gat
     _lib.check(rc)
 
 
+def matmul_fused_swiglu_save_factors(A, W, *, out=None, factors=None, stream=None,
+                                     config: TileConfig | None = None):
+    """Training forward: returns ``(h, factors)`` with ``h`` as ``matmul_fused_swiglu`` and
+    ``factors[M, 2N] = [silu(gate) | up * silu'(gate)]`` written by the same epilogue
+    (reference: the Triton side-store forward, ``swiglu/triton/impls.py:384-468``)."""
+    _check_matrix(A, "A")
+    _check_matrix(W, "W")
+    M, K = A.shape
+    K2, N2 = W.shape
+    if K != K2:
+        raise ValueError(f"K mismatch: A.K={K} vs W.K={K2}")
+    if N2 % 2:
+        raise ValueError(f"W's 2nd dim ({N2}) must be even")
+    N = N2 // 2
+    if K % 8 or N % 8:
+        raise ValueError(f"K={K} and N={N} must be multiples of 8")
+    dev = _same_device(("A", A), ("W", W))
+    h = _prep_out(out, M, N, dev)
+    f = _prep_out(factors, M, 2 * N, dev, "factors")
+    cfg = _pick_config(_lib.FORM_FUSED_SWIGLU_SAVE, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_matmul_fused_swiglu_save_factors(
+            A.data_ptr(), W.data_ptr(), h.data_ptr(), f.data_ptr(), M, N, K, _ld(A), _ld(W),
+            _ld(h), _ld(f), 0, N, C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+    return h, f
+
+
+def swiglu_grad_preact(dy, factors, *, out=None, stream=None):
+    """Backward elementwise step: ``[dy * factors[:, :N] | dy * factors[:, N:]]`` =
+    ``[d/d(up) | d/d(gate)]``.  ``out=factors`` computes in place.  (Reference:
+    ``_swiglu_grad_preact_normal_kernel``, ``swiglu/triton/impls.py:3947-3993``.)"""
+    _check_matrix(dy, "dy")
+    _check_matrix(factors, "factors")
+    M, N = dy.shape
+    if tuple(factors.shape) != (M, 2 * N):
+        raise ValueError(f"factors shape {tuple(factors.shape)} != {(M, 2 * N)}")
+    if N % 8:
+        raise ValueError(f"N={N} must be a multiple of 8")
+    dev = _same_device(("dy", dy), ("factors", factors))
+    o = _prep_out(out, M, 2 * N, dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_swiglu_grad_preact(dy.data_ptr(), factors.data_ptr(), o.data_ptr(), M,
+                                                N, _ld(dy), _ld(factors), _ld(o),
+                                                _stream_handle(stream, dev))
+    _lib.check(rc)
+    return o
+
+
 def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None):
     """``A @ B`` (bf16 in, fp32 accumulate, bf16 out) on the same TMA/tcgen05 pipeline:
     the down projection ``y = h @ W_down`` that consumes the stage's output.

@@ -19,7 +19,7 @@ from ._lib import TileConfig
 
 TABLE_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tile_table.json")
 FORM_NAMES = {_lib.FORM_SILU_MUL: "silu_mul", _lib.FORM_FUSED_SWIGLU: "fused_swiglu",
-              _lib.FORM_MATMUL: "matmul"}
+              _lib.FORM_MATMUL: "matmul", _lib.FORM_FUSED_SWIGLU_SAVE: "fused_swiglu_save"}
 
 _lock = threading.Lock()
 _table: dict[str, TileConfig] | None = None

@@ -1,0 +1,81 @@
+"""Side-store forward, backward elementwise kernel and the autograd wiring, against fp32
+torch expressions (``swiglu_oracle.swiglu_factors_f32`` / ``grad_preact_f32``)."""
+import pytest
+import torch
+
+import swiglu_oracle as orc
+from swiglu_fused_b200 import TileConfig, _lib, matmul_fused_swiglu
+from swiglu_fused_b200.autograd import fused_swiglu
+from swiglu_fused_b200.ops import matmul_fused_swiglu_save_factors, swiglu_grad_preact
+from swiglu_fused_b200.workloads import make_inputs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 128, 256), (512, 1024, 2048), (200, 136, 264),
+                                    (1024, 512, 384), (64, 256, 128), (1, 8, 8)])
+def test_save_factors_forward(M, K, N):
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + K)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    h32, f32 = orc.swiglu_factors_f32(inp["x"], inp["w"])
+    plain = matmul_fused_swiglu(x, w)
+    for cg, bk in [(1, 64), (2, 64), (2, 128), (1, 128)]:
+        hbuf = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+        fbuf = torch.full((M + 2, 2 * N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+        h, f = matmul_fused_swiglu_save_factors(x, w, out=hbuf[1:M + 1, 8:8 + N],
+                                                factors=fbuf[1:M + 1, 8:8 + 2 * N],
+                                                config=TileConfig(cg, bk, 0, 8))
+        # h is the same computation as the plain fused kernel
+        assert torch.equal(h.contiguous().view(torch.int16), plain.view(torch.int16)), (cg, bk)
+        rep_s = orc.compare(f[:, :N].contiguous().cpu(), f32[:, :N].to(torch.bfloat16).contiguous(),
+                            f32[:, :N].contiguous())
+        rep_d = orc.compare(f[:, N:].contiguous().cpu(), f32[:, N:].to(torch.bfloat16).contiguous(),
+                            f32[:, N:].contiguous())
+        assert rep_s.ok, f"silu factor {(cg, bk)}: {rep_s}"
+        assert rep_d.ok, f"gate factor {(cg, bk)}: {rep_d}"
+        for buf, r, c in ((hbuf, M, N), (fbuf, M, 2 * N)):
+            guard = buf.clone()
+            guard[1:r + 1, 8:8 + c] = float("nan")
+            assert torch.isnan(guard).all(), "wrote outside the outputs"
+
+
+@pytest.mark.parametrize("M,N", [(128, 128), (300, 264), (1024, 2048), (1, 8)])
+def test_grad_preact_kernel(M, N):
+    g = torch.Generator().manual_seed(M + N)
+    dy = torch.randn((M, N), generator=g).to(torch.bfloat16)
+    factors = torch.randn((M, 2 * N), generator=g).to(torch.bfloat16)
+    ref32 = orc.grad_preact_f32(dy, factors)
+    got = swiglu_grad_preact(dy.to(DEV), factors.to(DEV))
+    # one fp32 multiply rounded once: bit exact
+    assert torch.equal(got.cpu().view(torch.int16), ref32.to(torch.bfloat16).view(torch.int16))
+    fd = factors.to(DEV)
+    same = swiglu_grad_preact(dy.to(DEV), fd, out=fd)       # in place
+    assert same is fd and torch.equal(fd.view(torch.int16), got.view(torch.int16))
+
+
+def test_autograd_matches_fp32_autograd():
+    M, K, N = 512, 256, 384
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=5)
+    x = inp["x"].to(DEV).requires_grad_(True)
+    w = inp["w"].to(DEV).requires_grad_(True)
+    gen = torch.Generator().manual_seed(6)
+    dy = torch.randn((M, N), generator=gen).to(torch.bfloat16).to(DEV)
+    h = fused_swiglu(x, w)
+    h.backward(dy)
+    xf = inp["x"].float().to(DEV).requires_grad_(True)
+    wf = inp["w"].float().to(DEV).requires_grad_(True)
+    gu = xf @ wf
+    ref = torch.nn.functional.silu(gu[:, N:]) * gu[:, :N]
+    ref.backward(dy.float())
+    for got, want, name in ((x.grad, xf.grad, "grad_x"), (w.grad, wf.grad, "grad_w")):
+        err = (got.float() - want).abs().max().item()
+        scale = want.abs().max().item()
+        assert err <= 2e-2 * scale, f"{name}: max err {err} vs scale {scale}"
