@@ -386,6 +386,14 @@ int check_device(DeviceInfo** info) {
   int dev = 0;
   int rc = device_info(&dev, info);
   if (rc != SGL_OK) return rc;
+  // The driver entry point used for the tensor maps needs a context bound to THIS host
+  // thread; a thread that has only inherited the process-wide current device has none yet.
+  thread_local int bound_device = -1;
+  if (bound_device != dev) {
+    cudaError_t e = cudaSetDevice(dev);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaSetDevice");
+    bound_device = dev;
+  }
   if ((*info)->cc / 10 != 10)
     return fail(SGL_ERR_UNSUPPORTED_DEVICE,
                 "device %d has compute capability %d.%d; this library is built for sm_100a only",
