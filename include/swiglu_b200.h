@@ -147,21 +147,33 @@ int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream);
 
 /*
- * Row-parallel form of the same product with the reduce-scatter fused in: this rank's
- * partial product a @ b is ADDED (TMA reduce, atomic per element) into the buffer of the
- * rank that owns each row block.  Destination d owns rows [d*rows_per_dst, (d+1)*rows_per_dst)
- * of the [M, N] result and dsts[d] is the address of its [rows_per_dst, N] buffer (row pitch
- * ldc, element type fp32 if dst_is_f32 else bf16), which may be peer-GPU memory mapped into
- * this process.  rows_per_dst must be a multiple of 32.  The buffers must hold their initial
- * value (normally zero) before any rank launches; the caller synchronises the ranks before
- * and after.  Additions into fp32 are exact enough to be order independent at bf16 output
- * precision; additions into bf16 round after every rank's contribution.
- * No counterpart in the reference (single GPU, no down projection).
+ * Row-parallel form of the same product with the scatter half of a reduce-scatter fused in:
+ * destination d owns rows [d*rows_per_dst, (d+1)*rows_per_dst) of the [M, N] result and
+ * dsts[d] is the address of a [rows_per_dst, N] buffer on it (row pitch ldc; element type
+ * fp32 if dst_is_f32 else bf16), which may be peer-GPU memory mapped into this process.
+ * rows_per_dst must be a multiple of 32.
+ *   accumulate = 0: each tile of this rank's partial product a @ b is STORED (plain TMA
+ *     stores over NVLink) into the owner's buffer, which is this rank's private slot there;
+ *     the owner then adds its slots with sgl_sum_bf16_slots.  Deterministic, fp32 sums.
+ *   accumulate = 1: each tile is ADDED (TMA reduce, atomic per element) into a buffer all
+ *     ranks share, which must hold its initial value (normally zero) before any rank
+ *     launches.  Into fp32 the order of additions does not matter at bf16 output precision;
+ *     into bf16 every contribution rounds.  Measured slower than accumulate = 0.
+ * The caller synchronises the ranks before and after.  No counterpart in the reference
+ * (single GPU, no down projection).
  */
 int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
-                                   int64_t rows_per_dst, int dst_is_f32, int64_t M, int64_t N,
-                                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
-                                   const sgl_config* cfg, void* stream);
+                                   int64_t rows_per_dst, int dst_is_f32, int accumulate,
+                                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                   int64_t ldc, const sgl_config* cfg, void* stream);
+
+/*
+ * out[rows, cols] = bf16( sum over s < n_slots of slots[s * slot_stride + r * lds + c] ), summed
+ * in fp32 in slot order: the reduce half of the reduce-scatter above (HBM bound).
+ * slot_stride, lds and ldo are in elements.  No counterpart in the reference.
+ */
+int sgl_sum_bf16_slots(const void* slots, int n_slots, int64_t slot_stride, void* out,
+                       int64_t rows, int64_t cols, int64_t lds, int64_t ldo, void* stream);
 
 /*
  * Tile table access.  Replaces the module-level config lists and _legal /

@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = (
     "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_matmul_bf16",
     "sgl_matmul_bf16_reduce_scatter",
+    "sgl_sum_bf16_slots",
     "sgl_config_count",
     "sgl_config_get",
     "sgl_config_default",
@@ -137,8 +138,10 @@ def load() -> C.CDLL:
         lib.sgl_matmul_bf16.restype = ip
         lib.sgl_matmul_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_matmul_bf16_reduce_scatter.restype = ip
-        lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, i64,
+        lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, ip, i64,
                                                        i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_sum_bf16_slots.restype = ip
+        lib.sgl_sum_bf16_slots.argtypes = [vp, ip, i64, vp, i64, i64, i64, i64, vp]
         lib.sgl_config_count.restype = ip
         lib.sgl_config_count.argtypes = [ip]
         lib.sgl_config_get.restype = ip

@@ -286,7 +286,7 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
            const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int b_kmajor,
-           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           int reduce_add, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -360,6 +360,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.l2_hints = cfg.l2_hints;
   p.n_dst = n_dst;
   p.b_kmajor = b_kmajor;
+  p.reduce_add = reduce_add;
   p.reduce_rows = reduce_rows;
   p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
@@ -431,7 +432,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
@@ -493,7 +494,7 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
       return rc;
     n_dsts = 3;
   }
-  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, M, N, K, up_col0, gate_col0,
+  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -551,6 +552,33 @@ int sgl_swiglu_grad_preact(const void* dy, const void* factors, void* grad_preac
   return SGL_OK;
 }
 
+int sgl_sum_bf16_slots(const void* slots, int n_slots, int64_t slot_stride, void* out,
+                       int64_t rows, int64_t cols, int64_t lds, int64_t ldo, void* stream) {
+  int rc;
+  if ((rc = validate_ptr(slots, "slots")) || (rc = validate_ptr(out, "out"))) return rc;
+  if (n_slots < 1 || n_slots > 64)
+    return fail(SGL_ERR_BAD_ARGUMENT, "n_slots=%d outside [1, 64]", n_slots);
+  if ((rc = validate_shape(rows, cols, 8))) return rc;
+  if ((rc = validate_ld(lds, cols, "lds")) || (rc = validate_ld(ldo, cols, "ldo"))) return rc;
+  if (slot_stride % 8 != 0 || slot_stride < (rows - 1) * lds + cols)
+    return fail(SGL_ERR_BAD_STRIDE, "slot_stride=%lld too small or not a multiple of 8",
+                static_cast<long long>(slot_stride));
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+  const int64_t vecs = rows * (cols / 8);
+  int64_t blocks = (vecs + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  sgl::sum_slots_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                          static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(slots), static_cast<uint4*>(out), n_slots, slot_stride / 8,
+      static_cast<int>(rows), static_cast<int>(cols / 8), lds / 8, ldo / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "sum_slots_kernel launch");
+  g_launches.fetch_add(1);
+  return SGL_OK;
+}
+
 int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const* h_dsts,
                                       int n_dsts, int64_t M, int64_t N, int64_t K, int64_t ldx,
                                       int64_t ldw, int64_t ldh, int64_t up_col0,
@@ -563,7 +591,7 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
 }
 
 static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_dsts,
-                       int64_t reduce_rows, int dst_is_f32, int64_t M, int64_t N, int64_t K,
+                       int64_t reduce_rows, int dst_is_f32, int accumulate, int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg,
                        void* stream) {
   int rc;
@@ -606,25 +634,26 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
       return rc;
   }
   return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
-                f32 ? 1 : 0, 0, M, N, K, 0, 0, c, info, stream);
+                f32 ? 1 : 0, 0, accumulate, M, N, K, 0, 0, c, info, stream);
 }
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream) {
   void* dst[1] = {c};
-  return matmul_impl(a, b, dst, 1, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
+  return matmul_impl(a, b, dst, 1, 0, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
 }
 
 int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
-                                   int64_t rows_per_dst, int dst_is_f32, int64_t M, int64_t N,
+                                   int64_t rows_per_dst, int dst_is_f32, int accumulate,
+                                   int64_t M, int64_t N,
                                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                    const sgl_config* cfg, void* stream) {
   if (!dsts) return fail(SGL_ERR_NULL_POINTER, "dsts is NULL");
   if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
     return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
   if (rows_per_dst < 1) return fail(SGL_ERR_BAD_ARGUMENT, "rows_per_dst must be >= 1");
-  return matmul_impl(a, b, dsts, n_dsts, rows_per_dst, dst_is_f32, M, N, K, lda, ldb, ldc, cfg,
-                     stream);
+  return matmul_impl(a, b, dsts, n_dsts, rows_per_dst, dst_is_f32, accumulate ? 1 : 0, M, N, K,
+                     lda, ldb, ldc, cfg, stream);
 }
 
 int sgl_config_count(int form) {

@@ -52,4 +52,38 @@ grad_preact_kernel(const uint4* __restrict__ dy, const uint4* factors, uint4* ou
   }
 }
 
+// out[r, c] = bf16( sum over s of f32(slots[s][r, c]) ): the local half of a reduce-scatter
+// whose partial products were written by every rank into its own slot of this GPU's
+// buffer.  Summation in fp32 in slot order, so the result is deterministic.  HBM bound:
+// (n_slots + 1) * rows * cols * 2 bytes.
+__global__ void __launch_bounds__(256)
+sum_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, int n_slots,
+                 int64_t slot_stride_vec, int rows, int n_vec, int64_t lds_vec,
+                 int64_t ldo_vec) {
+  const int64_t total = static_cast<int64_t>(rows) * n_vec;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t row = i / n_vec;
+    const int64_t v = i - row * n_vec;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_slots; ++s) {
+      const uint4 t = slots[s * slot_stride_vec + row * lds_vec + v];
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += __uint_as_float(w[e] << 16);
+        acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
+      }
+    }
+    uint4 o;
+    __nv_bfloat162 r;
+    r = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&r);
+    out[row * ldo_vec + v] = o;
+  }
+}
+
 }  // namespace sgl

@@ -112,6 +112,8 @@ struct KernelParams {
   int reduce_rows;      // FORM_GEMM: > 0 = add into the destination that owns the row block
                         // (destination d owns rows [d * reduce_rows, (d+1) * reduce_rows))
   int out_f32;          // FORM_GEMM: destination element type is fp32 (else bf16)
+  int reduce_add;       // FORM_GEMM with reduce_rows > 0: 1 = add into the owner's buffer,
+                        // 0 = overwrite (the owner's buffer is this rank's private slot)
   unsigned long long wait_limit_ns;
 };
 
@@ -616,7 +618,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               const int x = x0 + (f32 ? u * 32 : (u >> 1) * 64);
               if (x < p.N && y < p.M) {
                 if (p.reduce_rows > 0) {
-                  ptx::tma_reduce_add_2d(&tm_h.m[dst], x, yy, nbuf);
+                  if (p.reduce_add) {
+                    ptx::tma_reduce_add_2d(&tm_h.m[dst], x, yy, nbuf);
+                  } else {
+                    ptx::tma_store_2d(&tm_h.m[dst], x, yy, nbuf, pol_h);
+                  }
                 } else {
                   for (int d = 0; d < p.n_dst; ++d)
                     ptx::tma_store_2d(&tm_h.m[d], x, y, nbuf, pol_h);

@@ -305,13 +305,17 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
 
 
 def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, dst_f32: bool,
-                               stream=None, config: TileConfig | None = None):
-    """Adds ``A @ B`` into the row-block owners' buffers (GEMM + reduce-scatter in one kernel).
+                               accumulate: bool = True, stream=None,
+                               config: TileConfig | None = None):
+    """Sends ``A @ B`` to the row-block owners' buffers (GEMM + scatter in one kernel).
 
     ``dst_ptrs[d]`` is the device address of the ``[rows_per_dst, N]`` buffer (fp32 if
-    ``dst_f32`` else bf16, row pitch ``ldc`` elements) of the rank that owns rows
+    ``dst_f32`` else bf16, row pitch ``ldc`` elements) on the rank that owns rows
     ``[d * rows_per_dst, (d+1) * rows_per_dst)``; peers' buffers are addressed through their
-    mapping in this process.  The caller zeroes the buffers and synchronises the ranks.
+    mapping in this process.  ``accumulate=True`` adds into a buffer shared by all ranks (the
+    caller zeroes it first); ``accumulate=False`` overwrites - the buffer is then this rank's
+    private slot on the owner, summed afterwards with ``sum_bf16_slots``.  The caller
+    synchronises the ranks.
     """
     _check_matrix(A, "A")
     _check_matrix(B, "B")
@@ -328,9 +332,32 @@ def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, d
     with torch.cuda.device(dev):
         rc = _lib.load().sgl_matmul_bf16_reduce_scatter(
             A.data_ptr(), B.data_ptr(), arr, len(dst_ptrs), int(rows_per_dst), int(bool(dst_f32)),
-            M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
+            int(bool(accumulate)), M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
             _stream_handle(stream, dev))
     _lib.check(rc)
+
+
+def sum_bf16_slots(slots, out=None, *, rows: int | None = None, stream=None):
+    """``out[r, c] = bf16(sum_s slots[s, r, c])`` with fp32 accumulation in slot order.
+    ``slots`` is ``[n_slots, R, C]`` bf16 (contiguous); ``rows`` limits the sum to the first
+    rows of every slot."""
+    if slots.dim() != 3 or slots.dtype != DTYPE or not slots.is_cuda or not slots.is_contiguous():
+        raise ValueError("slots must be a contiguous [n_slots, rows, cols] bf16 CUDA tensor")
+    n, R, Ccols = slots.shape
+    r = R if rows is None else int(rows)
+    if not 0 <= r <= R:
+        raise ValueError(f"rows={r} outside [0, {R}]")
+    if Ccols % 8:
+        raise ValueError(f"cols={Ccols} must be a multiple of 8")
+    dev = slots.device
+    if r == 0:
+        return out if out is not None else torch.empty((0, Ccols), dtype=DTYPE, device=dev)
+    o = _prep_out(out, r, Ccols, dev)
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_sum_bf16_slots(slots.data_ptr(), n, R * Ccols, o.data_ptr(), r, Ccols,
+                                            Ccols, _ld(o), _stream_handle(stream, dev))
+    _lib.check(rc)
+    return o
 
 
 def tune_matmul_silu_mul(A, B_gate, up, *, verbose=False, persist=False) -> TileConfig:

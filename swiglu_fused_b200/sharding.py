@@ -150,25 +150,64 @@ class RowShardedOutput:
         self.handle.barrier(channel=0)
 
 
-def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor,
-                           out: RowShardedOutput, *, stream=None, config=None) -> torch.Tensor:
-    """``y = h @ W_down`` for a column-sharded ``h``, reduce-scatter fused into the GEMM.
+class RowParallelSlots:
+    """Receive buffers of the slot-based reduce-scatter: on every rank a bf16 tensor
+    ``[world, rows_per_rank, N]`` in symmetric memory; slot s of rank o holds rank s's
+    partial product for the rows o owns.  Collective constructor."""
 
-    Rank r holds ``h_local = h[:, cols_r]`` (exactly what the column-parallel gate/up stage
-    leaves on it - no all-gather of ``h``) and ``w_down_local = W_down[cols_r, :]``.  Each
-    rank's kernel adds its partial product tile by tile into the buffer of the rank that
-    owns those rows (TMA reduce over NVLink), so every rank ends with the complete rows it
-    owns: ``out.tensor[:out.my_rows]``.  Barriers: zeroing -> launch -> completion.
+    def __init__(self, M: int, N: int, device, group=None):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        world = dist.get_world_size(self.group)
+        self.M, self.N = M, N
+        self.rows_per_rank = -(-(-(-M // world)) // ROW_ALIGN) * ROW_ALIGN
+        self.tensor = symm_mem.empty((world, self.rows_per_rank, N), dtype=torch.bfloat16,
+                                     device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        self.rank, self.world = self.handle.rank, self.handle.world_size
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.my_rows = max(0, min(self.rows_per_rank, M - self.rank * self.rows_per_rank))
+
+    def barrier(self) -> None:
+        self.handle.barrier(channel=0)
+
+
+def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor, bufs, *,
+                           out=None, stream=None, config=None) -> torch.Tensor:
+    """``y = h @ W_down`` for a column-sharded ``h`` with the reduce-scatter fused into the
+    GEMM, so ``h`` is never gathered.
+
+    Rank r holds ``h_local = h[:, cols_r]`` (what the column-parallel gate/up stage leaves on
+    it) and ``w_down_local = W_down[cols_r, :]``.  Returns the complete rows this rank owns.
+
+    ``bufs`` selects the algorithm:
+
+    * ``RowParallelSlots`` (recommended): every tile of the partial product is TMA-stored
+      into the owner's slot for this rank while the GEMM runs; after a barrier each rank adds
+      its ``world`` slots in fp32 (``sum_bf16_slots``).  Deterministic.  Returns bf16.
+    * ``RowShardedOutput``: tiles are ADDED into one shared buffer per owner with TMA
+      reduce operations (atomic per element).  Returns a view of that buffer (fp32 or bf16).
+      Measured slower than the slot form on NVLink; kept as the single-pass alternative.
     """
-    from .ops import matmul_bf16_reduce_scatter
+    from .ops import matmul_bf16_reduce_scatter, sum_bf16_slots
 
-    out.tensor.zero_()
-    out.barrier()                      # every buffer is zero before anybody adds into it
-    matmul_bf16_reduce_scatter(h_local, w_down_local, out.ptrs, out.rows_per_rank,
-                               out.tensor.stride(0), dst_f32=out.tensor.dtype == torch.float32,
-                               stream=stream, config=config)
-    out.barrier()                      # every rank's additions have landed
-    return out.tensor[:out.my_rows]
+    if isinstance(bufs, RowParallelSlots):
+        slot_bytes = bufs.rows_per_rank * bufs.N * 2
+        dsts = [p + bufs.rank * slot_bytes for p in bufs.ptrs]
+        bufs.barrier()                 # owners have finished reading the previous contents
+        matmul_bf16_reduce_scatter(h_local, w_down_local, dsts, bufs.rows_per_rank, bufs.N,
+                                   dst_f32=False, accumulate=False, stream=stream, config=config)
+        bufs.barrier()                 # every rank's tiles have landed
+        return sum_bf16_slots(bufs.tensor, out, rows=bufs.my_rows, stream=stream)
+    bufs.tensor.zero_()
+    bufs.barrier()                     # every buffer is zero before anybody adds into it
+    matmul_bf16_reduce_scatter(h_local, w_down_local, bufs.ptrs, bufs.rows_per_rank,
+                               bufs.tensor.stride(0), dst_f32=bufs.tensor.dtype == torch.float32,
+                               accumulate=True, stream=stream, config=config)
+    bufs.barrier()                     # every rank's additions have landed
+    return bufs.tensor[:bufs.my_rows]
 
 
 def fused_swiglu_m_sharded(x_local: torch.Tensor, w: torch.Tensor, *, out=None, stream=None,

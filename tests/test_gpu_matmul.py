@@ -85,6 +85,35 @@ def test_reduce_scatter_epilogue_on_one_gpu(dst_f32):
         assert rep.max_abs <= part * 2.0 ** -7 and rep.frac_within_1ulp >= 0.9, str(rep)
 
 
+def test_slot_scatter_and_slot_sum_on_one_gpu():
+    """Two 'ranks' (K halves) write their partial products into their own slots of two owners'
+    buffers (both on this GPU); each owner then sums its slots."""
+    from swiglu_fused_b200.ops import sum_bf16_slots
+
+    M, K, N = 1024, 512, 640
+    a, b = problem(M, K, N, seed=19)
+    ad, bd = a.to(DEV), b.to(DEV)
+    rows, world = 512, 2
+    owners = [torch.full((world, rows, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+              for _ in range(world)]
+    for r in range(world):
+        ks = slice(r * K // 2, (r + 1) * K // 2)
+        dsts = [o.data_ptr() + r * rows * N * 2 for o in owners]
+        matmul_bf16_reduce_scatter(ad[:, ks], bd[ks].contiguous(), dsts, rows, N, dst_f32=False,
+                                   accumulate=False)
+    torch.cuda.synchronize()
+    got = torch.cat([sum_bf16_slots(o) for o in owners], dim=0)
+    parts = [orc.matmul_f32(a[:, r * K // 2:(r + 1) * K // 2], b[r * K // 2:(r + 1) * K // 2])
+             .to(torch.bfloat16).float() for r in range(world)]
+    want = (parts[0] + parts[1]).to(torch.bfloat16)
+    rep = orc.compare(got.cpu(), want)
+    assert rep.frac_within_1ulp >= 0.999 and rep.max_floored_rel <= 1e-2, str(rep)
+    # a limited row count and an explicit output
+    out = torch.empty((100, N), dtype=torch.bfloat16, device=DEV)
+    sum_bf16_slots(owners[0], out, rows=100)
+    assert torch.equal(out.view(torch.int16), got[:100].contiguous().view(torch.int16))
+
+
 def test_reduce_scatter_rejects_bad_row_blocks():
     a = torch.zeros((256, 64), dtype=torch.bfloat16, device=DEV)
     b = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
