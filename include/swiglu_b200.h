@@ -147,6 +147,20 @@ int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream);
 
 /*
+ * Split-K form of sgl_matmul_bf16 for short, deep problems (few output tiles, large K - the
+ * down projection at decode batch sizes): K is cut into `splits` ranges (0 = choose), each
+ * range's partial tile is written in fp32 to its slot of `scratch`, and a second kernel adds
+ * the slots in fp32, in order (deterministic), into c (bf16).  `scratch` is device memory the
+ * caller owns; sgl_matmul_bf16_splitk_scratch_bytes says how much this problem needs
+ * (negative sgl_status on a bad shape).  Contents of scratch are overwritten; two calls that
+ * overlap on the GPU must not share it.  No counterpart in the reference.
+ */
+int64_t sgl_matmul_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int64_t K, int splits);
+int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldb, int64_t ldc, int splits, void* scratch,
+                           int64_t scratch_bytes, const sgl_config* cfg, void* stream);
+
+/*
  * Row-parallel form of the same product with the scatter half of a reduce-scatter fused in:
  * destination d owns rows [d*rows_per_dst, (d+1)*rows_per_dst) of the [M, N] result and
  * dsts[d] is the address of a [rows_per_dst, N] buffer on it (row pitch ldc; element type

@@ -31,6 +31,8 @@ EXPORTED_SYMBOLS = (
     "sgl_swiglu_grad_preact",
     "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_matmul_bf16",
+    "sgl_matmul_bf16_splitk_scratch_bytes",
+    "sgl_matmul_bf16_splitk",
     "sgl_matmul_bf16_reduce_scatter",
     "sgl_sum_bf16_slots",
     "sgl_config_count",
@@ -137,6 +139,11 @@ def load() -> C.CDLL:
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_matmul_bf16.restype = ip
         lib.sgl_matmul_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_bf16_splitk_scratch_bytes.restype = i64
+        lib.sgl_matmul_bf16_splitk_scratch_bytes.argtypes = [i64, i64, i64, ip]
+        lib.sgl_matmul_bf16_splitk.restype = ip
+        lib.sgl_matmul_bf16_splitk.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, ip, vp,
+                                               i64, cfgp, vp]
         lib.sgl_matmul_bf16_reduce_scatter.restype = ip
         lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, ip, i64,
                                                        i64, i64, i64, i64, i64, cfgp, vp]

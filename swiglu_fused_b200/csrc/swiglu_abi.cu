@@ -286,7 +286,7 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
            const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int b_kmajor,
-           int reduce_add, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           int reduce_add, int splits, int k_per_split, int slot_rows, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -298,7 +298,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   const int rows_per_tile = sgl::kBlockM * cfg.cta_group;
   const int64_t tiles_m = (M + rows_per_tile - 1) / rows_per_tile;
   const int64_t tiles_n = (N + v.out_cols - 1) / v.out_cols;
-  if (tiles_m * tiles_n > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
+  if (tiles_m * tiles_n * splits > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
 
   cudaError_t e;
   {
@@ -345,7 +345,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   if (cfg.max_ctas > 0 && cfg.max_ctas / cfg.cta_group < clusters)
     clusters = cfg.max_ctas / cfg.cta_group;
   if (clusters < 1) clusters = 1;
-  if (tiles_m * tiles_n < clusters) clusters = tiles_m * tiles_n;
+  if (tiles_m * tiles_n * splits < clusters) clusters = tiles_m * tiles_n * splits;
 
   sgl::KernelParams p;
   p.M = static_cast<int>(M);
@@ -361,6 +361,9 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.n_dst = n_dst;
   p.b_kmajor = b_kmajor;
   p.reduce_add = reduce_add;
+  p.splits = splits;
+  p.k_per_split = k_per_split;
+  p.slot_rows = slot_rows;
   p.reduce_rows = reduce_rows;
   p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
@@ -432,7 +435,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
@@ -494,7 +497,7 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
       return rc;
     n_dsts = 3;
   }
-  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, M, N, K, up_col0, gate_col0,
+  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, 1, 0, 0, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -550,6 +553,113 @@ int sgl_swiglu_grad_preact(const void* dy, const void* factors, void* grad_preac
   if (e != cudaSuccess) return fail_cuda(e, "grad_preact_kernel launch");
   g_launches.fetch_add(1);
   return SGL_OK;
+}
+
+namespace {
+
+// Split-K plan: K ranges are multiples of 128 (both BLOCK_K values divide it) and every
+// range is non-empty; slots are padded to whole 32-row store boxes.
+struct SplitPlan {
+  int splits;
+  int k_per_split;
+  int slot_rows;
+  int64_t scratch_bytes;
+};
+
+int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, SplitPlan* out) {
+  if (splits < 0 || splits > 64)
+    return fail(SGL_ERR_BAD_ARGUMENT, "splits=%d outside [0, 64] (0 = choose)", splits);
+  if (splits == 0) {
+    // Enough K ranges to give every SM pair a work unit, at least 512 of K each.
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    int64_t want = (sm_count / 2 + tiles - 1) / tiles;
+    const int64_t by_k = K / 512 > 0 ? K / 512 : 1;
+    if (want > by_k) want = by_k;
+    if (want > 16) want = 16;
+    splits = want < 1 ? 1 : static_cast<int>(want);
+  }
+  int64_t per = (K + splits - 1) / splits;
+  per = (per + 127) / 128 * 128;
+  out->k_per_split = static_cast<int>(per);
+  out->splits = static_cast<int>((K + per - 1) / per);
+  out->slot_rows = static_cast<int>((M + 31) / 32 * 32);
+  out->scratch_bytes = static_cast<int64_t>(out->splits) * out->slot_rows * N * 4;
+  return SGL_OK;
+}
+
+// a @ b through `plan.splits` fp32 partial tiles in `scratch`, then the fp32 slot sum into c.
+int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, const SplitPlan& plan,
+                      void* scratch, const sgl_config* cfg, DeviceInfo* info, void* stream) {
+  int rc;
+  sgl_config cf;
+  if ((rc = resolve_config(SGL_FORM_MATMUL, cfg, M, &cf))) return rc;
+  CUtensorMap ta, tb;
+  sgl::OutMaps tc;
+  std::memset(&tc, 0, sizeof(tc));
+  if ((rc = make_map(&ta, a, M, K, lda, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "a")) ||
+      (rc = make_map(&tb, b, K, N, ldb, cf.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     "b")) ||
+      (rc = make_map(&tc.m[0], scratch, static_cast<int64_t>(plan.splits) * plan.slot_rows, N, N,
+                     32, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE, "scratch", true)))
+    return rc;
+  if ((rc = launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, 1, 0, 1, 0, 0, plan.splits,
+                   plan.k_per_split, plan.slot_rows, M, N, K, 0, 0, cf, info, stream)))
+    return rc;
+  const int64_t vecs = M * (N / 8);
+  int64_t blocks = (vecs + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
+  if (blocks > cap) blocks = cap;
+  sgl::sum_slots_f32_kernel<<<static_cast<unsigned>(blocks), 256, 0,
+                              static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float4*>(scratch), static_cast<uint4*>(c), plan.splits,
+      static_cast<int64_t>(plan.slot_rows) * N / 4, static_cast<int>(M),
+      static_cast<int>(N / 8), N / 4, ldc / 8);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "sum_slots_f32_kernel launch");
+  g_launches.fetch_add(1);
+  return SGL_OK;
+}
+
+int validate_matmul(const void* a, const void* b, const void* c, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc) {
+  int rc;
+  if ((rc = validate_ptr(a, "a")) || (rc = validate_ptr(b, "b")) || (rc = validate_ptr(c, "c")))
+    return rc;
+  if ((rc = validate_shape(M, N, K))) return rc;
+  if ((rc = validate_ld(lda, K, "lda")) || (rc = validate_ld(ldb, N, "ldb")) ||
+      (rc = validate_ld(ldc, N, "ldc")))
+    return rc;
+  return SGL_OK;
+}
+
+}  // namespace
+
+int64_t sgl_matmul_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int64_t K, int splits) {
+  if (validate_shape(M, N, K)) return SGL_ERR_BAD_SHAPE;
+  SplitPlan plan;
+  // The automatic choice depends on the SM count; size for a B200 (148 SMs).
+  int rc = plan_splitk(M, N, K, splits, 148, &plan);
+  if (rc) return rc;
+  return plan.scratch_bytes;
+}
+
+int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                           int64_t lda, int64_t ldb, int64_t ldc, int splits, void* scratch,
+                           int64_t scratch_bytes, const sgl_config* cfg, void* stream) {
+  int rc;
+  if ((rc = validate_matmul(a, b, c, M, N, K, lda, ldb, ldc))) return rc;
+  if ((rc = validate_ptr(scratch, "scratch"))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+  SplitPlan plan;
+  if ((rc = plan_splitk(M, N, K, splits, 148, &plan))) return rc;
+  if (scratch_bytes < plan.scratch_bytes)
+    return fail(SGL_ERR_BAD_ARGUMENT, "scratch holds %lld bytes, %lld needed (%d K ranges)",
+                static_cast<long long>(scratch_bytes), static_cast<long long>(plan.scratch_bytes),
+                plan.splits);
+  return matmul_splitk_run(a, b, c, M, N, K, lda, ldb, ldc, plan, scratch, cfg, info, stream);
 }
 
 int sgl_sum_bf16_slots(const void* slots, int n_slots, int64_t slot_stride, void* out,
@@ -634,7 +744,7 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
       return rc;
   }
   return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
-                f32 ? 1 : 0, 0, accumulate, M, N, K, 0, 0, c, info, stream);
+                f32 ? 1 : 0, 0, accumulate, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,

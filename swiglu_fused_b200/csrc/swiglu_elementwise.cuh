@@ -66,22 +66,52 @@ sum_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, int n
        i += stride) {
     const int64_t row = i / n_vec;
     const int64_t v = i - row * n_vec;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, a4 = 0.f, a5 = 0.f, a6 = 0.f, a7 = 0.f;
     for (int s = 0; s < n_slots; ++s) {
       const uint4 t = slots[s * slot_stride_vec + row * lds_vec + v];
-      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        acc[2 * e] += __uint_as_float(w[e] << 16);
-        acc[2 * e + 1] += __uint_as_float(w[e] & 0xffff0000u);
-      }
+      a0 += __uint_as_float(t.x << 16);
+      a1 += __uint_as_float(t.x & 0xffff0000u);
+      a2 += __uint_as_float(t.y << 16);
+      a3 += __uint_as_float(t.y & 0xffff0000u);
+      a4 += __uint_as_float(t.z << 16);
+      a5 += __uint_as_float(t.z & 0xffff0000u);
+      a6 += __uint_as_float(t.w << 16);
+      a7 += __uint_as_float(t.w & 0xffff0000u);
     }
     uint4 o;
     __nv_bfloat162 r;
-    r = __floats2bfloat162_rn(acc[0], acc[1]); o.x = *reinterpret_cast<uint32_t*>(&r);
-    r = __floats2bfloat162_rn(acc[2], acc[3]); o.y = *reinterpret_cast<uint32_t*>(&r);
-    r = __floats2bfloat162_rn(acc[4], acc[5]); o.z = *reinterpret_cast<uint32_t*>(&r);
-    r = __floats2bfloat162_rn(acc[6], acc[7]); o.w = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a0, a1); o.x = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a2, a3); o.y = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a4, a5); o.z = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a6, a7); o.w = *reinterpret_cast<uint32_t*>(&r);
+    out[row * ldo_vec + v] = o;
+  }
+}
+
+// Same for fp32 slots (split-K partial tiles): out = bf16(sum of fp32 partials).
+__global__ void __launch_bounds__(256)
+sum_slots_f32_kernel(const float4* __restrict__ slots, uint4* __restrict__ out, int n_slots,
+                     int64_t slot_stride_vec4, int rows, int n_vec, int64_t lds_vec4,
+                     int64_t ldo_vec) {
+  const int64_t total = static_cast<int64_t>(rows) * n_vec;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t row = i / n_vec;
+    const int64_t v = i - row * n_vec;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    for (int s = 0; s < n_slots; ++s) {
+      const float4* src = slots + s * slot_stride_vec4 + row * lds_vec4 + 2 * v;
+      const float4 t0 = src[0], t1 = src[1];
+      a0.x += t0.x; a0.y += t0.y; a0.z += t0.z; a0.w += t0.w;
+      a1.x += t1.x; a1.y += t1.y; a1.z += t1.z; a1.w += t1.w;
+    }
+    uint4 o;
+    __nv_bfloat162 r;
+    r = __floats2bfloat162_rn(a0.x, a0.y); o.x = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a0.z, a0.w); o.y = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a1.x, a1.y); o.z = *reinterpret_cast<uint32_t*>(&r);
+    r = __floats2bfloat162_rn(a1.z, a1.w); o.w = *reinterpret_cast<uint32_t*>(&r);
     out[row * ldo_vec + v] = o;
   }
 }

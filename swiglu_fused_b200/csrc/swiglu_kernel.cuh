@@ -112,6 +112,9 @@ struct KernelParams {
   int reduce_rows;      // FORM_GEMM: > 0 = add into the destination that owns the row block
                         // (destination d owns rows [d * reduce_rows, (d+1) * reduce_rows))
   int out_f32;          // FORM_GEMM: destination element type is fp32 (else bf16)
+  int splits;           // FORM_GEMM: K is cut into `splits` ranges of k_per_split (a multiple
+  int k_per_split;      // of BLOCK_K); work unit u = tile u / splits, range u % splits, and
+  int slot_rows;        // range s writes its partial tile at row offset s * slot_rows
   int reduce_add;       // FORM_GEMM with reduce_rows > 0: 1 = add into the owner's buffer,
                         // 0 = overwrite (the owner's buffer is this rank's private slot)
   unsigned long long wait_limit_ns;
@@ -233,8 +236,20 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const uint32_t rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
-  const int total_tiles = p.tiles_m * p.tiles_n;
-  const int num_kb = (p.K + kBlockK - 1) / kBlockK;
+  // Work units: one per output tile, or (split-K, FORM_GEMM only) one per tile and K range.
+  const int splits = (kForm == FORM_GEMM) ? p.splits : 1;
+  const int total_tiles = p.tiles_m * p.tiles_n * splits;
+  // K range of unit u and its length in k-blocks.
+  auto unit_k0 = [&](int u) { return (splits > 1) ? (u % splits) * p.k_per_split : 0; };
+  auto unit_kb = [&](int u) {
+    int len = p.K;
+    if (splits > 1) {
+      len = p.K - (u % splits) * p.k_per_split;
+      len = len < p.k_per_split ? len : p.k_per_split;
+      len = len < 0 ? 0 : len;
+    }
+    return (len + kBlockK - 1) / kBlockK;
+  };
   const int stages = p.stages;
 
   // ---- shared memory carve-up (offsets identical in both CTAs of a pair) ----
@@ -300,9 +315,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters) {
-        const TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+        const TileCoord tc = tile_coord(t / splits, p.tiles_m, p.tiles_n, p.group_m);
         const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
         const int n0 = tc.n * T::kOutCols;
+        const int num_kb = unit_kb(t);
+        const int k_base = unit_k0(t);
         for (int kb = 0; kb < num_kb; ++kb) {
           SGL_PROF_BEGIN(tp0);
           if (!ptx::mbar_wait(bar_empty + 8 * s, ph ^ 1u, limit, abort_flag)) {
@@ -314,7 +331,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           const uint32_t full_local = bar_full + 8 * s;
           const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
           ptx::mbar_arrive_expect_tx_cluster(full, T::kStageBytes);
-          const int k0 = kb * kBlockK;
+          const int k0 = k_base + kb * kBlockK;
           const uint32_t a_dst = sA + s * T::kAStageBytes;
 #pragma unroll
           for (int j = 0; j < kBlockK / 64; ++j) {
@@ -397,6 +414,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         SGL_PROF_END(prof_te, tm0);
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + as * kAccCols;
+        const int num_kb = unit_kb(t);
         for (int kb = 0; kb < num_kb; ++kb) {
           SGL_PROF_BEGIN(tm1);
           if (!ptx::mbar_wait(bar_full + 8 * s, ph, limit, abort_flag)) {
@@ -456,7 +474,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const int i = g / T::kChunksPerTile;
       const int c = g - i * T::kChunksPerTile;
       const TileCoord tc =
-          tile_coord(cluster_id + i * num_clusters, p.tiles_m, p.tiles_n, p.group_m);
+          tile_coord((cluster_id + i * num_clusters) / splits, p.tiles_m, p.tiles_n, p.group_m);
       x = tc.n * T::kOutCols + c * kChunkCols;
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
     };
@@ -571,6 +589,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         if (p.reduce_rows > 0) {
           dst = y / p.reduce_rows;
           yy = y - dst * p.reduce_rows;
+        } else if (splits > 1) {
+          // this unit's K range has its own slot of slot_rows rows in the output tensor
+          yy = y + ((cluster_id + i * num_clusters) % splits) * p.slot_rows;
         }
         uint32_t nbuf = out_buf0;
 #pragma unroll 1
@@ -625,7 +646,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                   }
                 } else {
                   for (int d = 0; d < p.n_dst; ++d)
-                    ptx::tma_store_2d(&tm_h.m[d], x, y, nbuf, pol_h);
+                    ptx::tma_store_2d(&tm_h.m[d], x, yy, nbuf, pol_h);
                 }
               }
               ptx::bulk_commit_group();

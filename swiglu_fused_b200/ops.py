@@ -304,6 +304,48 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
     return c
 
 
+def splitk_scratch_bytes(M: int, N: int, K: int, splits: int = 0) -> int:
+    """Bytes of device scratch ``matmul_bf16_splitk`` needs for this problem."""
+    n = _lib.load().sgl_matmul_bf16_splitk_scratch_bytes(M, N, K, splits)
+    if n < 0:
+        _lib.check(int(n))
+    return int(n)
+
+
+def matmul_bf16_splitk(A, B, *, out=None, splits: int = 0, scratch=None, stream=None,
+                       config: TileConfig | None = None):
+    """``A @ B`` with K cut into ``splits`` ranges (0 = choose) - for short, deep problems
+    such as the down projection at decode batch sizes, where one tile per CTA pair would
+    leave most SMs idle.  Partial tiles go to ``scratch`` in fp32 and are then summed in fp32,
+    in order.  ``scratch`` is a caller-owned uint8 CUDA tensor of at least
+    ``splitk_scratch_bytes(M, N, K, splits)`` bytes (allocated here if omitted)."""
+    _check_matrix(A, "A")
+    _check_matrix(B, "B")
+    M, K = A.shape
+    K2, N = B.shape
+    if K2 != K:
+        raise ValueError(f"K mismatch: A.K={K} vs B.K={K2}")
+    if K % 8 or N % 8:
+        raise ValueError(f"K={K} and N={N} must be multiples of 8")
+    dev = _same_device(("A", A), ("B", B))
+    c = _prep_out(out, M, N, dev)
+    need = splitk_scratch_bytes(M, N, K, splits)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+    if scratch.dtype != torch.uint8 or not scratch.is_cuda or scratch.device != dev \
+            or not scratch.is_contiguous():
+        raise ValueError("scratch must be a contiguous uint8 CUDA tensor on the operands' device")
+    cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_matmul_bf16_splitk(
+            A.data_ptr(), B.data_ptr(), c.data_ptr(), M, N, K, _ld(A), _ld(B), _ld(c), int(splits),
+            scratch.data_ptr(), scratch.numel(), C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+    return c
+
+
 def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, dst_f32: bool,
                                accumulate: bool = True, stream=None,
                                config: TileConfig | None = None):
