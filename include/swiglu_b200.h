@@ -161,6 +161,36 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
                            int64_t scratch_bytes, const sgl_config* cfg, void* stream);
 
 /*
+ * sgl_matmul_bf16_splitk for callers that cannot hand over device memory of their own.
+ * (This entry point has no counterpart in the reference.)
+ *
+ * Who that is: code that runs where every byte of device memory has already been given to
+ * somebody else's pool (an inference server that reserves the whole GPU for its KV cache and
+ * exposes no allocator to plug-ins), or on a path where cudaMalloc is off limits because it
+ * synchronises the device or may fail late (a latency-critical decode loop, a callback from
+ * another library).  Such a caller still owns a, b and c, but has nowhere to put the fp32
+ * partial tiles.  Here they go into an 8 MiB array that is part of the library image on
+ * every GPU that loads it; the call itself performs no allocation of any kind.
+ *
+ * Limits and rules:
+ *   - splits (after the automatic choice when 0) x round_up(M, 32) x N x 4 bytes must fit
+ *     8 MiB (8388608); otherwise SGL_ERR_BAD_ARGUMENT with the sizes in sgl_last_error().
+ *     Example that just fits: M <= 64, N = 4096, 8 K ranges.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and remembers it; make that first
+ *     call before any stream capture begins on the device.
+ *   - All calls on one GPU share the one array.  Its contents after a call are that call's
+ *     partial tiles; nothing has to be cleared beforehand, because every element the summing
+ *     kernel reads is written earlier in the same call.  Two calls that can run at the same
+ *     time on one GPU (different streams, different host threads) race on it: serialise them
+ *     or use sgl_matmul_bf16_splitk with separate scratch.
+ * Results are identical to sgl_matmul_bf16_splitk for the same arguments.
+ */
+int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t M, int64_t N,
+                                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int splits,
+                                  const sgl_config* cfg, void* stream);
+
+/*
  * Row-parallel form of the same product with the scatter half of a reduce-scatter fused in:
  * destination d owns rows [d*rows_per_dst, (d+1)*rows_per_dst) of the [M, N] result and
  * dsts[d] is the address of a [rows_per_dst, N] buffer on it (row pitch ldc; element type

@@ -33,6 +33,7 @@ EXPORTED_SYMBOLS = (
     "sgl_matmul_bf16",
     "sgl_matmul_bf16_splitk_scratch_bytes",
     "sgl_matmul_bf16_splitk",
+    "sgl_matmul_bf16_splitk_static",
     "sgl_matmul_bf16_reduce_scatter",
     "sgl_sum_bf16_slots",
     "sgl_config_count",
@@ -144,6 +145,9 @@ def load() -> C.CDLL:
         lib.sgl_matmul_bf16_splitk.restype = ip
         lib.sgl_matmul_bf16_splitk.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, ip, vp,
                                                i64, cfgp, vp]
+        lib.sgl_matmul_bf16_splitk_static.restype = ip
+        lib.sgl_matmul_bf16_splitk_static.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, ip,
+                                                      cfgp, vp]
         lib.sgl_matmul_bf16_reduce_scatter.restype = ip
         lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, ip, i64,
                                                        i64, i64, i64, i64, i64, cfgp, vp]

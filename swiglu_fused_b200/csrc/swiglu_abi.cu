@@ -662,6 +662,59 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
   return matmul_splitk_run(a, b, c, M, N, K, lda, ldb, ldc, plan, scratch, cfg, info, stream);
 }
 
+// ---------------------------------------------------------------- no-allocation split-K
+//
+// Scratch for sgl_matmul_bf16_splitk_static.  Every GPU that loads this library carries
+// these 8 MiB until the process exits.  In HOST code the name below is only a stand-in for
+// the symbol, not a device address: the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device while that device is current.
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_splitk_static_scratch[kStaticScratchBytes];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+std::map<int, void*> g_static_scratch_ptr;   // device ordinal -> device address of the array
+
+// Device address of the static scratch on the CURRENT device (resolved on first use).
+int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  auto it = g_static_scratch_ptr.find(dev);
+  if (it == g_static_scratch_ptr.end()) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_splitk_static_scratch);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaGetSymbolAddress(static split-K scratch)");
+    if (!ptr) return fail(SGL_ERR_NULL_POINTER, "static split-K scratch resolved to NULL");
+    it = g_static_scratch_ptr.emplace(dev, ptr).first;
+  }
+  *out = it->second;
+  return SGL_OK;
+}
+}  // namespace
+
+int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t M, int64_t N,
+                                  int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int splits,
+                                  const sgl_config* cfg, void* stream) {
+  int rc;
+  if ((rc = validate_matmul(a, b, c, M, N, K, lda, ldb, ldc))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+  SplitPlan plan;
+  if ((rc = plan_splitk(M, N, K, splits, 148, &plan))) return rc;
+  if (plan.scratch_bytes > kStaticScratchBytes)
+    return fail(SGL_ERR_BAD_ARGUMENT,
+                "this problem needs %lld bytes of split-K scratch (%d K ranges x %d rows x %lld "
+                "columns x 4), the built-in scratch holds %lld: use fewer splits or "
+                "sgl_matmul_bf16_splitk with your own scratch",
+                static_cast<long long>(plan.scratch_bytes), plan.splits, plan.slot_rows,
+                static_cast<long long>(N), static_cast<long long>(kStaticScratchBytes));
+  void* scratch = nullptr;
+  if ((rc = static_scratch_for_current_device(&scratch))) return rc;
+  return matmul_splitk_run(a, b, c, M, N, K, lda, ldb, ldc, plan, scratch, cfg, info, stream);
+}
+
 int sgl_sum_bf16_slots(const void* slots, int n_slots, int64_t slot_stride, void* out,
                        int64_t rows, int64_t cols, int64_t lds, int64_t ldo, void* stream) {
   int rc;
