@@ -203,13 +203,16 @@ int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t
  *     ranks share, which must hold its initial value (normally zero) before any rank
  *     launches.  Into fp32 the order of additions does not matter at bf16 output precision;
  *     into bf16 every contribution rounds.  Measured slower than accumulate = 0.
+ * first_dst: the tile order starts with the rows owned by this destination and wraps around;
+ * rank r of a group passes (r + 1) % world (or any rotation) so that at every moment the
+ * ranks send to different owners instead of all swamping the same one.
  * The caller synchronises the ranks before and after.  No counterpart in the reference
  * (single GPU, no down projection).
  */
 int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
                                    int64_t rows_per_dst, int dst_is_f32, int accumulate,
-                                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                                   int64_t ldc, const sgl_config* cfg, void* stream);
+                                   int first_dst, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                   int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream);
 
 /*
  * out[rows, cols] = bf16( sum over s < n_slots of slots[s * slot_stride + r * lds + c] ), summed

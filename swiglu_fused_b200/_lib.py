@@ -149,8 +149,8 @@ def load() -> C.CDLL:
         lib.sgl_matmul_bf16_splitk_static.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, ip,
                                                       cfgp, vp]
         lib.sgl_matmul_bf16_reduce_scatter.restype = ip
-        lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, ip, i64,
-                                                       i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_bf16_reduce_scatter.argtypes = [vp, vp, C.POINTER(vp), ip, i64, ip, ip, ip,
+                                                       i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_sum_bf16_slots.restype = ip
         lib.sgl_sum_bf16_slots.argtypes = [vp, ip, i64, vp, i64, i64, i64, i64, vp]
         lib.sgl_config_count.restype = ip

@@ -286,7 +286,8 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
 
 int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
            const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int b_kmajor,
-           int reduce_add, int splits, int k_per_split, int slot_rows, int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
+           int reduce_add, int splits, int k_per_split, int slot_rows, int first_dst,
+           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
            const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
@@ -364,6 +365,12 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   p.splits = splits;
   p.k_per_split = k_per_split;
   p.slot_rows = slot_rows;
+  p.m_shift = 0;
+  if (reduce_rows > 0 && first_dst > 0) {
+    // start at the first tile row owned by destination first_dst
+    p.m_shift = static_cast<int>((static_cast<int64_t>(first_dst) * reduce_rows / rows_per_tile) %
+                                 tiles_m);
+  }
   p.reduce_rows = reduce_rows;
   p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
@@ -435,7 +442,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
+  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, 1, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
@@ -497,7 +504,7 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
       return rc;
     n_dsts = 3;
   }
-  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, 1, 0, 0, M, N, K, up_col0, gate_col0,
+  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, 1, 0, 0, 0, M, N, K, up_col0, gate_col0,
                 c, info, stream);
 }
 
@@ -605,7 +612,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
                      32, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE, "scratch", true)))
     return rc;
   if ((rc = launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, 1, 0, 1, 0, 0, plan.splits,
-                   plan.k_per_split, plan.slot_rows, M, N, K, 0, 0, cf, info, stream)))
+                   plan.k_per_split, plan.slot_rows, 0, M, N, K, 0, 0, cf, info, stream)))
     return rc;
   const int64_t vecs = M * (N / 8);
   int64_t blocks = (vecs + 255) / 256;
@@ -754,7 +761,8 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
 }
 
 static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_dsts,
-                       int64_t reduce_rows, int dst_is_f32, int accumulate, int64_t M, int64_t N, int64_t K,
+                       int64_t reduce_rows, int dst_is_f32, int accumulate, int first_dst,
+                       int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg,
                        void* stream) {
   int rc;
@@ -797,26 +805,28 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
       return rc;
   }
   return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
-                f32 ? 1 : 0, 0, accumulate, 1, 0, 0, M, N, K, 0, 0, c, info, stream);
+                f32 ? 1 : 0, 0, accumulate, 1, 0, 0, first_dst, M, N, K, 0, 0, c, info, stream);
 }
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream) {
   void* dst[1] = {c};
-  return matmul_impl(a, b, dst, 1, 0, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
+  return matmul_impl(a, b, dst, 1, 0, 0, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
 }
 
 int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,
                                    int64_t rows_per_dst, int dst_is_f32, int accumulate,
-                                   int64_t M, int64_t N,
+                                   int first_dst, int64_t M, int64_t N,
                                    int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                    const sgl_config* cfg, void* stream) {
   if (!dsts) return fail(SGL_ERR_NULL_POINTER, "dsts is NULL");
   if (n_dsts < 1 || n_dsts > sgl::kMaxDst)
     return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
   if (rows_per_dst < 1) return fail(SGL_ERR_BAD_ARGUMENT, "rows_per_dst must be >= 1");
-  return matmul_impl(a, b, dsts, n_dsts, rows_per_dst, dst_is_f32, accumulate ? 1 : 0, M, N, K,
-                     lda, ldb, ldc, cfg, stream);
+  if (first_dst < 0 || first_dst >= n_dsts)
+    return fail(SGL_ERR_BAD_ARGUMENT, "first_dst=%d outside [0, %d)", first_dst, n_dsts);
+  return matmul_impl(a, b, dsts, n_dsts, rows_per_dst, dst_is_f32, accumulate ? 1 : 0, first_dst,
+                     M, N, K, lda, ldb, ldc, cfg, stream);
 }
 
 int sgl_config_count(int form) {

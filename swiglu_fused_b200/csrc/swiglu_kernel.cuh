@@ -115,6 +115,8 @@ struct KernelParams {
   int splits;           // FORM_GEMM: K is cut into `splits` ranges of k_per_split (a multiple
   int k_per_split;      // of BLOCK_K); work unit u = tile u / splits, range u % splits, and
   int slot_rows;        // range s writes its partial tile at row offset s * slot_rows
+  int m_shift;          // tile rows are visited starting at this tile row (wrapping): ranks of a
+                        // reduce-scatter start at different owners so no owner is swamped
   int reduce_add;       // FORM_GEMM with reduce_rows > 0: 1 = add into the owner's buffer,
                         // 0 = overwrite (the owner's buffer is this rank's private slot)
   unsigned long long wait_limit_ns;
@@ -239,6 +241,12 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   // Work units: one per output tile, or (split-K, FORM_GEMM only) one per tile and K range.
   const int splits = (kForm == FORM_GEMM) ? p.splits : 1;
   const int total_tiles = p.tiles_m * p.tiles_n * splits;
+  auto shifted_tile = [&](int t) {
+    TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+    tc.m += p.m_shift;
+    if (tc.m >= p.tiles_m) tc.m -= p.tiles_m;
+    return tc;
+  };
   // K range of unit u and its length in k-blocks.
   auto unit_k0 = [&](int u) { return (splits > 1) ? (u % splits) * p.k_per_split : 0; };
   auto unit_kb = [&](int u) {
@@ -315,7 +323,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters) {
-        const TileCoord tc = tile_coord(t / splits, p.tiles_m, p.tiles_n, p.group_m);
+        const TileCoord tc = shifted_tile(t / splits);
         const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
         const int n0 = tc.n * T::kOutCols;
         const int num_kb = unit_kb(t);
@@ -473,8 +481,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     auto chunk_xy = [&](int g, int& x, int& y) {
       const int i = g / T::kChunksPerTile;
       const int c = g - i * T::kChunksPerTile;
-      const TileCoord tc =
-          tile_coord((cluster_id + i * num_clusters) / splits, p.tiles_m, p.tiles_n, p.group_m);
+      const TileCoord tc = shifted_tile((cluster_id + i * num_clusters) / splits);
       x = tc.n * T::kOutCols + c * kChunkCols;
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
     };

@@ -347,7 +347,7 @@ def matmul_bf16_splitk(A, B, *, out=None, splits: int = 0, scratch=None, stream=
 
 
 def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, dst_f32: bool,
-                               accumulate: bool = True, stream=None,
+                               accumulate: bool = True, first_dst: int = 0, stream=None,
                                config: TileConfig | None = None):
     """Sends ``A @ B`` to the row-block owners' buffers (GEMM + scatter in one kernel).
 
@@ -356,8 +356,9 @@ def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, d
     ``[d * rows_per_dst, (d+1) * rows_per_dst)``; peers' buffers are addressed through their
     mapping in this process.  ``accumulate=True`` adds into a buffer shared by all ranks (the
     caller zeroes it first); ``accumulate=False`` overwrites - the buffer is then this rank's
-    private slot on the owner, summed afterwards with ``sum_bf16_slots``.  The caller
-    synchronises the ranks.
+    private slot on the owner, summed afterwards with ``sum_bf16_slots``.  ``first_dst``
+    rotates the tile order so it starts with that owner's rows (ranks pass different values
+    to spread the traffic).  The caller synchronises the ranks.
     """
     _check_matrix(A, "A")
     _check_matrix(B, "B")
@@ -374,7 +375,7 @@ def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, d
     with torch.cuda.device(dev):
         rc = _lib.load().sgl_matmul_bf16_reduce_scatter(
             A.data_ptr(), B.data_ptr(), arr, len(dst_ptrs), int(rows_per_dst), int(bool(dst_f32)),
-            int(bool(accumulate)), M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
+            int(bool(accumulate)), int(first_dst), M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
             _stream_handle(stream, dev))
     _lib.check(rc)
 

@@ -198,14 +198,17 @@ def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor, bu
         dsts = [p + bufs.rank * slot_bytes for p in bufs.ptrs]
         bufs.barrier()                 # owners have finished reading the previous contents
         matmul_bf16_reduce_scatter(h_local, w_down_local, dsts, bufs.rows_per_rank, bufs.N,
-                                   dst_f32=False, accumulate=False, stream=stream, config=config)
+                                   dst_f32=False, accumulate=False,
+                                   first_dst=(bufs.rank + 1) % bufs.world, stream=stream,
+                                   config=config)
         bufs.barrier()                 # every rank's tiles have landed
         return sum_bf16_slots(bufs.tensor, out, rows=bufs.my_rows, stream=stream)
     bufs.tensor.zero_()
     bufs.barrier()                     # every buffer is zero before anybody adds into it
     matmul_bf16_reduce_scatter(h_local, w_down_local, bufs.ptrs, bufs.rows_per_rank,
                                bufs.tensor.stride(0), dst_f32=bufs.tensor.dtype == torch.float32,
-                               accumulate=True, stream=stream, config=config)
+                               accumulate=True, first_dst=(bufs.rank + 1) % bufs.world,
+                               stream=stream, config=config)
     bufs.barrier()                     # every rank's additions have landed
     return bufs.tensor[:bufs.my_rows]
 

@@ -68,7 +68,8 @@ def test_reduce_scatter_epilogue_on_one_gpu(dst_f32):
     ptrs = [t.data_ptr() for t in bufs]
     for r in range(2):                                   # rank r holds K-slice r
         ks = slice(r * K // 2, (r + 1) * K // 2)
-        matmul_bf16_reduce_scatter(ad[:, ks], bd[ks].contiguous(), ptrs, rows, N, dst_f32=dst_f32)
+        matmul_bf16_reduce_scatter(ad[:, ks], bd[ks].contiguous(), ptrs, rows, N, dst_f32=dst_f32,
+                                   first_dst=r)          # each 'rank' starts at a different owner
     torch.cuda.synchronize()
     got = torch.cat(bufs, dim=0)
     ref32 = orc.matmul_f32(a, b)
@@ -100,7 +101,7 @@ def test_slot_scatter_and_slot_sum_on_one_gpu():
         ks = slice(r * K // 2, (r + 1) * K // 2)
         dsts = [o.data_ptr() + r * rows * N * 2 for o in owners]
         matmul_bf16_reduce_scatter(ad[:, ks], bd[ks].contiguous(), dsts, rows, N, dst_f32=False,
-                                   accumulate=False)
+                                   accumulate=False, first_dst=(r + 1) % world)
     torch.cuda.synchronize()
     got = torch.cat([sum_bf16_slots(o) for o in owners], dim=0)
     parts = [orc.matmul_f32(a[:, r * K // 2:(r + 1) * K // 2], b[r * K // 2:(r + 1) * K // 2])
