@@ -202,7 +202,8 @@ int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t
  *   accumulate = 1: each tile is ADDED (TMA reduce, atomic per element) into a buffer all
  *     ranks share, which must hold its initial value (normally zero) before any rank
  *     launches.  Into fp32 the order of additions does not matter at bf16 output precision;
- *     into bf16 every contribution rounds.  Measured slower than accumulate = 0.
+ *     into bf16 every contribution rounds and the order (hence the last bit) varies run to
+ *     run.  Fastest form with a bf16 buffer; an fp32 buffer doubles the NVLink bytes.
  * first_dst: the tile order starts with the rows owned by this destination and wraps around;
  * rank r of a group passes (r + 1) % world (or any rotation) so that at every moment the
  * ranks send to different owners instead of all swamping the same one.

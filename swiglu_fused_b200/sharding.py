@@ -184,12 +184,13 @@ def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor, bu
 
     ``bufs`` selects the algorithm:
 
-    * ``RowParallelSlots`` (recommended): every tile of the partial product is TMA-stored
+    * ``RowParallelSlots`` (default choice: deterministic, fp32 sums): every tile of the partial product is TMA-stored
       into the owner's slot for this rank while the GEMM runs; after a barrier each rank adds
       its ``world`` slots in fp32 (``sum_bf16_slots``).  Deterministic.  Returns bf16.
     * ``RowShardedOutput``: tiles are ADDED into one shared buffer per owner with TMA
       reduce operations (atomic per element).  Returns a view of that buffer (fp32 or bf16).
-      Measured slower than the slot form on NVLink; kept as the single-pass alternative.
+      Single pass and, with a bf16 buffer, the fastest form, but every contribution rounds to
+      bf16 and the order of additions (hence the last bit) varies from run to run.
     """
     from .ops import matmul_bf16_reduce_scatter, sum_bf16_slots
 
