@@ -19,6 +19,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libswiglu_b200.so")
 SOURCES = [os.path.join(CSRC_DIR, "swiglu_abi.cu")]
 HEADERS = [
     os.path.join(CSRC_DIR, "swiglu_kernel.cuh"),
+    os.path.join(CSRC_DIR, "swiglu_elementwise.cuh"),
     os.path.join(CSRC_DIR, "ptx_sm100.cuh"),
     os.path.join(os.path.dirname(PKG_DIR), "include", "swiglu_b200.h"),
 ]

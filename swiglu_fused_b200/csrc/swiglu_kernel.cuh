@@ -1,6 +1,6 @@
 // Persistent, warp-specialised fused SwiGLU gate/up kernel for sm_100a.
 //
-// Two forms share one skeleton:
+// Four forms share one skeleton:
 //   FORM_SILU_MUL  h = silu(x @ W_gate) * up              (up is an input)
 //       replaces matmul_silu_mul_impl, swiglu/_matmul_silu_mul.cu:323-652
 //   FORM_FUSED     h = silu(x @ W[:, gate cols]) * (x @ W[:, up cols])
@@ -10,9 +10,11 @@
 //       only in Triton: _fused_swiglu_wide_packed_save_factors_kernel,
 //       swiglu/triton/impls.py:384-468)
 //   FORM_GEMM      y = a @ b, no activation: the down projection that consumes h.  Its
-//       epilogue can ADD each tile into the buffer of the rank that owns those rows
-//       (TMA reduce over NVLink): GEMM + reduce-scatter in one kernel.  No counterpart in
-//       the reference, which stops at h.
+//       epilogue can send each tile to the rank that owns those rows - stored into that
+//       rank's slot for this sender, or ADDED into a shared buffer (TMA reduce) - over
+//       NVLink: GEMM + reduce-scatter in one kernel.  It can also cut K into ranges whose
+//       partial tiles go to separate slots (split-K).  No counterpart in the reference,
+//       which stops at h.
 //
 // Design (not the reference's):
 //   * persistent grid, one CTA (or CTA pair) per SM, static GROUP_SIZE_M-swizzled
