@@ -274,6 +274,14 @@ int sgl_shard_range(int64_t total, int64_t align, int world, int rank, int64_t* 
  * (swiglu/_matmul_silu_mul.cu:152-161).
  */
 int sgl_device_status(uint32_t* words);
+/*
+ * Self-test of the bounded waits: launches one tiny kernel whose only thread waits, with the
+ * given limit (<= 1 s), on a barrier nobody signals.  The wait must run out, the kernel must
+ * record the time-out and exit normally; the next sgl_device_status then returns
+ * SGL_ERR_DEVICE_STATUS with code 0x1ff and the context stays usable.  Nothing faults, traps
+ * or hangs.  No counterpart in the reference.
+ */
+int sgl_selftest_wait_timeout(uint64_t limit_ns, void* stream);
 /* Per-wait time limit in nanoseconds for kernels launched afterwards (default 2e9). */
 int sgl_set_wait_limit_ns(uint64_t ns);
 

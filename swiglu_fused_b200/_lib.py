@@ -44,6 +44,7 @@ EXPORTED_SYMBOLS = (
     "sgl_query",
     "sgl_shard_range",
     "sgl_device_status",
+    "sgl_selftest_wait_timeout",
     "sgl_set_wait_limit_ns",
     "sgl_last_error",
     "sgl_version",
@@ -169,6 +170,8 @@ def load() -> C.CDLL:
         lib.sgl_shard_range.argtypes = [i64, i64, ip, ip, C.POINTER(i64), C.POINTER(i64)]
         lib.sgl_device_status.restype = ip
         lib.sgl_device_status.argtypes = [C.POINTER(C.c_uint32)]
+        lib.sgl_selftest_wait_timeout.restype = ip
+        lib.sgl_selftest_wait_timeout.argtypes = [C.c_uint64, vp]
         lib.sgl_set_wait_limit_ns.restype = ip
         lib.sgl_set_wait_limit_ns.argtypes = [C.c_uint64]
         lib.sgl_last_error.restype = C.c_char_p

@@ -939,6 +939,18 @@ int sgl_device_status(uint32_t* words) {
   return SGL_OK;
 }
 
+int sgl_selftest_wait_timeout(uint64_t limit_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull)
+    return fail(SGL_ERR_BAD_ARGUMENT, "limit must be in (0, 1e9] ns");
+  DeviceInfo* info = nullptr;
+  int rc = check_device(&info);
+  if (rc) return rc;
+  sgl::wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail_cuda(e, "wait_timeout_selftest_kernel launch");
+  return SGL_OK;
+}
+
 int sgl_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) return fail(SGL_ERR_BAD_ARGUMENT, "wait limit must be > 0");
   g_wait_limit_ns.store(ns);

@@ -31,24 +31,35 @@ grad_preact_kernel(const uint4* __restrict__ dy, const uint4* factors, uint4* ou
                    int64_t lddy_vec, int64_t ldf_vec, int64_t ldo_vec) {
   const int64_t total = static_cast<int64_t>(M) * n_vec;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // Two independent 16-byte vectors per thread and iteration: six loads in flight before the
+  // first store.
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += stride) {
-    const int64_t row = i / n_vec;
-    const int64_t v = i - row * n_vec;
-    const uint4 g = dy[row * lddy_vec + v];
-    const uint4 s = factors[row * ldf_vec + v];
-    const uint4 d = factors[row * ldf_vec + n_vec + v];
-    uint4 o0, o1;
-    o0.x = mul_bf16x2_f32(g.x, s.x);
-    o0.y = mul_bf16x2_f32(g.y, s.y);
-    o0.z = mul_bf16x2_f32(g.z, s.z);
-    o0.w = mul_bf16x2_f32(g.w, s.w);
-    o1.x = mul_bf16x2_f32(g.x, d.x);
-    o1.y = mul_bf16x2_f32(g.y, d.y);
-    o1.z = mul_bf16x2_f32(g.z, d.z);
-    o1.w = mul_bf16x2_f32(g.w, d.w);
-    out[row * ldo_vec + v] = o0;
-    out[row * ldo_vec + n_vec + v] = o1;
+       i += 2 * stride) {
+    const int64_t j = i + stride;
+    const bool two = j < total;
+    const int64_t row0 = i / n_vec, v0 = i - row0 * n_vec;
+    const int64_t row1 = two ? j / n_vec : row0, v1 = two ? j - row1 * n_vec : v0;
+    const uint4 g0 = dy[row0 * lddy_vec + v0];
+    const uint4 s0 = factors[row0 * ldf_vec + v0];
+    const uint4 d0 = factors[row0 * ldf_vec + n_vec + v0];
+    const uint4 g1 = dy[row1 * lddy_vec + v1];
+    const uint4 s1 = factors[row1 * ldf_vec + v1];
+    const uint4 d1 = factors[row1 * ldf_vec + n_vec + v1];
+    uint4 o;
+    o.x = mul_bf16x2_f32(g0.x, s0.x); o.y = mul_bf16x2_f32(g0.y, s0.y);
+    o.z = mul_bf16x2_f32(g0.z, s0.z); o.w = mul_bf16x2_f32(g0.w, s0.w);
+    out[row0 * ldo_vec + v0] = o;
+    o.x = mul_bf16x2_f32(g0.x, d0.x); o.y = mul_bf16x2_f32(g0.y, d0.y);
+    o.z = mul_bf16x2_f32(g0.z, d0.z); o.w = mul_bf16x2_f32(g0.w, d0.w);
+    out[row0 * ldo_vec + n_vec + v0] = o;
+    if (two) {
+      o.x = mul_bf16x2_f32(g1.x, s1.x); o.y = mul_bf16x2_f32(g1.y, s1.y);
+      o.z = mul_bf16x2_f32(g1.z, s1.z); o.w = mul_bf16x2_f32(g1.w, s1.w);
+      out[row1 * ldo_vec + v1] = o;
+      o.x = mul_bf16x2_f32(g1.x, d1.x); o.y = mul_bf16x2_f32(g1.y, d1.y);
+      o.z = mul_bf16x2_f32(g1.z, d1.z); o.w = mul_bf16x2_f32(g1.w, d1.w);
+      out[row1 * ldo_vec + n_vec + v1] = o;
+    }
   }
 }
 

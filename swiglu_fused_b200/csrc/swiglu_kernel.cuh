@@ -70,6 +70,7 @@ enum : unsigned {
   kErrMmaTmemEmptyWait = 0x103,
   kErrEpiTmemFullWait = 0x104,
   kErrEpiUpWait = 0x105,
+  kErrSelfTestWait = 0x1ff,   // the deliberate timeout of wait_timeout_selftest_kernel
 };
 
 // First-error record, readable from the host with cudaMemcpyFromSymbol.
@@ -223,6 +224,22 @@ __device__ __forceinline__ void report_error(unsigned code, unsigned detail, int
   }
   atomicAdd(&g_status[3], 1u);
   *reinterpret_cast<volatile int*>(abort_flag) = 1;
+}
+
+// Exercises the bounded-wait path on real hardware without any risk of a hang: one thread
+// waits on an mbarrier that nobody will ever arrive on, with the given time limit, and must
+// come back with a timeout, record kErrSelfTestWait in g_status and exit normally.
+__global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int flags[2];
+  if (threadIdx.x == 0) {
+    flags[0] = 0;
+    flags[1] = 0;
+    const uint32_t b = ptx::smem_u32(&bar);
+    ptx::mbar_init(b, 1);
+    ptx::fence_mbar_init();
+    if (!ptx::mbar_wait(b, 0, limit_ns, flags)) report_error(kErrSelfTestWait, 0, flags);
+  }
 }
 
 template <int kForm, int kCtaGroup, int kBlockK>

@@ -372,3 +372,25 @@ def test_concurrent_launches_from_two_host_threads():
     assert not errors, errors
     for o in outs:
         assert torch.equal(bits(o), bits(ref))
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+    """Failure detection without a fault: a wait nobody satisfies times out after 2 ms, the
+    kernel records it and exits, the host sees the status, and the next launch works."""
+    import time
+
+    lib = _lib.load()
+    torch.cuda.synchronize()
+    _lib.device_status()                                   # clean before
+    t0 = time.perf_counter()
+    assert lib.sgl_selftest_wait_timeout(2_000_000, None) == 0
+    with pytest.raises(_lib.SglError) as err:
+        _lib.device_status()                               # synchronises, reads, clears
+    elapsed = time.perf_counter() - t0
+    assert err.value.code == -9 and "0x1ff" in err.value.message
+    assert elapsed < 1.0, f"the bounded wait took {elapsed:.3f} s for a 2 ms limit"
+    assert _lib.device_status()[0] == 0                    # record was cleared
+    inp = make_inputs(256, 128, 256, form="fused_swiglu", seed=91)
+    ref32 = orc.fused_swiglu_f32(inp["x"], inp["w"])
+    h = matmul_fused_swiglu(inp["x"].to(DEV), inp["w"].to(DEV))
+    assert orc.compare(h.cpu(), ref32.to(torch.bfloat16), ref32).ok
