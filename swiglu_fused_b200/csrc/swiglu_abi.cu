@@ -250,6 +250,7 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 2;
     c->block_k = 64;
     c->group_m = 16;
+    c->l2_hints = 2 | (1 << 4);   // x evict-last, h and factor stores evict-first (measured)
   } else if (form != SGL_FORM_SILU_MUL && M >= 2048) {
     c->cta_group = 2;
     c->block_k = 128;
