@@ -287,7 +287,7 @@ def run_ours(args) -> None:
     if not args.no_e2e and args.form == "fused_swiglu":
         e2e_steps = max(2, min(args.steps, 8))
         pipe = HostPipeline(rows.count, K_DIM, N_OUT, device=dev,
-                            blocks=8 if rows.count >= 2048 else 1)
+                            blocks=max(1, min(16, rows.count // 2048)))
         x_host = torch.empty((rows.count, K_DIM), dtype=torch.bfloat16).pin_memory()
         w_host = torch.empty((K_DIM, 2 * N_OUT), dtype=torch.bfloat16).pin_memory()
         h_host = torch.empty((rows.count, N_OUT), dtype=torch.bfloat16).pin_memory()

@@ -14,6 +14,10 @@
  *   - inputs are borrowed for the duration of the enqueue only; the library
  *     never allocates device memory and never synchronises unless stated;
  *   - `stream` is a cudaStream_t / CUstream passed as void* (NULL = default);
+ *   - the first launch of a kernel variant on a device raises its shared-memory limit and
+ *     queries the cluster occupancy (cudaFuncSetAttribute, cudaOccupancyMaxActiveClusters);
+ *     make that first call outside stream capture - later calls only encode tensor maps on
+ *     the host and launch;
  *   - functions return 0 on success, a negative sgl_status on invalid use and a
  *     positive cudaError_t value when the CUDA runtime or driver failed;
  *     sgl_last_error() describes the last failure of the calling thread.
