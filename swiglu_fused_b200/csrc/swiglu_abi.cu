@@ -68,10 +68,11 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // Rank-2 bf16 map over a row-major [rows, cols] tensor with row pitch `ld`
-// elements; box = box_cols (<= 64, one 128-byte swizzle row) x box_rows.
+// elements; box = box_cols (one swizzle row: <= 128 bytes, or <= 64 with the 64B swizzle)
+// x box_rows.
 int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld,
              int box_rows, int box_cols, CUtensorMapL2promotion promo, const char* name,
-             bool f32 = false) {
+             bool f32 = false, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(SGL_ERR_NO_DRIVER, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -80,7 +81,7 @@ int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                   const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     return fail(SGL_ERR_TENSOR_MAP,
@@ -248,7 +249,7 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->group_m = 8;
   } else if (form == SGL_FORM_FUSED_SWIGLU_SAVE) {
     c->cta_group = 2;
-    c->block_k = 64;
+    c->block_k = (M >= 2048) ? 128 : 64;
     c->group_m = 16;
     c->l2_hints = 2 | (1 << 4);   // x evict-last, h and factor stores evict-first (measured)
   } else if (form != SGL_FORM_SILU_MUL && M >= 2048) {
@@ -490,18 +491,22 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "w")))
     return rc;
   for (int d = 0; d < n_dsts; ++d) {
-    if ((rc = make_map(&th.m[d], h_dsts[d], M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       "h")))
+    // the side-store form stages 32-column half chunks (64-byte rows, 64B swizzle)
+    if ((rc = factors ? make_map(&th.m[d], h_dsts[d], M, N, ldh, 32, 32,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, "h", false,
+                                 CU_TENSOR_MAP_SWIZZLE_64B)
+                      : make_map(&th.m[d], h_dsts[d], M, N, ldh, 32, 64,
+                                 CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
       return rc;
   }
   if (factors) {
     // m[1]: the silu block, columns [0, N); m[2]: the gate-factor block, columns [N, 2N).
     // Separate maps so a ragged last tile is clipped at N, not at 2N.
     char* f = static_cast<char*>(factors);
-    if ((rc = make_map(&th.m[1], f, M, N, ldf, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       "factors")) ||
-        (rc = make_map(&th.m[2], f + 2 * N, M, N, ldf, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                       "factors")))
+    if ((rc = make_map(&th.m[1], f, M, N, ldf, 32, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       "factors", false, CU_TENSOR_MAP_SWIZZLE_64B)) ||
+        (rc = make_map(&th.m[2], f + 2 * N, M, N, ldf, 32, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                       "factors", false, CU_TENSOR_MAP_SWIZZLE_64B)))
       return rc;
     n_dsts = 3;
   }

@@ -132,9 +132,10 @@ struct KernelTraits {
   static constexpr bool kInPlace = (kForm == FORM_SILU_MUL);
   static constexpr bool kIsFused = (kForm == FORM_FUSED || kForm == FORM_FUSED_SAVE);
   static constexpr int kOutCols = kIsFused ? 128 : 256;
-  // staging buffers per epilogue warp: the side-store form fills h, silu and the gate
-  // factor of a chunk at once
-  static constexpr int kNumOutBufs = (kForm == FORM_FUSED_SAVE) ? 3 : kOutBufs;
+  // staging per epilogue warp: two 64-column chunk buffers, or for the side-store form three
+  // 32-column buffers (h, silu, gate factor) so that a BLOCK_K = 128 ring still fits
+  static constexpr int kNumOutBufs = kOutBufs;
+  static constexpr int kSaveBufBytes = 32 * 32 * 2;   // 32 rows x 64 B
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
   static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
   static constexpr int kBSlabs = kBColsPerCta / 64;           // 64-column slabs this CTA loads
@@ -142,7 +143,10 @@ struct KernelTraits {
   static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
   static constexpr int kBStageBytes = kBSlabs * kBSlabBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kOutStagingBytes = kInPlace ? 0 : kEpiWarps * kNumOutBufs * kChunkBytes;
+  static constexpr int kOutStagingBytes =
+      kInPlace ? 0
+               : (kForm == FORM_FUSED_SAVE ? kEpiWarps * 3 * kSaveBufBytes
+                                           : kEpiWarps * kNumOutBufs * kChunkBytes);
   static constexpr int kUpStagingBytes =
       (kForm == FORM_SILU_MUL) ? kEpiWarps * kUpBufs * kChunkBytes : 0;
   static constexpr int kBarrierBytes = 512;
@@ -484,7 +488,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   } else {
     // =========================== epilogue ===========================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
-    const uint32_t out_buf0 = sOut + q * (T::kNumOutBufs * kChunkBytes);
+    const uint32_t out_buf0 =
+        sOut + q * (kForm == FORM_FUSED_SAVE ? 3 * T::kSaveBufBytes : T::kNumOutBufs * kChunkBytes);
     const uint32_t up_buf0 = sUp + q * (kUpBufs * kChunkBytes);
     const uint32_t my_bar_up = bar_up + 8 * (q * kUpBufs);
     const uint32_t tempty_leader_base = (kCtaGroup == 2) ? ptx::mapa(bar_tempty, 0) : bar_tempty;
@@ -549,15 +554,17 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
 
       if constexpr (kForm == FORM_FUSED_SAVE) {
-        // Side-store epilogue: per 64-column chunk fill three staging buffers (h, silu(gate),
-        // up * silu'(gate)) and store them with three TMA stores in one bulk group.
+        // Side-store epilogue: per 32-column half chunk fill three small staging buffers
+        // (h, silu(gate), up * silu'(gate); 64-byte rows, 64B swizzle) and store them with
+        // three TMA stores in one bulk group.
         // tm_h.m[0] = h, m[1] = silu block of the factors, m[2] = gate-factor block.
+        constexpr uint32_t kSB = T::kSaveBufBytes;
+        const uint32_t off_row = static_cast<uint32_t>(lane) * 64u;
+        const uint32_t sw64 = (static_cast<uint32_t>(lane) >> 1) & 3u;
 #pragma unroll 1
         for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
           int x, y;
           chunk_xy(g, x, y);
-          if (lane == 0) ptx::bulk_wait_group_read<0>();
-          __syncwarp();
 #pragma unroll 1
           for (int half = 0; half < 2; ++half) {
             const int col = c * kChunkCols + half * 32;
@@ -571,6 +578,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               __syncwarp();
               if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
             }
+            if (lane == 0) ptx::bulk_wait_group_read<0>();   // previous half's stores have read
+            __syncwarp();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint32_t wh[4], ws[4], wd[4];
@@ -584,24 +593,25 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                 ws[e] = pack_bf16x2(s0, s1);
                 wd[e] = pack_bf16x2(d0, d1);
               }
-              const uint32_t off = row_off + ((static_cast<uint32_t>(half * 4 + j) ^ row_sw) << 4);
+              const uint32_t off = off_row + ((static_cast<uint32_t>(j) ^ sw64) << 4);
               asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + off),
                            "r"(wh[0]), "r"(wh[1]), "r"(wh[2]), "r"(wh[3]) : "memory");
-              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + kChunkBytes + off),
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + kSB + off),
                            "r"(ws[0]), "r"(ws[1]), "r"(ws[2]), "r"(ws[3]) : "memory");
-              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + 2 * kChunkBytes + off),
+              asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(out_buf0 + 2 * kSB + off),
                            "r"(wd[0]), "r"(wd[1]), "r"(wd[2]), "r"(wd[3]) : "memory");
             }
-          }
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (x < p.N && y < p.M) {
-              ptx::tma_store_2d(&tm_h.m[0], x, y, out_buf0, pol_h);
-              ptx::tma_store_2d(&tm_h.m[1], x, y, out_buf0 + kChunkBytes, pol_h);
-              ptx::tma_store_2d(&tm_h.m[2], x, y, out_buf0 + 2 * kChunkBytes, pol_h);
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int xh = x + half * 32;
+              if (xh < p.N && y < p.M) {
+                ptx::tma_store_2d(&tm_h.m[0], xh, y, out_buf0, pol_h);
+                ptx::tma_store_2d(&tm_h.m[1], xh, y, out_buf0 + kSB, pol_h);
+                ptx::tma_store_2d(&tm_h.m[2], xh, y, out_buf0 + 2 * kSB, pol_h);
+              }
+              ptx::bulk_commit_group();
             }
-            ptx::bulk_commit_group();
           }
         }
       } else if constexpr (kForm == FORM_GEMM) {

@@ -27,7 +27,7 @@ def test_save_factors_forward(M, K, N):
     x, w = inp["x"].to(DEV), inp["w"].to(DEV)
     h32, f32 = orc.swiglu_factors_f32(inp["x"], inp["w"])
     plain = matmul_fused_swiglu(x, w)
-    for cg, bk in [(1, 64), (2, 64), (2, 128)]:     # (1, 128) leaves no room for a 2-stage ring
+    for cg, bk in [(1, 64), (1, 128), (2, 64), (2, 128)]:
         hbuf = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
         fbuf = torch.full((M + 2, 2 * N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
         h, f = matmul_fused_swiglu_save_factors(x, w, out=hbuf[1:M + 1, 8:8 + N],
