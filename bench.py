@@ -136,15 +136,16 @@ def cpu_reference_rate(target_s: float, threads: int) -> dict:
                       f"torch fp32 CPU, {dt:.2f} s", "rows": rows_target, "seconds": dt}
 
 
-def gpu_baselines(x, w, n_out: int, iters: int) -> dict:
+def gpu_baselines(x, w, n_out: int, iters: int, ours) -> dict:
     """Library baselines on the same GPU, same tensors: cuBLAS [M,2N] GEMM alone, plus eager
     and torch.compile'd ``silu(gu[:, N:]) * gu[:, :N]`` (the reference's B1/B2,
-    ``bench_fused.py:52-62``).  Reported beside the kernel, never used by it."""
+    ``bench_fused.py:52-62``).  Reported beside the kernel, never used by it.  The candidates
+    are timed round-robin (three rounds, medians) together with this build's kernel, so that
+    all of them see the same thermal / power-cap state."""
     import torch.nn.functional as F
 
     def timed(fn):
-        for _ in range(3):
-            fn()
+        fn()
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
@@ -154,19 +155,26 @@ def gpu_baselines(x, w, n_out: int, iters: int) -> dict:
         torch.cuda.synchronize()
         return s.elapsed_time(e) / iters
 
-    out = {"cublas_gemm_ms": timed(lambda: x @ w)}
-
     def eager():
         gu = x @ w
         return F.silu(gu[:, n_out:]) * gu[:, :n_out]
 
-    out["cublas_plus_eager_act_ms"] = timed(eager)
+    cands = {"this_build_ms": ours, "cublas_gemm_ms": lambda: x @ w,
+             "cublas_plus_eager_act_ms": eager}
+    out = {}
     try:
         act = torch.compile(lambda gu: F.silu(gu[:, n_out:]) * gu[:, :n_out])
-        out["cublas_plus_compiled_act_ms"] = timed(lambda: act(x @ w))
+        act(x @ w)                                   # compile outside the timing
+        cands["cublas_plus_compiled_act_ms"] = lambda: act(x @ w)
     except Exception as e:  # inductor unavailable on this box
         out["cublas_plus_compiled_act_ms"] = None
         out["compile_error"] = repr(e)[:200]
+    samples = {k: [] for k in cands}
+    for _ in range(3):
+        for k, fn in cands.items():
+            samples[k].append(timed(fn))
+    for k, v in samples.items():
+        out[k] = sorted(v)[1]
     return out
 
 
@@ -368,10 +376,11 @@ def run_ours(args) -> None:
         del inp3, up, h3
         _lib.device_status()
         if not args.no_gpu_baselines:
-            line["gpu_baselines"] = gpu_baselines(x, w, N_OUT, max(5, args.steps // 2))
-            b = line["gpu_baselines"].get("cublas_plus_compiled_act_ms") or \
-                line["gpu_baselines"].get("cublas_plus_eager_act_ms")
-            line["gpu_baselines"]["speedup_vs_cublas_plus_act"] = b / ms_per_step if b else None
+            gb = gpu_baselines(x, w, N_OUT, max(5, args.steps // 2), step)
+            b = gb.get("cublas_plus_compiled_act_ms") or gb.get("cublas_plus_eager_act_ms")
+            gb["speedup_vs_cublas_plus_act"] = b / gb["this_build_ms"] if b else None
+            gb["note"] = "round-robin timing, medians of 3 rounds; speedup uses this_build_ms"
+            line["gpu_baselines"] = gb
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = {k: v for k, v in cpu_reference_rate(12.0, os.cpu_count() or 1).items()
                                     if k in ("value", "unit", "cores", "kind", "sample")}
