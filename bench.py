@@ -42,7 +42,7 @@ M_TOTAL, K_DIM, N_OUT = 32768, 3072, 12288
 WORKLOAD = "c3_fused: matmul_fused_swiglu 32768x3072x12288 bf16, W=[W_up|W_gate] packed [3072,24576]"
 METRIC = "fused_swiglu_tflops"
 UNIT = "TFLOP/s"
-PUBLISHED_V4_TFLOPS = 1257.0   # reference README, 1x B200, same shape
+PUBLISHED_V4_TFLOPS = 1257.0   # the reference README's V4 figure (README.md:106): 1x B200, same shape
 # DRAM traffic of one full-size launch on one GPU: dram__bytes_read.sum + dram__bytes_write.sum
 # from a one-pass ncu capture of this workload (profiles/swiglu_kernel_fused_c3_full_dram_traffic.md).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.27e9
