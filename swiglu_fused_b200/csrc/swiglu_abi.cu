@@ -145,12 +145,14 @@ bool config_fields_ok(const sgl_config& c) {
          ((c.l2_hints >> 2) & 3) != 3 && ((c.l2_hints >> 4) & 3) != 3 && ((c.l2_hints >> 6) & 3) != 3;
 }
 
-// Built-in tile table (cta_group, block_k, stages (0 = deepest), group_m).
+// Built-in tile table (cta_group, block_k, stages (0 = deepest), group_m, max_ctas, l2_hints).
 const sgl_config kTable[] = {
     {2, 64, 0, 8, 0, 0, {0, 0}},  {2, 64, 0, 4, 0, 0, {0, 0}},  {2, 64, 0, 16, 0, 0, {0, 0}},
     {2, 64, 0, 1, 0, 0, {0, 0}},  {2, 64, 0, 32, 0, 0, {0, 0}}, {2, 128, 0, 8, 0, 0, {0, 0}},
     {2, 128, 0, 16, 0, 0, {0, 0}}, {1, 64, 0, 8, 0, 0, {0, 0}}, {1, 64, 0, 16, 0, 0, {0, 0}},
     {1, 64, 0, 1, 0, 0, {0, 0}},  {1, 128, 0, 8, 0, 0, {0, 0}},
+    // x loads evict-last + output stores evict-first (l2_hints = 2 | 1 << 4)
+    {2, 128, 0, 16, 0, 18, {0, 0}}, {2, 64, 0, 16, 0, 18, {0, 0}}, {2, 128, 0, 12, 0, 18, {0, 0}},
 };
 constexpr int kTableSize = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 

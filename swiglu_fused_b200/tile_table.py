@@ -87,7 +87,7 @@ def legal_configs(form: int, M: int, N: int, K: int) -> list[TileConfig]:
         rows = 128 * c.cta_group
         tiles_m = -(-M // rows)
         eff_group = min(c.group_m, tiles_m)
-        sig = (c.cta_group, c.block_k, c.stages, eff_group)
+        sig = (c.cta_group, c.block_k, c.stages, eff_group, c.l2_hints)
         if sig in seen:
             continue
         seen.add(sig)
