@@ -100,7 +100,6 @@ using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMa
 struct Variant {
   KernelFn fn;
   int out_cols;
-  int stage_bytes;
   int max_stages;
   int (*smem_bytes)(int);
 };
@@ -116,7 +115,6 @@ Variant make_variant() {
   Variant v;
   v.fn = sgl::swiglu_kernel<F, G, BK>;
   v.out_cols = T::kOutCols;
-  v.stage_bytes = T::kStageBytes;
   v.max_stages = T::max_stages();
   v.smem_bytes = smem_bytes_of<F, G, BK>;
   return v;
@@ -288,95 +286,109 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
   return SGL_OK;
 }
 
-int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtensorMap& tup,
-           const sgl::OutMaps& th, int n_dst, int reduce_rows, int out_f32, int b_kmajor,
-           int reduce_add, int splits, int k_per_split, int slot_rows, int first_dst,
-           int64_t M, int64_t N, int64_t K, int64_t col0, int64_t col1,
-           const sgl_config& cfg, DeviceInfo* info, void* stream) {
-  const int vi = form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
-  const Variant& v = variant(form, cfg.cta_group, cfg.block_k);
+// Everything one kernel launch needs besides the tile configuration.
+struct LaunchSpec {
+  int form = SGL_FORM_FUSED_SWIGLU;
+  const CUtensorMap* x = nullptr;    // A operand
+  const CUtensorMap* w = nullptr;    // B operand
+  const CUtensorMap* up = nullptr;   // silu_mul form only (any valid map otherwise)
+  const sgl::OutMaps* out = nullptr;
+  int64_t M = 0, N = 0, K = 0;
+  int64_t col0 = 0, col1 = 0;        // B column (or row) offsets: see KernelParams
+  int n_dst = 1;
+  int b_kmajor = 0;
+  int out_f32 = 0;
+  int reduce_rows = 0, reduce_add = 0, first_dst = 0;     // reduce-scatter epilogue
+  int splits = 1, k_per_split = 0, slot_rows = 0;         // split-K
+};
+
+// Clusters of this variant that can be resident at once (1 CTA or CTA pair per SM).
+int query_max_clusters(const Variant& v, int cta_group, int sm_count) {
+  int n = sm_count / cta_group;
+  if (cta_group == 2) {
+    cudaLaunchConfig_t qc = {};
+    qc.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2), 1, 1);
+    qc.blockDim = dim3(sgl::kNumThreads, 1, 1);
+    qc.dynamicSmemBytes = static_cast<size_t>(v.smem_bytes(v.max_stages));
+    cudaLaunchAttribute qa[1];
+    qa[0].id = cudaLaunchAttributeClusterDimension;
+    qa[0].val.clusterDim.x = 2;
+    qa[0].val.clusterDim.y = 1;
+    qa[0].val.clusterDim.z = 1;
+    qc.attrs = qa;
+    qc.numAttrs = 1;
+    int q = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&q, reinterpret_cast<const void*>(v.fn), &qc);
+    if (e == cudaSuccess && q > 0) {
+      if (q < n) n = q;
+    } else {
+      cudaGetLastError();   // keep the SM-count estimate
+    }
+  }
+  return n > 0 ? n : 1;
+}
+
+int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* stream) {
+  const int vi = s.form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
+  const Variant& v = variant(s.form, cfg.cta_group, cfg.block_k);
   const int smem = v.smem_bytes(cfg.stages);
   if (smem > info->max_smem_optin)
     return fail(SGL_ERR_BAD_CONFIG, "configuration needs %d bytes of shared memory, device has %d",
                 smem, info->max_smem_optin);
 
   const int rows_per_tile = sgl::kBlockM * cfg.cta_group;
-  const int64_t tiles_m = (M + rows_per_tile - 1) / rows_per_tile;
-  const int64_t tiles_n = (N + v.out_cols - 1) / v.out_cols;
-  if (tiles_m * tiles_n * splits > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
+  const int64_t tiles_m = (s.M + rows_per_tile - 1) / rows_per_tile;
+  const int64_t tiles_n = (s.N + v.out_cols - 1) / v.out_cols;
+  const int64_t units = tiles_m * tiles_n * s.splits;
+  if (units > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
 
   cudaError_t e;
   {
+    // First launch of this variant on this device: raise its dynamic shared-memory limit to
+    // the deepest ring and ask how many clusters fit.
     std::lock_guard<std::mutex> lock(g_dev_mutex);
-    if (info->smem_set[vi] < smem) {
+    const int smem_max = v.smem_bytes(v.max_stages);
+    if (info->smem_set[vi] < smem_max) {
       e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
       if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(max dynamic smem)");
-      info->smem_set[vi] = smem;
+      info->smem_set[vi] = smem_max;
     }
-    if (info->max_clusters[vi] == 0) {
-      int n = info->sm_count / cfg.cta_group;
-      if (cfg.cta_group == 2) {
-        cudaLaunchConfig_t qc = {};
-        qc.gridDim = dim3(static_cast<unsigned>(info->sm_count / 2 * 2), 1, 1);
-        qc.blockDim = dim3(sgl::kNumThreads, 1, 1);
-        qc.dynamicSmemBytes = static_cast<size_t>(v.smem_bytes(v.max_stages));
-        cudaLaunchAttribute qa[1];
-        qa[0].id = cudaLaunchAttributeClusterDimension;
-        qa[0].val.clusterDim.x = 2;
-        qa[0].val.clusterDim.y = 1;
-        qa[0].val.clusterDim.z = 1;
-        qc.attrs = qa;
-        qc.numAttrs = 1;
-        int q = 0;
-        // The attribute must cover the query's shared memory too.
-        cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
-                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             v.smem_bytes(v.max_stages));
-        if (info->smem_set[vi] < v.smem_bytes(v.max_stages))
-          info->smem_set[vi] = v.smem_bytes(v.max_stages);
-        e = cudaOccupancyMaxActiveClusters(&q, reinterpret_cast<const void*>(v.fn), &qc);
-        if (e == cudaSuccess && q > 0) {
-          if (q < n) n = q;
-        } else {
-          cudaGetLastError();
-        }
-      }
-      info->max_clusters[vi] = n > 0 ? n : 1;
-    }
+    if (info->max_clusters[vi] == 0)
+      info->max_clusters[vi] = query_max_clusters(v, cfg.cta_group, info->sm_count);
   }
 
   int64_t clusters = info->max_clusters[vi];
   if (cfg.max_ctas > 0 && cfg.max_ctas / cfg.cta_group < clusters)
     clusters = cfg.max_ctas / cfg.cta_group;
   if (clusters < 1) clusters = 1;
-  if (tiles_m * tiles_n * splits < clusters) clusters = tiles_m * tiles_n * splits;
+  if (units < clusters) clusters = units;
 
   sgl::KernelParams p;
-  p.M = static_cast<int>(M);
-  p.N = static_cast<int>(N);
-  p.K = static_cast<int>(K);
-  p.b_col0 = static_cast<int>(col0);
-  p.b_col1 = static_cast<int>(col1);
+  p.M = static_cast<int>(s.M);
+  p.N = static_cast<int>(s.N);
+  p.K = static_cast<int>(s.K);
+  p.b_col0 = static_cast<int>(s.col0);
+  p.b_col1 = static_cast<int>(s.col1);
   p.tiles_m = static_cast<int>(tiles_m);
   p.tiles_n = static_cast<int>(tiles_n);
   p.group_m = cfg.group_m;
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
-  p.n_dst = n_dst;
-  p.b_kmajor = b_kmajor;
-  p.reduce_add = reduce_add;
-  p.splits = splits;
-  p.k_per_split = k_per_split;
-  p.slot_rows = slot_rows;
+  p.n_dst = s.n_dst;
+  p.b_kmajor = s.b_kmajor;
+  p.reduce_rows = s.reduce_rows;
+  p.reduce_add = s.reduce_add;
+  p.out_f32 = s.out_f32;
+  p.splits = s.splits;
+  p.k_per_split = s.k_per_split;
+  p.slot_rows = s.slot_rows;
   p.m_shift = 0;
-  if (reduce_rows > 0 && first_dst > 0) {
+  if (s.reduce_rows > 0 && s.first_dst > 0) {
     // start at the first tile row owned by destination first_dst
-    p.m_shift = static_cast<int>((static_cast<int64_t>(first_dst) * reduce_rows / rows_per_tile) %
-                                 tiles_m);
+    p.m_shift = static_cast<int>(
+        (static_cast<int64_t>(s.first_dst) * s.reduce_rows / rows_per_tile) % tiles_m);
   }
-  p.reduce_rows = reduce_rows;
-  p.out_f32 = out_f32;
   p.wait_limit_ns = g_wait_limit_ns.load();
 
   cudaLaunchConfig_t lc = {};
@@ -391,7 +403,7 @@ int launch(int form, const CUtensorMap& tx, const CUtensorMap& tw, const CUtenso
   attrs[0].val.clusterDim.z = 1;
   lc.attrs = attrs;
   lc.numAttrs = 1;
-  e = cudaLaunchKernelEx(&lc, v.fn, tx, tw, tup, th, p);
+  e = cudaLaunchKernelEx(&lc, v.fn, *s.x, *s.w, *s.up, *s.out, p);
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
   g_launches.fetch_add(1);
   return SGL_OK;
@@ -446,7 +458,16 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
       (rc = make_map(&tup, up, M, N, ldup, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, "up")) ||
       (rc = make_map(&th.m[0], h, M, N, ldh, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "h")))
     return rc;
-  return launch(SGL_FORM_SILU_MUL, tx, tw, tup, th, 1, 0, 0, 0, 0, 1, 0, 0, 0, M, N, K, 0, 0, c, info, stream);
+  LaunchSpec spec;
+  spec.form = SGL_FORM_SILU_MUL;
+  spec.x = &tx;
+  spec.w = &tw;
+  spec.up = &tup;
+  spec.out = &th;
+  spec.M = M;
+  spec.N = N;
+  spec.K = K;
+  return launch(spec, c, info, stream);
 }
 
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
@@ -512,8 +533,20 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
       return rc;
     n_dsts = 3;
   }
-  return launch(form, tx, tw, th.m[0], th, n_dsts, 0, 0, w_is_nk, 0, 1, 0, 0, 0, M, N, K, up_col0, gate_col0,
-                c, info, stream);
+  LaunchSpec spec;
+  spec.form = form;
+  spec.x = &tx;
+  spec.w = &tw;
+  spec.up = &th.m[0];
+  spec.out = &th;
+  spec.M = M;
+  spec.N = N;
+  spec.K = K;
+  spec.col0 = up_col0;
+  spec.col1 = gate_col0;
+  spec.n_dst = n_dsts;
+  spec.b_kmajor = w_is_nk;
+  return launch(spec, c, info, stream);
 }
 
 int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
@@ -619,9 +652,20 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
       (rc = make_map(&tc.m[0], scratch, static_cast<int64_t>(plan.splits) * plan.slot_rows, N, N,
                      32, 32, CU_TENSOR_MAP_L2_PROMOTION_NONE, "scratch", true)))
     return rc;
-  if ((rc = launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, 1, 0, 1, 0, 0, plan.splits,
-                   plan.k_per_split, plan.slot_rows, 0, M, N, K, 0, 0, cf, info, stream)))
-    return rc;
+  LaunchSpec spec;
+  spec.form = SGL_FORM_MATMUL;
+  spec.x = &ta;
+  spec.w = &tb;
+  spec.up = &tc.m[0];
+  spec.out = &tc;
+  spec.M = M;
+  spec.N = N;
+  spec.K = K;
+  spec.out_f32 = 1;
+  spec.splits = plan.splits;
+  spec.k_per_split = plan.k_per_split;
+  spec.slot_rows = plan.slot_rows;
+  if ((rc = launch(spec, cf, info, stream))) return rc;
   const int64_t vecs = M * (N / 8);
   int64_t blocks = (vecs + 255) / 256;
   const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
@@ -812,8 +856,21 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
                        CU_TENSOR_MAP_L2_PROMOTION_NONE, "c", f32)))
       return rc;
   }
-  return launch(SGL_FORM_MATMUL, ta, tb, tc.m[0], tc, n_dsts, static_cast<int>(reduce_rows),
-                f32 ? 1 : 0, 0, accumulate, 1, 0, 0, first_dst, M, N, K, 0, 0, c, info, stream);
+  LaunchSpec spec;
+  spec.form = SGL_FORM_MATMUL;
+  spec.x = &ta;
+  spec.w = &tb;
+  spec.up = &tc.m[0];
+  spec.out = &tc;
+  spec.M = M;
+  spec.N = N;
+  spec.K = K;
+  spec.n_dst = n_dsts;
+  spec.out_f32 = f32 ? 1 : 0;
+  spec.reduce_rows = static_cast<int>(reduce_rows);
+  spec.reduce_add = accumulate;
+  spec.first_dst = first_dst;
+  return launch(spec, c, info, stream);
 }
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
