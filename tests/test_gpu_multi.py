@@ -113,3 +113,30 @@ def test_sharded_launchers_on_gpus(M, K, N):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert flags == [1, 1, 1], flags
+
+
+def test_two_devices_from_one_process():
+    """One process driving two GPUs: per-device kernel attributes, status words and tensor
+    maps must not leak from one device to the other."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    import swiglu_oracle as orc
+    from swiglu_fused_b200 import _lib, matmul_fused_swiglu, matmul_silu_mul
+    from swiglu_fused_b200.workloads import make_inputs
+
+    inp = make_inputs(640, 256, 384, form="fused_swiglu", seed=33)
+    ref32 = orc.fused_swiglu_f32(inp["x"], inp["w"])
+    outs = []
+    for d in (1, 0, 1):                      # device 1 first: nothing was set up on it yet
+        dev = torch.device("cuda", d)
+        h = matmul_fused_swiglu(inp["x"].to(dev), inp["w"].to(dev))
+        with torch.cuda.device(dev):
+            torch.cuda.synchronize()
+            _lib.device_status()
+        assert h.device == dev
+        assert orc.compare(h.cpu(), ref32.to(torch.bfloat16), ref32).ok
+        outs.append(h.cpu())
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+    assert torch.equal(outs[0].view(torch.int16), outs[2].view(torch.int16))
+    with pytest.raises(ValueError):          # operands on different devices are rejected
+        matmul_fused_swiglu(inp["x"].to("cuda:0"), inp["w"].to("cuda:1"))
