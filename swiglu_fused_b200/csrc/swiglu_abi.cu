@@ -67,12 +67,45 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// Rank-2 bf16 map over a row-major [rows, cols] tensor with row pitch `ld`
+// A tensor map is a pure function of these parameters, so encoded maps are kept in a small
+// per-thread cache (the reference caches its maps too, keyed by pointers only:
+// swiglu/matmul_silu_mul.py:62-75).  Saves the driver call on repeated launches over the
+// same buffers, which is what a decode loop or a CUDA-graph-free serving step does.
+struct MapKey {
+  const void* base;
+  int64_t rows, cols, ld;
+  int32_t box_rows, box_cols, promo, swizzle, f32;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld &&
+           box_rows == o.box_rows && box_cols == o.box_cols && promo == o.promo &&
+           swizzle == o.swizzle && f32 == o.f32;
+  }
+};
+struct MapCacheEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapCacheSize = 64;   // direct mapped
+
+// Rank-2 bf16 (or fp32) map over a row-major [rows, cols] tensor with row pitch `ld`
 // elements; box = box_cols (one swizzle row: <= 128 bytes, or <= 64 with the 64B swizzle)
 // x box_rows.
 int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int64_t ld,
              int box_rows, int box_cols, CUtensorMapL2promotion promo, const char* name,
              bool f32 = false, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  thread_local MapCacheEntry cache[kMapCacheSize] = {};
+  const MapKey key{base, rows, cols, ld, box_rows, box_cols, static_cast<int32_t>(promo),
+                   static_cast<int32_t>(swizzle), f32 ? 1 : 0};
+  uint64_t h = reinterpret_cast<uintptr_t>(base) >> 4;
+  h ^= static_cast<uint64_t>(rows) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(cols) * 0xC2B2AE3D27D4EB4Full;
+  h ^= static_cast<uint64_t>(box_rows * 131 + box_cols * 7 + static_cast<int>(swizzle));
+  MapCacheEntry& e = cache[(h ^ (h >> 29)) % kMapCacheSize];
+  if (e.valid && e.key == key) {
+    *out = e.map;
+    return SGL_OK;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(SGL_ERR_NO_DRIVER, "cuTensorMapEncodeTiled is not available");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
@@ -80,8 +113,8 @@ int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int
   cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(out, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                  const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
+                  const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     return fail(SGL_ERR_TENSOR_MAP,
@@ -89,6 +122,9 @@ int make_map(CUtensorMap* out, const void* base, int64_t rows, int64_t cols, int
                 name, static_cast<int>(r), static_cast<long long>(rows),
                 static_cast<long long>(cols), static_cast<long long>(ld));
   }
+  e.key = key;
+  e.map = *out;
+  e.valid = true;
   return SGL_OK;
 }
 
