@@ -115,6 +115,12 @@ def load() -> C.CDLL:
         if _lib is not None:
             return _lib
         path = lib_path()
+        if not os.path.exists(path) and path == _build.LIB_PATH:
+            # A fresh checkout has sources only: compile once if a compiler is at hand.
+            try:
+                _build.build_library()
+            except RuntimeError:
+                pass
         if not os.path.exists(path):
             raise RuntimeError(
                 f"{path} is missing: build it with `python -m swiglu_fused_b200.build` "
