@@ -73,3 +73,24 @@ def test_candidate_configs_drop_pairs_for_a_single_row_tile():
     assert small and all(c.cta_group == 1 for c in small)
     big = tile_table.legal_configs(_lib.FORM_FUSED_SWIGLU, 32768, 12288, 3072)
     assert any(c.cta_group == 2 for c in big) and any(c.cta_group == 1 for c in big)
+
+
+def test_shipped_tile_table_entries_are_valid_configurations():
+    import json
+    import os
+
+    path = tile_table.TABLE_PATH
+    assert os.path.exists(path)
+    raw = json.load(open(path))
+    names = {v: k for k, v in tile_table.FORM_NAMES.items()}
+    assert raw["entries"], "the shipped table should carry the tuned benchmark shapes"
+    for key, v in raw["entries"].items():
+        form_name, shape = key.split(":")
+        M, N, K = (int(t) for t in shape.split("x"))
+        form = names[form_name]
+        cfg = _lib.TileConfig(v["cta_group"], v["block_k"], v["stages"], v["group_m"], 0,
+                              v.get("l2_hints", 0))
+        assert 0 < _lib.config_smem_bytes(form, cfg) <= 227 * 1024, key
+        assert M >= 1 and N % 8 == 0 and K % 8 == 0
+    # the headline shape is tuned
+    assert tile_table.lookup(_lib.FORM_FUSED_SWIGLU, 32768, 12288, 3072) is not None
