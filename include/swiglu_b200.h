@@ -151,6 +151,20 @@ int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream);
 
 /*
+ * sgl_matmul_bf16 with either operand stored transposed, read in place (no transpose copy):
+ *   a_transposed != 0: a is stored [K, M] (row pitch lda >= M, M a multiple of 8);
+ *   b_transposed != 0: b is stored [N, K] (row pitch ldb >= K).
+ * These are the two GEMMs of the backward pass over the packed weight W[K, 2N]:
+ *   grad_x[M, K]  = grad_preact[M, 2N] @ W^T   -> b = W,  b_transposed = 1
+ *   grad_W[K, 2N] = x^T @ grad_preact          -> a = x,  a_transposed = 1
+ * (the reference issues them through cuBLAS on two streams,
+ * _packed_grad_input_weight, swiglu/triton/impls.py:100-124).
+ */
+int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, int a_transposed,
+                       int b_transposed, const sgl_config* cfg, void* stream);
+
+/*
  * Split-K form of sgl_matmul_bf16 for short, deep problems (few output tiles, large K - the
  * down projection at decode batch sizes): K is cut into `splits` ranges (0 = choose), each
  * range's partial tile is written in fp32 to its slot of `scratch`, and a second kernel adds

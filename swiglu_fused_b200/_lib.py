@@ -31,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "sgl_swiglu_grad_preact",
     "sgl_matmul_fused_swiglu_multi_dst",
     "sgl_matmul_bf16",
+    "sgl_matmul_bf16_ex",
     "sgl_matmul_bf16_splitk_scratch_bytes",
     "sgl_matmul_bf16_splitk",
     "sgl_matmul_bf16_splitk_static",
@@ -147,6 +148,9 @@ def load() -> C.CDLL:
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_matmul_bf16.restype = ip
         lib.sgl_matmul_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_bf16_ex.restype = ip
+        lib.sgl_matmul_bf16_ex.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, ip, ip, cfgp,
+                                           vp]
         lib.sgl_matmul_bf16_splitk_scratch_bytes.restype = i64
         lib.sgl_matmul_bf16_splitk_scratch_bytes.argtypes = [i64, i64, i64, ip]
         lib.sgl_matmul_bf16_splitk.restype = ip

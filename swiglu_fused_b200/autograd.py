@@ -1,16 +1,17 @@
 """``torch.autograd`` wiring of the stage for training.
 
 Forward: the side-store kernel (h + factors in one launch).  Backward: the elementwise
-kernel of this library for ``grad_preact``, then two plain GEMMs
-(``grad_x = grad_preact @ W^T``, ``grad_W = x^T @ grad_preact``) through ``torch.matmul``
-(cuBLAS), which are library GEMMs and not part of the accelerated path.  The reference
-keeps its autograd Functions in its Triton module (``swiglu/triton/impls.py:2913-3369``).
+kernel for ``grad_preact``, then ``grad_x = grad_preact @ W^T`` and
+``grad_W = x^T @ grad_preact`` on the GEMM form of the same kernel, each reading its
+transposed operand in place.  The reference keeps its autograd Functions in its Triton
+module (``swiglu/triton/impls.py:2913-3369``) and runs the two GEMMs through cuBLAS
+(``:100-124``).
 """
 from __future__ import annotations
 
 import torch
 
-from .ops import matmul_fused_swiglu_save_factors, swiglu_grad_preact
+from .ops import matmul_bf16, matmul_fused_swiglu_save_factors, swiglu_grad_preact
 
 
 class FusedSwiGLUFunction(torch.autograd.Function):
@@ -24,8 +25,8 @@ class FusedSwiGLUFunction(torch.autograd.Function):
     def backward(ctx, grad_h: torch.Tensor):
         x, w, factors = ctx.saved_tensors
         grad_preact = swiglu_grad_preact(grad_h.contiguous(), factors, out=factors)  # in place
-        grad_x = grad_preact @ w.t() if ctx.needs_input_grad[0] else None
-        grad_w = x.t() @ grad_preact if ctx.needs_input_grad[1] else None
+        grad_x = matmul_bf16(grad_preact, w, transpose_b=True) if ctx.needs_input_grad[0] else None
+        grad_w = matmul_bf16(x, grad_preact, transpose_a=True) if ctx.needs_input_grad[1] else None
         return grad_x, grad_w
 
 

@@ -318,10 +318,12 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, uint32_t
 
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 D:
 // [4,6) D format (1 = f32), [7,10) A format (1 = bf16), [10,13) B format
-// (1 = bf16), [15] A major (0 = K), [16] B major (1 = MN), [17,23) N >> 3,
+// (1 = bf16), [15] A major (0 = K, 1 = MN), [16] B major (0 = K, 1 = MN), [17,23) N >> 3,
 // [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool b_mn_major) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_major,
+                                                       bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) |
+         ((b_mn_major ? 1u : 0u) << 16) |
          ((static_cast<uint32_t>(n >> 3) & 0x3Fu) << 17) |
          ((static_cast<uint32_t>(m >> 4) & 0x1Fu) << 24);
 }

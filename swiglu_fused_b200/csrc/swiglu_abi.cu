@@ -332,6 +332,7 @@ struct LaunchSpec {
   int64_t M = 0, N = 0, K = 0;
   int64_t col0 = 0, col1 = 0;        // B column (or row) offsets: see KernelParams
   int n_dst = 1;
+  int a_mnmajor = 0;
   int b_kmajor = 0;
   int out_f32 = 0;
   int reduce_rows = 0, reduce_add = 0, first_dst = 0;     // reduce-scatter epilogue
@@ -412,6 +413,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
   p.n_dst = s.n_dst;
+  p.a_mnmajor = s.a_mnmajor;
   p.b_kmajor = s.b_kmajor;
   p.reduce_rows = s.reduce_rows;
   p.reduce_add = s.reduce_add;
@@ -913,6 +915,50 @@ int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream) {
   void* dst[1] = {c};
   return matmul_impl(a, b, dst, 1, 0, 0, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
+}
+
+int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, int a_transposed,
+                       int b_transposed, const sgl_config* cfg, void* stream) {
+  int rc;
+  if ((rc = validate_ptr(a, "a")) || (rc = validate_ptr(b, "b")) || (rc = validate_ptr(c, "c")))
+    return rc;
+  if ((rc = validate_shape(M, N, K))) return rc;
+  if (a_transposed && M % 8 != 0)
+    return fail(SGL_ERR_BAD_SHAPE, "M=%lld must be a multiple of 8 when a is stored [K, M]",
+                static_cast<long long>(M));
+  if ((rc = validate_ld(lda, a_transposed ? M : K, "lda")) ||
+      (rc = validate_ld(ldb, b_transposed ? K : N, "ldb")) || (rc = validate_ld(ldc, N, "ldc")))
+    return rc;
+  sgl_config cf;
+  if ((rc = resolve_config(SGL_FORM_MATMUL, cfg, M, &cf))) return rc;
+  DeviceInfo* info = nullptr;
+  if ((rc = check_device(&info))) return rc;
+  CUtensorMap ta, tb;
+  sgl::OutMaps tc;
+  std::memset(&tc, 0, sizeof(tc));
+  if ((rc = a_transposed ? make_map(&ta, a, K, M, lda, cf.block_k, 64,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "a")
+                         : make_map(&ta, a, M, K, lda, sgl::kBlockM, 64,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "a")) ||
+      (rc = b_transposed ? make_map(&tb, b, N, K, ldb, 128, 64,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")
+                         : make_map(&tb, b, K, N, ldb, cf.block_k, 64,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")) ||
+      (rc = make_map(&tc.m[0], c, M, N, ldc, 32, 64, CU_TENSOR_MAP_L2_PROMOTION_NONE, "c")))
+    return rc;
+  LaunchSpec spec;
+  spec.form = SGL_FORM_MATMUL;
+  spec.x = &ta;
+  spec.w = &tb;
+  spec.up = &tc.m[0];
+  spec.out = &tc;
+  spec.M = M;
+  spec.N = N;
+  spec.K = K;
+  spec.a_mnmajor = a_transposed ? 1 : 0;
+  spec.b_kmajor = b_transposed ? 1 : 0;
+  return launch(spec, cf, info, stream);
 }
 
 int sgl_matmul_bf16_reduce_scatter(const void* a, const void* b, void* const* dsts, int n_dsts,

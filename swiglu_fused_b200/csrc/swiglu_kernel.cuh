@@ -110,6 +110,8 @@ struct KernelParams {
   int stages;           // shared-memory ring depth actually used
   int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
   int n_dst;            // destinations in OutMaps actually used (>= 1)
+  int a_mnmajor;        // A operand is stored transposed, [k, m] (the reduction index is the row):
+                        // x^T @ g products of the backward pass without a transpose copy
   int b_kmajor;         // weight operand is stored [n, k] (nn.Linear layout) instead of [k, n];
                         // b_col0 / b_col1 are then row offsets of that tensor
   int reduce_rows;      // FORM_GEMM: > 0 = add into the destination that owns the row block
@@ -364,10 +366,19 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           ptx::mbar_arrive_expect_tx_cluster(full, T::kStageBytes);
           const int k0 = k_base + kb * kBlockK;
           const uint32_t a_dst = sA + s * T::kAStageBytes;
+          if (p.a_mnmajor) {
+            // A stored [k, m]: two slabs of 64 m-columns x kBlockK k-rows, like the weight.
 #pragma unroll
-          for (int j = 0; j < kBlockK / 64; ++j) {
-            ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64, m0,
-                                             full, pol_x);
+            for (int j = 0; j < kBlockM / 64; ++j) {
+              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockK * 128), &tm_x, m0 + j * 64, k0,
+                                               full, pol_x);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kBlockK / 64; ++j) {
+              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64,
+                                               m0, full, pol_x);
+            }
           }
           const uint32_t b_dst = sB + s * T::kBStageBytes;
           if (p.b_kmajor) {
@@ -421,9 +432,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc =
-          ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols, /*b_mn_major=*/p.b_kmajor == 0);
+      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols,
+                                                  /*a_mn_major=*/p.a_mnmajor != 0,
+                                                  /*b_mn_major=*/p.b_kmajor == 0);
       const bool b_kmajor = p.b_kmajor != 0;
+      const bool a_mnmajor = p.a_mnmajor != 0;
       constexpr uint16_t mask = (kCtaGroup == 2) ? 0x3 : 0x1;
       int s = 0;
       uint32_t ph = 0;
@@ -461,8 +474,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           for (int kk = 0; kk < kBlockK / 16; ++kk) {
             // x tile: K-major, one 128-row x 64-col swizzled box per 64 k;
             // 16 k = 32 bytes inside the 128-byte swizzle row.
-            const uint64_t a_desc = ptx::smem_desc_sw128(
-                a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
+            // ([k, m] storage: M-major slabs [kBlockK rows][64 m], 16 k = 16 rows.)
+            const uint64_t a_desc =
+                a_mnmajor ? ptx::smem_desc_sw128(a_base + kk * 16 * 128, kBlockK * 128, 1024)
+                          : ptx::smem_desc_sw128(
+                                a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
             // weight tile, [k, n] storage: N-major slabs [kBlockK rows][64 cols], 16 k = 16
             // rows; [n, k] storage: K-major like x, rows = n, 16 k = 32 bytes.
             const uint64_t b_desc =

@@ -276,20 +276,24 @@ def swiglu_grad_preact(dy, factors, *, out=None, stream=None):
     return o
 
 
-def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None):
-    """``A @ B`` (bf16 in, fp32 accumulate, bf16 out) on the same TMA/tcgen05 pipeline:
-    the down projection ``y = h @ W_down`` that consumes the stage's output.
+def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None,
+                transpose_a: bool = False, transpose_b: bool = False):
+    """``op(A) @ op(B)`` (bf16 in, fp32 accumulate, bf16 out) on the same TMA/tcgen05
+    pipeline: the down projection ``y = h @ W_down`` that consumes the stage's output, and
+    with the transpose flags the two GEMMs of the backward pass.
 
-    A : [M, K] bf16, B : [K, N] bf16 (row-major), returns [M, N] bf16.
+    A : [M, K] bf16, or [K, M] with ``transpose_a`` (read in place, no transpose copy)
+    B : [K, N] bf16, or [N, K] with ``transpose_b``
+    returns [M, N] bf16.
     """
-    _check_matrix(A, "A", allow_empty_rows=True)
+    _check_matrix(A, "A", allow_empty_rows=not transpose_a)
     _check_matrix(B, "B")
-    M, K = A.shape
-    K2, N = B.shape
+    M, K = (A.shape[1], A.shape[0]) if transpose_a else A.shape
+    K2, N = (B.shape[1], B.shape[0]) if transpose_b else B.shape
     if K2 != K:
-        raise ValueError(f"K mismatch: A.K={K} vs B.K={K2}")
-    if K % 8 or N % 8:
-        raise ValueError(f"K={K} and N={N} must be multiples of 8")
+        raise ValueError(f"K mismatch: op(A).K={K} vs op(B).K={K2}")
+    if K % 8 or N % 8 or (transpose_a and M % 8):
+        raise ValueError(f"K={K}, N={N} (and M={M} when A is transposed) must be multiples of 8")
     dev = _same_device(("A", A), ("B", B))
     if M == 0:
         return out if out is not None else torch.empty((0, N), dtype=DTYPE, device=dev)
@@ -297,9 +301,10 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
     cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
     with torch.cuda.device(dev):
-        rc = _lib.load().sgl_matmul_bf16(
+        rc = _lib.load().sgl_matmul_bf16_ex(
             A.data_ptr(), B.data_ptr(), c.data_ptr(), M, N, K, _ld(A), _ld(B), _ld(c),
-            C.byref(cfg_c) if cfg_c is not None else None, _stream_handle(stream, dev))
+            int(transpose_a), int(transpose_b), C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
     _lib.check(rc)
     return c
 

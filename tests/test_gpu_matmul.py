@@ -47,6 +47,24 @@ def test_matmul_matches_fp32_reference(M, K, N):
         big.fill_(float("nan"))
 
 
+@pytest.mark.parametrize("M,K,N", [(256, 128, 256), (512, 1024, 768), (200, 136, 264),
+                                    (1024, 520, 384), (64, 2048, 128)])
+@pytest.mark.parametrize("ta,tb", [(False, True), (True, False), (True, True)])
+def test_transposed_operands_are_read_in_place(M, K, N, ta, tb):
+    a, b = problem(M, K, N, seed=M * 3 + K + N)
+    ref32 = orc.matmul_f32(a, b)
+    ad = (a.t().contiguous() if ta else a).to(DEV)        # stored [K, M] when ta
+    bd = (b.t().contiguous() if tb else b).to(DEV)        # stored [N, K] when tb
+    plain = matmul_bf16(a.to(DEV), b.to(DEV))
+    for cg, bk in VARIANTS:
+        got = matmul_bf16(ad, bd, transpose_a=ta, transpose_b=tb, config=TileConfig(cg, bk, 0, 8))
+        rep = orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32)
+        assert rep.ok, f"{(M, K, N)} ta={ta} tb={tb} cg={cg} bk={bk}: {rep}"
+    # same products, same accumulation order: identical to the untransposed call
+    assert torch.equal(matmul_bf16(ad, bd, transpose_a=ta, transpose_b=tb).view(torch.int16),
+                       plain.view(torch.int16))
+
+
 def test_matmul_equals_cublas_on_exact_data():
     # small integers: every product and partial sum is exact, so any correct GEMM agrees bit for bit
     g = torch.Generator().manual_seed(1)
