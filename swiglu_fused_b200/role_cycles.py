@@ -1,0 +1,110 @@
+"""Cycle accounting of the kernel's roles (developer tool).
+
+    python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|silu_mul] [--rows M]
+                                            [--block-k 64|128] [--group-m G]
+
+Builds a second copy of the library with ``-DSGL_PROFILE`` (``libswiglu_b200_prof.so``, next to
+the normal one), in which every role of ``swiglu_kernel`` adds up, per CTA, the SM cycles it
+spends waiting: the MMA issuer for a free accumulator and for operands, the TMA producer for a
+free ring slot, the epilogue for an accumulator and for ``up``.  Prints the averages as a share
+of the MMA loop, the cycles per 64-wide k-block against the 512-cycle tensor-core ideal, and the
+spread between the fastest and the slowest CTA pair (what a dynamic tile scheduler could gain).
+The normal library carries none of this code.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import os
+import subprocess
+
+from . import build as _build
+
+PROF_LIB = os.path.join(_build.PKG_DIR, "libswiglu_b200_prof.so")
+
+
+def build_profile_library() -> str:
+    srcs = _build.SOURCES + _build.HEADERS
+    if os.path.exists(PROF_LIB) and all(os.path.getmtime(p) <= os.path.getmtime(PROF_LIB)
+                                        for p in srcs if os.path.exists(p)):
+        return PROF_LIB
+    cmd = [_build.find_nvcc(), *_build.NVCC_FLAGS, "-DSGL_PROFILE", "-o", PROF_LIB,
+           *_build.SOURCES]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{proc.stderr}")
+    return PROF_LIB
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--form", choices=("fused_swiglu", "silu_mul"), default="fused_swiglu")
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--n", type=int, default=12288)
+    ap.add_argument("--block-k", type=int, default=0, help="0 = the default configuration")
+    ap.add_argument("--group-m", type=int, default=0)
+    args = ap.parse_args()
+
+    os.environ["SWIGLU_B200_LIB"] = build_profile_library()
+    import numpy as np
+    import torch
+
+    from . import _lib
+    from .ops import matmul_fused_swiglu, matmul_silu_mul
+
+    dev = torch.device("cuda:0")
+    M, K, N = args.rows, args.k, args.n
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
+    w = torch.empty((K, 2 * N), device=dev, dtype=torch.bfloat16).normal_(0, K ** -0.5, generator=g)
+    out = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+    form = _lib.FORM_FUSED_SWIGLU if args.form == "fused_swiglu" else _lib.FORM_SILU_MUL
+    cfg = _lib.default_config(form, M, N, K)
+    if args.block_k or args.group_m:
+        cfg = _lib.TileConfig(cfg.cta_group, args.block_k or cfg.block_k, 0,
+                              args.group_m or cfg.group_m)
+    if args.form == "fused_swiglu":
+        def run():
+            matmul_fused_swiglu(x, w, out=out, config=cfg)
+    else:
+        w_gate = w[:, N:].contiguous()
+        up = x @ w[:, :N].contiguous()
+
+        def run():
+            matmul_silu_mul(x, w_gate, up, out=out, config=cfg)
+
+    lib = _lib.load()
+    lib.sgl_debug_profile.restype = C.c_int
+    lib.sgl_debug_profile.argtypes = [C.POINTER(C.c_ulonglong)]
+    for _ in range(20):
+        run()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    run()
+    t1.record()
+    torch.cuda.synchronize()
+    buf = (C.c_ulonglong * (512 * 8))()
+    _lib.check(lib.sgl_debug_profile(buf))
+    n_ctas = min(512, _lib.query(_lib.QUERY_SM_COUNT))
+    p = np.frombuffer(buf, dtype=np.uint64).reshape(512, 8)[:n_ctas].astype(np.float64)
+    lead = p[0::cfg.cta_group]              # the MMA issuer runs in the leader CTA of a pair
+    loop = lead[:, 2]
+    tiles = np.maximum(lead[:, 7], 1)
+    kblocks = tiles * (-(-K // 64))
+    print(f"{args.form} {M}x{K}x{N} {cfg}: {t0.elapsed_time(t1):.3f} ms")
+    print(f"  MMA loop {loop.mean():.0f} clk per CTA; {(loop / kblocks).mean():.0f} clk per 64-k "
+          f"block (tensor-core ideal 512)")
+    print(f"  MMA issuer waits: free accumulator {100 * (lead[:, 0] / loop).mean():.1f} %, "
+          f"operands {100 * (lead[:, 1] / loop).mean():.1f} %")
+    print(f"  TMA producer waits for a ring slot {100 * p[:, 3].mean() / loop.mean():.1f} %")
+    print(f"  epilogue: waits for an accumulator {100 * p[:, 4].mean() / loop.mean():.1f} %, "
+          f"for up {100 * p[:, 5].mean() / loop.mean():.1f} %, busy "
+          f"{100 * p[:, 6].mean() / loop.mean():.1f} %")
+    print(f"  load balance: slowest / mean CTA = {loop.max() / loop.mean():.4f}, "
+          f"tiles per CTA {int(tiles.min())}..{int(tiles.max())}")
+
+
+if __name__ == "__main__":
+    main()
