@@ -176,3 +176,22 @@ def test_query_without_device_reports_cuda_error_not_crash():
         with pytest.raises(_lib.SglError):
             _lib.query(_lib.QUERY_SM_COUNT)
     assert _lib.kernel_launches() >= 0
+
+
+def test_splitk_scratch_plan():
+    lib = _lib.load()
+    f = lib.sgl_matmul_bf16_splitk_scratch_bytes
+    # 8 ranges x 64 rows x 4096 columns x 4 bytes: exactly the built-in scratch size
+    assert f(64, 4096, 14336, 8) == 8 << 20
+    # rows are padded to whole 32-row store boxes
+    assert f(33, 4096, 14336, 8) == 8 * 64 * 4096 * 4
+    # K ranges are multiples of 128 and never empty: 1000 / 8 -> ranges of 128 -> 8 ranges
+    assert f(64, 256, 1000, 8) == 8 * 64 * 256 * 4
+    # more ranges than 128-wide pieces of K: clipped (K = 256 has only 2)
+    assert f(64, 256, 256, 8) == 2 * 64 * 256 * 4
+    # automatic choice: one tile of output, 14336 deep -> many ranges; many tiles -> one range
+    assert f(64, 256, 14336, 0) == 16 * 64 * 256 * 4
+    assert f(8192, 8192, 4096, 0) == 1 * 8192 * 8192 * 4
+    assert f(64, 4096, 14332, 8) == -2       # K not a multiple of 8
+    assert f(0, 4096, 14336, 8) == -2
+    assert f(64, 4096, 14336, 65) == -10     # too many ranges
