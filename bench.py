@@ -294,8 +294,7 @@ def run_ours(args) -> None:
     e2e = None
     if not args.no_e2e and args.form == "fused_swiglu":
         e2e_steps = max(2, min(args.steps, 8))
-        pipe = HostPipeline(rows.count, K_DIM, N_OUT, device=dev,
-                            blocks=max(1, min(16, rows.count // 2048)))
+        pipe = HostPipeline(rows.count, K_DIM, N_OUT, device=dev)
         x_host = torch.empty((rows.count, K_DIM), dtype=torch.bfloat16).pin_memory()
         w_host = torch.empty((K_DIM, 2 * N_OUT), dtype=torch.bfloat16).pin_memory()
         h_host = torch.empty((rows.count, N_OUT), dtype=torch.bfloat16).pin_memory()
@@ -319,9 +318,11 @@ def run_ours(args) -> None:
                "h2d_bytes_per_step": 2 * (x.numel() + w.numel()),
                "d2h_bytes_per_step": 2 * h.numel(), "ms_per_step": te.item() * 1e3,
                "steps": e2e_steps, "launches": e2e_launches, "matches_device_run": e2e_same,
-               "note": "per rank: pinned host x and W copied in, h copied out, every step; "
-                       "row blocks pipelined on 3 streams; timed on the host clock around "
-                       "the calls, max over ranks"}
+               "note": "per rank: pinned host x and W copied in, h copied out, every step, by one "
+                       "sgl_host_pipeline_run call (3 streams; the first rows are computed per "
+                       "weight column window so the copy out starts while W is still arriving); "
+                       "timed on the host clock around the calls, max over ranks"}
+        pipe.close()
         del pipe, x_host, w_host, h_host
 
     peaks = load_peaks()

@@ -303,6 +303,45 @@ int sgl_selftest_wait_timeout(uint64_t limit_ns, void* stream);
 /* Per-wait time limit in nanoseconds for kernels launched afterwards (default 2e9). */
 int sgl_set_wait_limit_ns(uint64_t ns);
 
+/*
+ * Host-buffer pipeline: the fused_swiglu or silu_mul operator for a caller whose x, weight (and
+ * up) and h live in HOST memory.  No counterpart in the reference, whose benchmarks create every
+ * tensor on the GPU (bench_fused.py:35-36, bench.py:35-37); this is the work a host-side caller
+ * has to do around the launch, overlapped: copies in, launches and copies out run on three
+ * streams in row blocks.  Because h is the largest tensor, the schedule starts its copy out as
+ * early as it can: the first `first_rows` rows are computed one weight column window at a time
+ * while the weight is still arriving (`windows` windows), the rest in blocks of `block_rows`
+ * rows over all columns.  0 for any of the three picks a default (3/16 of M, 1/16 of M, 8).
+ *
+ *   create   allocates the device buffers (x, weight, h, and up for silu_mul), three streams and
+ *            the events on the current device; `form` is SGL_FORM_FUSED_SWIGLU (weight [K, 2N],
+ *            up columns first) or SGL_FORM_SILU_MUL (weight [K, N], plus up [M, N]).
+ *   run      one pass; pitches in elements; up_host is ignored for fused_swiglu.  Returns after
+ *            h_host is complete (synchronous).  Host buffers should be page-locked, otherwise
+ *            the copies do not overlap.  copy_weight = 0 reuses the weight copied by an earlier
+ *            run.  Not re-entrant: one run at a time per pipeline.
+ *   query    bytes moved and kernels launched per run, device bytes held.
+ *   destroy  frees everything create made; NULL is accepted.
+ * These are the only functions of the library that allocate device memory or block the host.
+ */
+typedef struct sgl_host_pipeline sgl_host_pipeline;
+enum {
+  SGL_PIPE_H2D_BYTES = 0,           /* per run with copy_weight = 1 */
+  SGL_PIPE_H2D_BYTES_NO_WEIGHT = 1, /* per run with copy_weight = 0 */
+  SGL_PIPE_D2H_BYTES = 2,
+  SGL_PIPE_LAUNCHES = 3,            /* kernels per run with copy_weight = 1 */
+  SGL_PIPE_LAUNCHES_NO_WEIGHT = 4,
+  SGL_PIPE_DEVICE_BYTES = 5
+};
+int sgl_host_pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t first_rows,
+                             int64_t block_rows, int windows, const sgl_config* cfg,
+                             sgl_host_pipeline** out);
+int sgl_host_pipeline_run(sgl_host_pipeline* p, const void* x_host, int64_t ldx,
+                          const void* w_host, int64_t ldw, const void* up_host, int64_t ldup,
+                          void* h_host, int64_t ldh, int copy_weight);
+int sgl_host_pipeline_query(const sgl_host_pipeline* p, int what, int64_t* out);
+int sgl_host_pipeline_destroy(sgl_host_pipeline* p);
+
 /* Message for the last non-zero return on the calling thread ("" if none). */
 const char* sgl_last_error(void);
 

@@ -22,6 +22,13 @@ QUERY_MAX_SMEM_OPTIN = 1
 QUERY_COMPUTE_CAPABILITY = 2
 QUERY_KERNEL_LAUNCHES = 3
 
+PIPE_H2D_BYTES = 0
+PIPE_H2D_BYTES_NO_WEIGHT = 1
+PIPE_D2H_BYTES = 2
+PIPE_LAUNCHES = 3
+PIPE_LAUNCHES_NO_WEIGHT = 4
+PIPE_DEVICE_BYTES = 5
+
 # Every symbol include/swiglu_b200.h declares.
 EXPORTED_SYMBOLS = (
     "sgl_matmul_silu_mul",
@@ -47,6 +54,10 @@ EXPORTED_SYMBOLS = (
     "sgl_device_status",
     "sgl_selftest_wait_timeout",
     "sgl_set_wait_limit_ns",
+    "sgl_host_pipeline_create",
+    "sgl_host_pipeline_run",
+    "sgl_host_pipeline_query",
+    "sgl_host_pipeline_destroy",
     "sgl_last_error",
     "sgl_version",
 )
@@ -184,6 +195,15 @@ def load() -> C.CDLL:
         lib.sgl_selftest_wait_timeout.argtypes = [C.c_uint64, vp]
         lib.sgl_set_wait_limit_ns.restype = ip
         lib.sgl_set_wait_limit_ns.argtypes = [C.c_uint64]
+        lib.sgl_host_pipeline_create.restype = ip
+        lib.sgl_host_pipeline_create.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp,
+                                                 C.POINTER(vp)]
+        lib.sgl_host_pipeline_run.restype = ip
+        lib.sgl_host_pipeline_run.argtypes = [vp, vp, i64, vp, i64, vp, i64, vp, i64, ip]
+        lib.sgl_host_pipeline_query.restype = ip
+        lib.sgl_host_pipeline_query.argtypes = [vp, ip, C.POINTER(i64)]
+        lib.sgl_host_pipeline_destroy.restype = ip
+        lib.sgl_host_pipeline_destroy.argtypes = [vp]
         lib.sgl_last_error.restype = C.c_char_p
         lib.sgl_last_error.argtypes = []
         lib.sgl_version.restype = ip

@@ -5,7 +5,8 @@
 // (swiglu/_pycuda_loader.py:128-144; this library is built ahead of time).
 //
 // No function here allocates device memory or synchronises, except
-// sgl_device_status, which is a debugging aid and says so.
+// sgl_device_status, which is a debugging aid and says so, and the host-buffer
+// pipeline (swiglu_host_pipeline.cuh), whose job is to own device buffers.
 
 #include "../../include/swiglu_b200.h"
 
@@ -1120,3 +1121,5 @@ const char* sgl_last_error(void) { return t_last_error.c_str(); }
 int sgl_version(void) { return 100; }
 
 }  // extern "C"
+
+#include "swiglu_host_pipeline.cuh"

@@ -1,126 +1,109 @@
 """End-to-end path for callers whose tensors live in HOST memory.
 
-``HostPipeline.run(x_host, w_host, h_host)`` does what a caller of the operator
-with host buffers has to do - copy x and W in, run the fused kernel, copy h out -
-but in row blocks on three streams, so the host->device copy of block i+1, the
-kernel of block i and the device->host copy of block i-1 overlap.  Device
-buffers are allocated once, at construction; ``run`` allocates nothing.
+``HostPipeline.run(x_host, w_host, h_host)`` does what a caller of the operator with host
+buffers has to do - copy x and W in, run the fused kernel, copy h out - through the library's
+native pipeline (``sgl_host_pipeline_*``): copies in, launches and copies out overlap on three
+streams, and the first rows are computed one weight column window at a time so that the copy
+out of ``h`` (the longest leg) starts while the weight is still arriving.  Device buffers are
+allocated once, at construction; ``run`` allocates nothing and returns when ``h_host`` is
+complete.
 
 The reference has no such path (its benchmark creates every tensor on the GPU,
-``bench_fused.py:35-36``); this exists so the end-to-end cost, PCIe included, can
-be measured through the same public operator.
+``bench_fused.py:35-36``); this exists so the end-to-end cost, PCIe included, can be measured
+through the same public operator.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
-from .ops import matmul_fused_swiglu, matmul_silu_mul
+from . import _lib
 
 
-class HostPipeline:
-    """Fused form: ``h_host = silu(x_host @ W_gate) * (x_host @ W_up)``."""
+def _check_host(t: torch.Tensor, name: str, rows: int, cols: int) -> None:
+    if t.device.type != "cpu":
+        raise ValueError(f"{name} must be a host tensor, got {t.device}")
+    if t.dtype != torch.bfloat16:
+        raise ValueError(f"{name} must be bfloat16, got {t.dtype}")
+    if t.dim() != 2 or tuple(t.shape) != (rows, cols):
+        raise ValueError(f"{name} must be [{rows}, {cols}], got {tuple(t.shape)}")
+    if t.stride(1) != 1:
+        raise ValueError(f"{name} must have unit stride along its rows")
 
-    def __init__(self, M: int, K: int, N: int, *, device="cuda:0", blocks: int = 8,
-                 row_align: int = 256, config=None):
+
+class _NativePipeline:
+    form = _lib.FORM_FUSED_SWIGLU
+
+    def __init__(self, M: int, K: int, N: int, *, device="cuda:0", first_rows: int = 0,
+                 block_rows: int = 0, windows: int = 0, config=None):
         self.M, self.K, self.N = M, K, N
         self.device = torch.device(device)
-        self.config = config
-        rows = -(-M // blocks)
-        rows = max(row_align, -(-rows // row_align) * row_align)
-        self.bounds = [(r, min(M, r + rows)) for r in range(0, M, rows)]
+        self._lib = _lib.load()
+        self._handle = C.c_void_p()
+        cfg = C.byref(config.to_c()) if config is not None else None
         with torch.cuda.device(self.device):
-            self.x_d = torch.empty((M, K), dtype=torch.bfloat16, device=self.device)
-            self.w_d = torch.empty((K, 2 * N), dtype=torch.bfloat16, device=self.device)
-            self.h_d = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-            self.s_in = torch.cuda.Stream(self.device)
-            self.s_run = torch.cuda.Stream(self.device)
-            self.s_out = torch.cuda.Stream(self.device)
-            n = len(self.bounds)
-            self.ev_w = torch.cuda.Event()
-            self.ev_x = [torch.cuda.Event() for _ in range(n)]
-            self.ev_h = [torch.cuda.Event() for _ in range(n)]
-        self.h2d_bytes = 2 * (M * K + K * 2 * N)
-        self.d2h_bytes = 2 * M * N
-        self.launches_per_run = len(self.bounds)
+            _lib.check(self._lib.sgl_host_pipeline_create(
+                self.form, M, N, K, first_rows, block_rows, windows, cfg,
+                C.byref(self._handle)))
+        self.h2d_bytes = self._query(_lib.PIPE_H2D_BYTES)
+        self.h2d_bytes_no_weight = self._query(_lib.PIPE_H2D_BYTES_NO_WEIGHT)
+        self.d2h_bytes = self._query(_lib.PIPE_D2H_BYTES)
+        self.launches_per_run = self._query(_lib.PIPE_LAUNCHES)
+        self.launches_per_run_no_weight = self._query(_lib.PIPE_LAUNCHES_NO_WEIGHT)
+        self.device_bytes = self._query(_lib.PIPE_DEVICE_BYTES)
+
+    def _query(self, what: int) -> int:
+        out = C.c_int64()
+        _lib.check(self._lib.sgl_host_pipeline_query(self._handle, what, C.byref(out)))
+        return out.value
+
+    def close(self) -> None:
+        if self._handle:
+            self._lib.sgl_host_pipeline_destroy(self._handle)
+            self._handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _run(self, x_host, w_host, up_host, h_host, copy_weight: bool):
+        if not self._handle:
+            raise RuntimeError("pipeline is closed")
+        _check_host(x_host, "x_host", self.M, self.K)
+        _check_host(h_host, "h_host", self.M, self.N)
+        w_cols = 2 * self.N if self.form == _lib.FORM_FUSED_SWIGLU else self.N
+        if copy_weight:
+            _check_host(w_host, "w_host", self.K, w_cols)
+        if up_host is not None:
+            _check_host(up_host, "up_host", self.M, self.N)
+        _lib.check(self._lib.sgl_host_pipeline_run(
+            self._handle, x_host.data_ptr(), x_host.stride(0),
+            w_host.data_ptr() if copy_weight else None, w_host.stride(0) if copy_weight else 0,
+            up_host.data_ptr() if up_host is not None else None,
+            up_host.stride(0) if up_host is not None else 0,
+            h_host.data_ptr(), h_host.stride(0), 1 if copy_weight else 0))
+        return h_host
+
+
+class HostPipeline(_NativePipeline):
+    """Fused form: ``h_host = silu(x_host @ W_gate) * (x_host @ W_up)``, ``W = [W_up | W_gate]``."""
+
+    form = _lib.FORM_FUSED_SWIGLU
 
     def run(self, x_host: torch.Tensor, w_host: torch.Tensor, h_host: torch.Tensor,
             copy_weight: bool = True) -> torch.Tensor:
         """One pass.  Host tensors should be pinned so the copies are asynchronous.
         Returns ``h_host`` after the last device->host copy has completed."""
-        cur = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_run, self.s_out):
-            s.wait_stream(cur)
-        with torch.cuda.stream(self.s_in):
-            if copy_weight:
-                self.w_d.copy_(w_host, non_blocking=True)
-            self.ev_w.record(self.s_in)
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.x_d[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
-                self.ev_x[i].record(self.s_in)
-        with torch.cuda.stream(self.s_run):
-            self.s_run.wait_event(self.ev_w)
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.s_run.wait_event(self.ev_x[i])
-                matmul_fused_swiglu(self.x_d[r0:r1], self.w_d, out=self.h_d[r0:r1],
-                                    config=self.config)
-                self.ev_h[i].record(self.s_run)
-        with torch.cuda.stream(self.s_out):
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.s_out.wait_event(self.ev_h[i])
-                h_host[r0:r1].copy_(self.h_d[r0:r1], non_blocking=True)
-        self.s_out.synchronize()
-        return h_host
+        return self._run(x_host, w_host, None, h_host, copy_weight)
 
 
-class HostPipelineSiluMul:
-    """silu_mul form: ``h_host = silu(x_host @ W_gate) * up_host`` in row blocks."""
+class HostPipelineSiluMul(_NativePipeline):
+    """silu_mul form: ``h_host = silu(x_host @ W_gate) * up_host``."""
 
-    def __init__(self, M: int, K: int, N: int, *, device="cuda:0", blocks: int = 8,
-                 row_align: int = 256, config=None):
-        self.M, self.K, self.N = M, K, N
-        self.device = torch.device(device)
-        self.config = config
-        rows = -(-M // blocks)
-        rows = max(row_align, -(-rows // row_align) * row_align)
-        self.bounds = [(r, min(M, r + rows)) for r in range(0, M, rows)]
-        with torch.cuda.device(self.device):
-            self.x_d = torch.empty((M, K), dtype=torch.bfloat16, device=self.device)
-            self.w_d = torch.empty((K, N), dtype=torch.bfloat16, device=self.device)
-            self.up_d = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-            self.h_d = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-            self.s_in = torch.cuda.Stream(self.device)
-            self.s_run = torch.cuda.Stream(self.device)
-            self.s_out = torch.cuda.Stream(self.device)
-            n = len(self.bounds)
-            self.ev_w = torch.cuda.Event()
-            self.ev_x = [torch.cuda.Event() for _ in range(n)]
-            self.ev_h = [torch.cuda.Event() for _ in range(n)]
-        self.h2d_bytes = 2 * (M * K + K * N + M * N)
-        self.d2h_bytes = 2 * M * N
-        self.launches_per_run = len(self.bounds)
+    form = _lib.FORM_SILU_MUL
 
     def run(self, x_host, w_gate_host, up_host, h_host, copy_weight: bool = True):
-        cur = torch.cuda.current_stream(self.device)
-        for s in (self.s_in, self.s_run, self.s_out):
-            s.wait_stream(cur)
-        with torch.cuda.stream(self.s_in):
-            if copy_weight:
-                self.w_d.copy_(w_gate_host, non_blocking=True)
-            self.ev_w.record(self.s_in)
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.x_d[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
-                self.up_d[r0:r1].copy_(up_host[r0:r1], non_blocking=True)
-                self.ev_x[i].record(self.s_in)
-        with torch.cuda.stream(self.s_run):
-            self.s_run.wait_event(self.ev_w)
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.s_run.wait_event(self.ev_x[i])
-                matmul_silu_mul(self.x_d[r0:r1], self.w_d, self.up_d[r0:r1],
-                                out=self.h_d[r0:r1], config=self.config)
-                self.ev_h[i].record(self.s_run)
-        with torch.cuda.stream(self.s_out):
-            for i, (r0, r1) in enumerate(self.bounds):
-                self.s_out.wait_event(self.ev_h[i])
-                h_host[r0:r1].copy_(self.h_d[r0:r1], non_blocking=True)
-        self.s_out.synchronize()
-        return h_host
+        return self._run(x_host, w_gate_host, up_host, h_host, copy_weight)

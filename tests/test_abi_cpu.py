@@ -195,3 +195,25 @@ def test_splitk_scratch_plan():
     assert f(64, 4096, 14332, 8) == -2       # K not a multiple of 8
     assert f(0, 4096, 14336, 8) == -2
     assert f(64, 4096, 14336, 65) == -10     # too many ranges
+
+
+def test_host_pipeline_rejects_bad_arguments_before_touching_a_device():
+    import ctypes as C
+    lib = _lib.load()
+    handle = C.c_void_p()
+    create = lib.sgl_host_pipeline_create
+    assert create(_lib.FORM_MATMUL, 256, 256, 64, 0, 0, 0, None, C.byref(handle)) == -10
+    assert create(_lib.FORM_FUSED_SWIGLU, 256, 260, 64, 0, 0, 0, None, C.byref(handle)) == -2
+    assert create(_lib.FORM_FUSED_SWIGLU, 256, 256, 64, -1, 0, 0, None, C.byref(handle)) == -10
+    assert create(_lib.FORM_FUSED_SWIGLU, 256, 256, 64, 0, 0, 65, None, C.byref(handle)) == -10
+    assert create(_lib.FORM_FUSED_SWIGLU, 256, 256, 64, 0, 0, 0, None, None) == -1
+    assert not handle.value
+    out = C.c_int64()
+    assert lib.sgl_host_pipeline_query(None, _lib.PIPE_D2H_BYTES, C.byref(out)) == -1
+    assert lib.sgl_host_pipeline_run(None, None, 0, None, 0, None, 0, None, 0, 1) == -1
+    assert lib.sgl_host_pipeline_destroy(None) == 0
+    import torch
+    if not torch.cuda.is_available():
+        # no device: a CUDA error code and a message, not a crash
+        rc = create(_lib.FORM_FUSED_SWIGLU, 256, 256, 64, 0, 0, 0, None, C.byref(handle))
+        assert rc > 0 and lib.sgl_last_error()

@@ -1,0 +1,123 @@
+"""Host-buffer pipeline (``sgl_host_pipeline_*``): host tensors in, host tensor out, through the
+C ABI.  The result must be bit-identical to the device-resident operator on the same inputs
+(the pipeline only reorders the work into column windows and row blocks, and both of those are
+bit-exact re-tilings of the same per-element arithmetic), and within the stated tolerance of
+the fp32 oracle."""
+import pytest
+import torch
+
+import swiglu_oracle as orc
+from swiglu_fused_b200 import _lib, matmul_fused_swiglu, matmul_silu_mul
+from swiglu_fused_b200.host_pipeline import HostPipeline, HostPipelineSiluMul
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    _lib.device_status()
+
+
+def fused_problem(M, K, N, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    w = (torch.randn((K, 2 * N), generator=g) * K ** -0.5).to(torch.bfloat16)
+    return x, w
+
+
+def same_bits(a, b):
+    return torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+@pytest.mark.parametrize("M,K,N,kw", [
+    (4096, 512, 2048, {}),                                   # defaults: 8 windows of 256
+    (5000, 264, 1288, {}),                                   # ragged rows and last window
+    (3000, 128, 512, {"first_rows": 1000, "block_rows": 1024, "windows": 2}),
+    (300, 64, 136, {}),                                      # smaller than one block
+    (2048, 256, 1024, {"first_rows": 2048}),                 # phase 1 only
+    (2048, 256, 1024, {"windows": 1}),                       # whole weight, then rows
+])
+def test_fused_pipeline_matches_device_operator(M, K, N, kw):
+    x, w = fused_problem(M, K, N, seed=M + N)
+    want = matmul_fused_swiglu(x.to(DEV), w.to(DEV)).cpu()
+    rep = orc.compare(want, orc.fused_swiglu_f32(x, w).to(torch.bfloat16),
+                      orc.fused_swiglu_f32(x, w))
+    assert rep.ok, rep
+    pipe = HostPipeline(M, K, N, device=DEV, **kw)
+    xh, wh = x.pin_memory(), w.pin_memory()
+    hh = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    n0 = _lib.kernel_launches()
+    pipe.run(xh, wh, hh)
+    assert _lib.kernel_launches() - n0 == pipe.launches_per_run
+    assert same_bits(hh, want)
+    # second pass on the resident weight: row blocks only
+    hh.fill_(float("nan"))
+    n0 = _lib.kernel_launches()
+    pipe.run(xh, None, hh, copy_weight=False)
+    assert _lib.kernel_launches() - n0 == pipe.launches_per_run_no_weight
+    assert same_bits(hh, want)
+    assert pipe.h2d_bytes == 2 * (M * K + 2 * K * N)
+    assert pipe.h2d_bytes_no_weight == 2 * M * K
+    assert pipe.d2h_bytes == 2 * M * N
+    assert pipe.device_bytes == 2 * (M * K + 2 * K * N + M * N)
+    pipe.close()
+
+
+def test_fused_pipeline_pitched_and_pageable_host_buffers():
+    M, K, N = 1536, 136, 520
+    x, w = fused_problem(M, K, N, seed=3)
+    want = matmul_fused_swiglu(x.to(DEV), w.to(DEV)).cpu()
+    # rows wider than the data: the pitch is honoured on the way in and on the way out
+    xb = torch.zeros((M, K + 24), dtype=torch.bfloat16)
+    wb = torch.zeros((K, 2 * N + 8), dtype=torch.bfloat16)
+    hb = torch.full((M, N + 16), 7.0, dtype=torch.bfloat16)
+    xb[:, :K] = x
+    wb[:, :2 * N] = w
+    pipe = HostPipeline(M, K, N, device=DEV)
+    pipe.run(xb[:, :K], wb[:, :2 * N], hb[:, :N])          # pageable memory: slower, still right
+    assert same_bits(hb[:, :N].contiguous(), want)
+    assert (hb[:, N:] == 7.0).all(), "wrote beyond the N columns of a pitched host row"
+
+
+@pytest.mark.parametrize("M,K,N", [(4096, 256, 2048), (2500, 72, 776)])
+def test_silu_mul_pipeline_matches_device_operator(M, K, N):
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    wg = (torch.randn((K, N), generator=g) * K ** -0.5).to(torch.bfloat16)
+    up = torch.randn((M, N), generator=g).to(torch.bfloat16)
+    want = matmul_silu_mul(x.to(DEV), wg.to(DEV), up.to(DEV)).cpu()
+    ref32 = orc.silu_mul_f32(x, wg, up)
+    assert orc.compare(want, ref32.to(torch.bfloat16), ref32).ok
+    pipe = HostPipelineSiluMul(M, K, N, device=DEV)
+    hh = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    pipe.run(x.pin_memory(), wg.pin_memory(), up.pin_memory(), hh)
+    assert same_bits(hh, want)
+    hh.fill_(float("nan"))
+    pipe.run(x.pin_memory(), None, up.pin_memory(), hh, copy_weight=False)
+    assert same_bits(hh, want)
+    assert pipe.h2d_bytes == 2 * (M * K + K * N + M * N)
+
+
+def test_pipeline_argument_errors():
+    with pytest.raises(ValueError):
+        HostPipeline(0, 64, 64, device=DEV)
+    with pytest.raises(ValueError):
+        HostPipeline(256, 64, 68, device=DEV)               # N not a multiple of 8
+    with pytest.raises(ValueError):
+        HostPipeline(256, 64, 64, device=DEV, windows=65)
+    pipe = HostPipeline(256, 64, 64, device=DEV)
+    x = torch.zeros((256, 64), dtype=torch.bfloat16)
+    w = torch.zeros((64, 128), dtype=torch.bfloat16)
+    h = torch.zeros((256, 64), dtype=torch.bfloat16)
+    with pytest.raises(ValueError):
+        pipe.run(x.to(DEV), w, h)                           # device tensor where host is expected
+    with pytest.raises(ValueError):
+        pipe.run(x, w[:, :64], h)                           # wrong weight shape
+    with pytest.raises(ValueError):
+        pipe.run(x.float(), w, h)
+    pipe.close()
+    with pytest.raises(RuntimeError):
+        pipe.run(x, w, h)
