@@ -342,6 +342,41 @@ int sgl_host_pipeline_run(sgl_host_pipeline* p, const void* x_host, int64_t ldx,
 int sgl_host_pipeline_query(const sgl_host_pipeline* p, int what, int64_t* out);
 int sgl_host_pipeline_destroy(sgl_host_pipeline* p);
 
+/*
+ * Single-process multi-GPU launcher for the fused form: one host thread, up to 8 GPUs owned by
+ * the calling process.  The reference is single-GPU (one context, swiglu/_pycuda_loader.py:47-55);
+ * no counterpart there.  The partition is sgl_shard_range's (rows in multiples of 256, columns
+ * in multiples of 128), the same as the one-process-per-GPU launchers use.
+ *
+ *   create   devices[0..n) are CUDA device ordinals (a device may be listed twice); enables peer
+ *            access between them where the hardware allows, creates two events per device;
+ *            the caller's current device is restored.
+ *   fused_swiglu  x, w, h (and streams, or NULL for the null streams) are arrays of n per-device
+ *            pointers; M, N, K are the GLOBAL sizes; pitches in elements, common to all devices.
+ *       SGL_MGPU_M_SHARD         x[r]: rows of shard r, [rows_r, K]; w[r]: packed [K, 2N] replica;
+ *                                h[r]: [rows_r, N].  No traffic between devices.
+ *       SGL_MGPU_N_SHARD         x[r]: full [M, K] replica; w[r]: unsplit packed weight replica,
+ *                                column windows read in place; h[r]: local block [M, cols_r]
+ *                                (ldh >= cols_r).  No traffic between devices.
+ *       SGL_MGPU_N_SHARD_GATHER  as N_SHARD, but each h[d] is a full [M, N] buffer (ldh >= N) and
+ *                                device r's epilogue stores its columns into every h[d] (plain TMA
+ *                                stores through peer access, no multicast): all-gather fused into
+ *                                the kernel.  Before the launches every stream waits for an event
+ *                                on every other stream (all h free), and again after them (every
+ *                                stream then sees the whole h).  Needs peer access everywhere.
+ *            Enqueues only: no host wait, and no kernel waits on another kernel.
+ *   size     number of devices in the group (0 for NULL).
+ *   destroy  frees the events; peer access stays enabled.  NULL is accepted.
+ */
+typedef struct sgl_mgpu sgl_mgpu;
+enum { SGL_MGPU_M_SHARD = 0, SGL_MGPU_N_SHARD = 1, SGL_MGPU_N_SHARD_GATHER = 2 };
+int sgl_mgpu_create(int n, const int* devices, sgl_mgpu** out);
+int sgl_mgpu_fused_swiglu(sgl_mgpu* g, int mode, const void* const* x, const void* const* w,
+                          void* const* h, int64_t M, int64_t N, int64_t K, int64_t ldx,
+                          int64_t ldw, int64_t ldh, const sgl_config* cfg, void* const* streams);
+int sgl_mgpu_size(const sgl_mgpu* g);
+int sgl_mgpu_destroy(sgl_mgpu* g);
+
 /* Message for the last non-zero return on the calling thread ("" if none). */
 const char* sgl_last_error(void);
 

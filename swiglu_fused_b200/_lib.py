@@ -22,6 +22,10 @@ QUERY_MAX_SMEM_OPTIN = 1
 QUERY_COMPUTE_CAPABILITY = 2
 QUERY_KERNEL_LAUNCHES = 3
 
+MGPU_M_SHARD = 0
+MGPU_N_SHARD = 1
+MGPU_N_SHARD_GATHER = 2
+
 PIPE_H2D_BYTES = 0
 PIPE_H2D_BYTES_NO_WEIGHT = 1
 PIPE_D2H_BYTES = 2
@@ -58,6 +62,10 @@ EXPORTED_SYMBOLS = (
     "sgl_host_pipeline_run",
     "sgl_host_pipeline_query",
     "sgl_host_pipeline_destroy",
+    "sgl_mgpu_create",
+    "sgl_mgpu_fused_swiglu",
+    "sgl_mgpu_size",
+    "sgl_mgpu_destroy",
     "sgl_last_error",
     "sgl_version",
 )
@@ -204,6 +212,15 @@ def load() -> C.CDLL:
         lib.sgl_host_pipeline_query.argtypes = [vp, ip, C.POINTER(i64)]
         lib.sgl_host_pipeline_destroy.restype = ip
         lib.sgl_host_pipeline_destroy.argtypes = [vp]
+        lib.sgl_mgpu_create.restype = ip
+        lib.sgl_mgpu_create.argtypes = [ip, C.POINTER(ip), C.POINTER(vp)]
+        lib.sgl_mgpu_fused_swiglu.restype = ip
+        lib.sgl_mgpu_fused_swiglu.argtypes = [vp, ip, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                              i64, i64, i64, i64, i64, i64, cfgp, C.POINTER(vp)]
+        lib.sgl_mgpu_size.restype = ip
+        lib.sgl_mgpu_size.argtypes = [vp]
+        lib.sgl_mgpu_destroy.restype = ip
+        lib.sgl_mgpu_destroy.argtypes = [vp]
         lib.sgl_last_error.restype = C.c_char_p
         lib.sgl_last_error.argtypes = []
         lib.sgl_version.restype = ip

@@ -22,6 +22,7 @@ HEADERS = [
     os.path.join(CSRC_DIR, "swiglu_elementwise.cuh"),
     os.path.join(CSRC_DIR, "ptx_sm100.cuh"),
     os.path.join(CSRC_DIR, "swiglu_host_pipeline.cuh"),
+    os.path.join(CSRC_DIR, "swiglu_mgpu.cuh"),
     os.path.join(os.path.dirname(PKG_DIR), "include", "swiglu_b200.h"),
 ]
 

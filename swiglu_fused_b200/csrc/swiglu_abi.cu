@@ -1123,3 +1123,4 @@ int sgl_version(void) { return 100; }
 }  // extern "C"
 
 #include "swiglu_host_pipeline.cuh"
+#include "swiglu_mgpu.cuh"

@@ -217,3 +217,25 @@ def test_host_pipeline_rejects_bad_arguments_before_touching_a_device():
         # no device: a CUDA error code and a message, not a crash
         rc = create(_lib.FORM_FUSED_SWIGLU, 256, 256, 64, 0, 0, 0, None, C.byref(handle))
         assert rc > 0 and lib.sgl_last_error()
+
+
+def test_mgpu_rejects_bad_arguments_before_touching_a_device():
+    import ctypes as C
+    lib = _lib.load()
+    handle = C.c_void_p()
+    one = (C.c_int * 1)(0)
+    nine = (C.c_int * 9)(*([0] * 9))
+    assert lib.sgl_mgpu_create(1, one, None) == -1
+    assert lib.sgl_mgpu_create(1, None, C.byref(handle)) == -1
+    assert lib.sgl_mgpu_create(0, one, C.byref(handle)) == -10
+    assert lib.sgl_mgpu_create(9, nine, C.byref(handle)) == -10
+    assert not handle.value
+    assert lib.sgl_mgpu_size(None) == 0
+    assert lib.sgl_mgpu_destroy(None) == 0
+    assert lib.sgl_mgpu_fused_swiglu(None, 0, None, None, None, 256, 256, 64, 64, 512, 256, None,
+                                     None) == -1
+    import torch
+    if not torch.cuda.is_available():
+        rc = lib.sgl_mgpu_create(1, one, C.byref(handle))
+        assert rc != 0 and lib.sgl_last_error()
+        assert not handle.value
