@@ -107,3 +107,68 @@ class HostPipelineSiluMul(_NativePipeline):
 
     def run(self, x_host, w_gate_host, up_host, h_host, copy_weight: bool = True):
         return self._run(x_host, w_gate_host, up_host, h_host, copy_weight)
+
+
+def _main() -> None:
+    """``python -m swiglu_fused_b200.host_pipeline``: time the pipeline on the headline shape
+    (or ``--rows/--k/--n``) for one or several schedules, next to the raw copy rates of the
+    host link.  Prints one line per schedule; every result is checked, bit for bit, against the
+    device-resident operator."""
+    import argparse
+    import time
+
+    from .ops import matmul_fused_swiglu
+
+    ap = argparse.ArgumentParser(description="time the host-buffer pipeline")
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--n", type=int, default=12288)
+    ap.add_argument("--schedule", action="append", default=None, metavar="FIRST,BLOCK,WINDOWS",
+                    help="first_rows,block_rows,windows (0 = default); may be repeated")
+    ap.add_argument("--reps", type=int, default=6)
+    args = ap.parse_args()
+    M, K, N = args.rows, args.k, args.n
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
+    w = torch.empty((K, 2 * N), device=dev, dtype=torch.bfloat16).normal_(0, K ** -0.5, generator=g)
+    want = matmul_fused_swiglu(x, w)
+    xh = torch.empty((M, K), dtype=torch.bfloat16).pin_memory()
+    wh = torch.empty((K, 2 * N), dtype=torch.bfloat16).pin_memory()
+    hh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    xh.copy_(x)
+    wh.copy_(w)
+    for name, dst, src in (("host->device (x)", x, xh), ("device->host (h)", hh, want)):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(3):
+            dst.copy_(src, non_blocking=True)
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / 3
+        print(f"{name}: {src.numel() * 2 / dt / 1e9:.1f} GB/s ({dt * 1e3:.2f} ms)")
+    schedules = [tuple(int(v) for v in s.split(",")) for s in (args.schedule or ["0,0,0"])]
+    for first, block, windows in schedules:
+        pipe = HostPipeline(M, K, N, device=dev, first_rows=first, block_rows=block,
+                            windows=windows)
+        for _ in range(2):
+            pipe.run(xh, wh, hh)
+        same = torch.equal(hh.view(torch.int16), want.cpu().view(torch.int16))
+        with_w, without_w = [], []
+        for _ in range(args.reps):
+            t0 = time.perf_counter()
+            pipe.run(xh, wh, hh)
+            with_w.append((time.perf_counter() - t0) * 1e3)
+        for _ in range(args.reps):
+            t0 = time.perf_counter()
+            pipe.run(xh, None, hh, copy_weight=False)
+            without_w.append((time.perf_counter() - t0) * 1e3)
+        print(f"first_rows={first} block_rows={block} windows={windows}: "
+              f"{sorted(with_w)[len(with_w) // 2]:.2f} ms per run "
+              f"({pipe.launches_per_run} launches), weight resident "
+              f"{sorted(without_w)[len(without_w) // 2]:.2f} ms, "
+              f"bit-identical to the device run: {same}")
+        pipe.close()
+
+
+if __name__ == "__main__":
+    _main()
