@@ -239,3 +239,43 @@ def test_mgpu_rejects_bad_arguments_before_touching_a_device():
         rc = lib.sgl_mgpu_create(1, one, C.byref(handle))
         assert rc != 0 and lib.sgl_last_error()
         assert not handle.value
+
+
+def test_header_is_plain_c_and_a_c_program_links_against_the_library(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 (no C++, no torch types) and a C
+    program must link against the library and call it."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    lib_file = _lib.lib_path()
+    src = tmp_path / "use_abi.c"
+    src.write_text(r'''
+#include <stdio.h>
+#include <string.h>
+#include "swiglu_b200.h"
+int main(void) {
+  sgl_config cfg;
+  int64_t b = 0, c = 0, tm = 0, tn = 0;
+  if (sgl_version() < 100) return 1;
+  if (sgl_config_count(SGL_FORM_FUSED_SWIGLU) < 1) return 2;
+  if (sgl_config_default(SGL_FORM_FUSED_SWIGLU, 32768, 12288, 3072, &cfg) != SGL_OK) return 3;
+  if (sgl_config_smem_bytes(SGL_FORM_FUSED_SWIGLU, &cfg) <= 0) return 4;
+  if (sgl_shard_range(32768, 256, 8, 3, &b, &c) != SGL_OK || b != 3 * 4096 || c != 4096) return 5;
+  if (sgl_tile_coord(0, 4, 4, 2, &tm, &tn) != SGL_OK) return 6;
+  if (sgl_matmul_fused_swiglu(NULL, NULL, NULL, 1, 8, 8, 8, 16, 8, 0, 8, NULL, NULL)
+      != SGL_ERR_NULL_POINTER) return 7;
+  if (strlen(sgl_last_error()) == 0) return 8;
+  printf("cta_group=%d block_k=%d\n", cfg.cta_group, cfg.block_k);
+  return 0;
+}
+''')
+    exe = tmp_path / "use_abi"
+    inc = os.path.dirname(HEADER)
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", f"-I{inc}",
+                    str(src), "-o", str(exe), lib_file,
+                    f"-Wl,-rpath,{os.path.dirname(lib_file)}"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
+    assert "cta_group=2 block_k=128" in out.stdout
