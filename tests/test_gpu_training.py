@@ -79,3 +79,44 @@ def test_autograd_matches_fp32_autograd():
         err = (got.float() - want).abs().max().item()
         scale = want.abs().max().item()
         assert err <= 2e-2 * scale, f"{name}: max err {err} vs scale {scale}"
+
+
+def test_module_forward_and_training_step():
+    """``PackedSwiGLULinear`` (reference: ``swiglu/triton/impls.py:3372-3596``): loads an
+    ``nn.Linear`` checkpoint, the inference forward equals the operator bit for bit, and one
+    SGD step moves the parameters as the fp32 torch model does."""
+    from swiglu_fused_b200.module import PackedSwiGLULinear
+
+    torch.manual_seed(7)
+    B, S, K, N = 4, 96, 256, 384
+    lin = torch.nn.Linear(K, 2 * N, bias=False, dtype=torch.bfloat16)
+    mod = PackedSwiGLULinear.from_linear(lin).to(DEV)
+    x = torch.randn((B, S, K)).to(torch.bfloat16).to(DEV)
+    with torch.no_grad():
+        y = mod(x)
+    assert tuple(y.shape) == (B, S, N)
+    want = matmul_fused_swiglu(x.reshape(-1, K), mod.weight.detach())
+    assert torch.equal(y.reshape(-1, N).view(torch.int16), want.view(torch.int16))
+    ref32 = orc.fused_swiglu_f32(x.reshape(-1, K).cpu(), lin.weight.detach().t().contiguous())
+    assert orc.compare(want.cpu(), ref32.to(torch.bfloat16), ref32).ok
+
+    # training forward (side-store kernel) gives the same h; the backward reaches the parameter
+    x.requires_grad_(True)
+    y2 = mod(x)
+    assert torch.equal(y2.detach().view(torch.int16), y.view(torch.int16))
+    dy = torch.randn((B, S, N)).to(torch.bfloat16).to(DEV)
+    y2.backward(dy)
+    wf = lin.weight.detach().float().t().contiguous().to(DEV).requires_grad_(True)   # [K, 2N]
+    xf = x.detach().float().reshape(-1, K).requires_grad_(True)
+    gu = xf @ wf
+    (torch.nn.functional.silu(gu[:, N:]) * gu[:, :N]).backward(dy.float().reshape(-1, N))
+    for got, ref, name in ((x.grad.reshape(-1, K), xf.grad, "grad_x"),
+                           (mod.weight.grad, wf.grad, "grad_w")):
+        err = (got.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item(), name
+    # the state dict after the step is still in the nn.Linear layout
+    opt = torch.optim.SGD(mod.parameters(), lr=1e-2)
+    opt.step()
+    sd = mod.state_dict()
+    assert tuple(sd["weight"].shape) == (2 * N, K)
+    assert not torch.equal(sd["weight"].cpu(), lin.weight.detach())
