@@ -27,10 +27,24 @@ from .ops import matmul_fused_swiglu
 from .weights import pack_swiglu_linear_weight, unpack_swiglu_linear_weight
 
 
+_BACKWARD_MODES = {"save_preact", "save_factors", "save_factors_normal", "save_factors_cute_bwd",
+                   "onload_save_factors", "cublas_save_factors"}
+
+
 class PackedSwiGLULinear(torch.nn.Module):
-    def __init__(self, in_features: int, hidden_features: int, *, device=None,
-                 dtype=torch.bfloat16) -> None:
+    """``block_n_half``, ``backward_mode`` and ``parameter_layout`` are the reference
+    constructor's tuning switches (``swiglu/triton/impls.py:3388-3408``); they are accepted,
+    checked against the same sets and otherwise unused: there is one native forward/backward
+    path and one parameter layout here."""
+
+    def __init__(self, in_features: int, hidden_features: int, *, block_n_half=None,
+                 backward_mode: str = "save_factors_normal", parameter_layout: str = "normal",
+                 device=None, dtype=torch.bfloat16) -> None:
         super().__init__()
+        if backward_mode not in _BACKWARD_MODES:
+            raise ValueError(f"unknown backward_mode {backward_mode!r}")
+        if parameter_layout not in ("packed", "normal"):
+            raise ValueError(f"unknown parameter_layout {parameter_layout!r}")
         if in_features % 8 or hidden_features % 8:
             raise ValueError("in_features and hidden_features must be multiples of 8 "
                              f"(16-byte rows), got {in_features} and {hidden_features}")
@@ -41,13 +55,13 @@ class PackedSwiGLULinear(torch.nn.Module):
         self.reset_parameters()
 
     @classmethod
-    def from_linear(cls, linear: torch.nn.Linear) -> "PackedSwiGLULinear":
+    def from_linear(cls, linear: torch.nn.Linear, **kwargs) -> "PackedSwiGLULinear":
         if linear.bias is not None:
             raise ValueError("the projection has no bias term")
         if linear.out_features % 2:
             raise ValueError("out_features must be 2 * hidden_features")
         module = cls(linear.in_features, linear.out_features // 2, device=linear.weight.device,
-                     dtype=linear.weight.dtype)
+                     dtype=linear.weight.dtype, **kwargs)
         module.load_linear_weight_(linear.weight)
         return module
 

@@ -55,3 +55,20 @@ def test_from_linear_and_back():
     # plugging into a container keeps the nn.Linear layout under the usual key
     seq = torch.nn.Sequential(m)
     assert tuple(seq.state_dict()["0.weight"].shape) == (32, 40)
+
+
+def test_reference_import_path_and_constructor_switches():
+    from swiglu.triton.impls import (PackedSwiGLULinear as P, pack_swiglu_linear_weight,
+                                     unpack_swiglu_linear_weight)
+    assert P is PackedSwiGLULinear
+    m = P(64, 32, block_n_half=64, backward_mode="save_factors", parameter_layout="packed",
+          device="cpu")
+    lw = m.linear_weight()
+    assert torch.equal(pack_swiglu_linear_weight(lw, 64), m.weight.detach())
+    assert torch.equal(unpack_swiglu_linear_weight(m.weight.detach(), 64), lw)
+    with pytest.raises(ValueError):
+        P(64, 32, backward_mode="nope", device="cpu")
+    with pytest.raises(ValueError):
+        P(64, 32, parameter_layout="nope", device="cpu")
+    with pytest.raises(ImportError):
+        from swiglu.triton.impls import fused_swiglu_wide_packed  # noqa: F401
