@@ -1,6 +1,6 @@
 """Cycle accounting of the kernel's roles (developer tool).
 
-    python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|silu_mul] [--rows M]
+    python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|fused_swiglu_save|silu_mul] [--rows M]
                                             [--block-k 64|128] [--group-m G]
 
 Builds a second copy of the library with ``-DSGL_PROFILE`` (``libswiglu_b200_prof.so``, next to
@@ -38,7 +38,8 @@ def build_profile_library() -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--form", choices=("fused_swiglu", "silu_mul"), default="fused_swiglu")
+    ap.add_argument("--form", choices=("fused_swiglu", "fused_swiglu_save", "silu_mul"),
+                    default="fused_swiglu")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--n", type=int, default=12288)
@@ -51,7 +52,7 @@ def main() -> None:
     import torch
 
     from . import _lib
-    from .ops import matmul_fused_swiglu, matmul_silu_mul
+    from .ops import matmul_fused_swiglu, matmul_fused_swiglu_save_factors, matmul_silu_mul
 
     dev = torch.device("cuda:0")
     M, K, N = args.rows, args.k, args.n
@@ -59,7 +60,8 @@ def main() -> None:
     x = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
     w = torch.empty((K, 2 * N), device=dev, dtype=torch.bfloat16).normal_(0, K ** -0.5, generator=g)
     out = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
-    form = _lib.FORM_FUSED_SWIGLU if args.form == "fused_swiglu" else _lib.FORM_SILU_MUL
+    form = {"fused_swiglu": _lib.FORM_FUSED_SWIGLU, "fused_swiglu_save": _lib.FORM_FUSED_SWIGLU_SAVE,
+            "silu_mul": _lib.FORM_SILU_MUL}[args.form]
     cfg = _lib.default_config(form, M, N, K)
     if args.block_k or args.group_m:
         cfg = _lib.TileConfig(cfg.cta_group, args.block_k or cfg.block_k, 0,
@@ -67,6 +69,11 @@ def main() -> None:
     if args.form == "fused_swiglu":
         def run():
             matmul_fused_swiglu(x, w, out=out, config=cfg)
+    elif args.form == "fused_swiglu_save":
+        factors = torch.empty((M, 2 * N), device=dev, dtype=torch.bfloat16)
+
+        def run():
+            matmul_fused_swiglu_save_factors(x, w, out=out, factors=factors, config=cfg)
     else:
         w_gate = w[:, N:].contiguous()
         up = x @ w[:, :N].contiguous()
