@@ -166,7 +166,8 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
 
 /*
  * Split-K form of sgl_matmul_bf16 for short, deep problems (few output tiles, large K - the
- * down projection at decode batch sizes): K is cut into `splits` ranges (0 = choose), each
+ * down projection at decode batch sizes): K is cut into `splits` ranges (0 = choose: as many as
+ * fill one wave of SMs), each
  * range's partial tile is written in fp32 to its slot of `scratch`, and a second kernel adds
  * the slots in fp32, in order (deterministic), into c (bf16).  `scratch` is device memory the
  * caller owns; sgl_matmul_bf16_splitk_scratch_bytes says how much this problem needs
@@ -191,8 +192,9 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
  * every GPU that loads it; the call itself performs no allocation of any kind.
  *
  * Limits and rules:
- *   - splits (after the automatic choice when 0) x round_up(M, 32) x N x 4 bytes must fit
- *     8 MiB (8388608); otherwise SGL_ERR_BAD_ARGUMENT with the sizes in sgl_last_error().
+ *   - splits x round_up(M, 32) x N x 4 bytes must fit 8 MiB (8388608); otherwise
+ *     SGL_ERR_BAD_ARGUMENT with the sizes in sgl_last_error().  splits = 0 picks the largest
+ *     useful number of ranges that fits (down to 1, which must fit too).
  *     Example that just fits: M <= 64, N = 4096, 8 K ranges.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and remembers it; make that first
@@ -202,7 +204,9 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
  *     kernel reads is written earlier in the same call.  Two calls that can run at the same
  *     time on one GPU (different streams, different host threads) race on it: serialise them
  *     or use sgl_matmul_bf16_splitk with separate scratch.
- * Results are identical to sgl_matmul_bf16_splitk for the same arguments.
+ * Results are identical to sgl_matmul_bf16_splitk for the same arguments and the same number
+ * of K ranges (pass `splits` explicitly where the two must agree bit for bit: here an
+ * automatic choice is lowered until it fits the 8 MiB, there it is not).
  */
 int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t M, int64_t N,
                                   int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int splits,

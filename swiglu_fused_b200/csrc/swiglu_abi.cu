@@ -653,24 +653,36 @@ struct SplitPlan {
   int64_t scratch_bytes;
 };
 
-int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, SplitPlan* out) {
+int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, SplitPlan* out,
+                int64_t max_scratch = 0) {
   if (splits < 0 || splits > 64)
     return fail(SGL_ERR_BAD_ARGUMENT, "splits=%d outside [0, 64] (0 = choose)", splits);
-  if (splits == 0) {
-    // Enough K ranges to give every SM pair a work unit, at least 512 of K each.
-    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    int64_t want = (sm_count / 2 + tiles - 1) / tiles;
+  const bool automatic = splits == 0;
+  if (automatic) {
+    // As many K ranges as fill ONE wave of workers (a second, partly filled wave would cost
+    // as much as a full one), at least 512 of K each.  Up to 128 rows the default
+    // configuration runs one CTA per 128-row tile, above that a CTA pair per 256-row tile.
+    const bool single = M <= 128;
+    const int64_t workers = single ? sm_count : sm_count / 2;
+    const int64_t row_tile = single ? 128 : 256;
+    const int64_t tiles = ((M + row_tile - 1) / row_tile) * ((N + 255) / 256);
+    int64_t want = workers / tiles;
     const int64_t by_k = K / 512 > 0 ? K / 512 : 1;
     if (want > by_k) want = by_k;
     if (want > 16) want = 16;
     splits = want < 1 ? 1 : static_cast<int>(want);
   }
-  int64_t per = (K + splits - 1) / splits;
-  per = (per + 127) / 128 * 128;
-  out->k_per_split = static_cast<int>(per);
-  out->splits = static_cast<int>((K + per - 1) / per);
   out->slot_rows = static_cast<int>((M + 31) / 32 * 32);
-  out->scratch_bytes = static_cast<int64_t>(out->splits) * out->slot_rows * N * 4;
+  for (;;) {
+    int64_t per = (K + splits - 1) / splits;
+    per = (per + 127) / 128 * 128;
+    out->k_per_split = static_cast<int>(per);
+    out->splits = static_cast<int>((K + per - 1) / per);
+    out->scratch_bytes = static_cast<int64_t>(out->splits) * out->slot_rows * N * 4;
+    // an automatic choice gives way to a fixed scratch size; an explicit one does not
+    if (!automatic || max_scratch <= 0 || out->scratch_bytes <= max_scratch || splits <= 1) break;
+    --splits;
+  }
   return SGL_OK;
 }
 
@@ -800,7 +812,7 @@ int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
   SplitPlan plan;
-  if ((rc = plan_splitk(M, N, K, splits, 148, &plan))) return rc;
+  if ((rc = plan_splitk(M, N, K, splits, 148, &plan, kStaticScratchBytes))) return rc;
   if (plan.scratch_bytes > kStaticScratchBytes)
     return fail(SGL_ERR_BAD_ARGUMENT,
                 "this problem needs %lld bytes of split-K scratch (%d K ranges x %d rows x %lld "

@@ -192,6 +192,10 @@ def test_splitk_scratch_plan():
     # automatic choice: one tile of output, 14336 deep -> many ranges; many tiles -> one range
     assert f(64, 256, 14336, 0) == 16 * 64 * 256 * 4
     assert f(8192, 8192, 4096, 0) == 1 * 8192 * 8192 * 4
+    # decode-size down projection: 16 column tiles, one CTA each -> 9 ranges fill 144 of 148 SMs
+    assert f(64, 4096, 14336, 0) == 9 * 64 * 4096 * 4
+    # above 128 rows CTA pairs work on 256-row tiles: 74 pairs / 16 tiles -> 4 ranges, one wave
+    assert f(256, 4096, 14336, 0) == 4 * 256 * 4096 * 4
     assert f(64, 4096, 14332, 8) == -2       # K not a multiple of 8
     assert f(0, 4096, 14336, 8) == -2
     assert f(64, 4096, 14336, 65) == -10     # too many ranges
