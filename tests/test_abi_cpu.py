@@ -283,3 +283,31 @@ int main(void) {
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0, (out.returncode, out.stdout, out.stderr)
     assert "cta_group=2 block_k=128" in out.stdout
+
+
+def test_ctypes_prototypes_match_the_header():
+    """Every declared function has a ctypes prototype with the same number of parameters, and
+    pointer / 64-bit / int parameters are bound as such (an ABI drift between the header and the
+    binding would otherwise only show up as corrupted arguments on the GPU)."""
+    import ctypes as C
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    decls = re.findall(r"\b(?:int|int64_t|const char\*)\s+(sgl_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text)
+    assert len(decls) == len(_lib.EXPORTED_SYMBOLS)
+    lib = _lib.load()
+    for name, params in decls:
+        params = params.strip()
+        plist = [] if params in ("", "void") else [p.strip() for p in params.split(",")]
+        fn = getattr(lib, name)
+        assert fn.argtypes is not None, f"{name} has no ctypes prototype"
+        assert len(fn.argtypes) == len(plist), (name, plist, fn.argtypes)
+        for decl, ctype in zip(plist, fn.argtypes):
+            if "*" in decl:
+                assert ctype is C.c_void_p or issubclass(ctype, C._Pointer) or ctype is C.c_char_p, \
+                    (name, decl, ctype)
+            elif decl.startswith("int64_t"):
+                assert ctype is C.c_int64, (name, decl, ctype)
+            elif decl.startswith("uint64_t"):
+                assert ctype is C.c_uint64, (name, decl, ctype)
+            elif decl.startswith("int "):
+                assert ctype is C.c_int, (name, decl, ctype)
