@@ -376,7 +376,17 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
 
   const int rows_per_tile = sgl::kBlockM * cfg.cta_group;
   const int64_t tiles_m = (s.M + rows_per_tile - 1) / rows_per_tile;
-  const int64_t tiles_n = (s.N + v.out_cols - 1) / v.out_cols;
+  // GEMM form on single-CTA tiles ([k, n] weight, no split-K, no reduce-scatter): a short
+  // problem with few 256-column tiles leaves most SMs idle while a handful stream all of B;
+  // halve the tile width (down to 64) while the tiles still fit half the SMs.
+  int acc_cols = sgl::kAccCols;
+  if (s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && !s.b_kmajor && s.splits == 1 &&
+      s.reduce_rows == 0) {
+    while (acc_cols > 64 && tiles_m * ((s.N + acc_cols - 1) / acc_cols) * 2 <= info->sm_count)
+      acc_cols /= 2;
+  }
+  const int tile_cols = s.form == SGL_FORM_MATMUL ? acc_cols : v.out_cols;
+  const int64_t tiles_n = (s.N + tile_cols - 1) / tile_cols;
   const int64_t units = tiles_m * tiles_n * s.splits;
   if (units > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
 
@@ -418,6 +428,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.b_kmajor = s.b_kmajor;
   p.reduce_rows = s.reduce_rows;
   p.reduce_add = s.reduce_add;
+  p.acc_cols = acc_cols;
   p.out_f32 = s.out_f32;
   p.splits = s.splits;
   p.k_per_split = s.k_per_split;

@@ -124,6 +124,9 @@ struct KernelParams {
                         // reduce-scatter start at different owners so no owner is swamped
   int reduce_add;       // FORM_GEMM with reduce_rows > 0: 1 = add into the owner's buffer,
                         // 0 = overwrite (the owner's buffer is this rank's private slot)
+  int acc_cols;         // FORM_GEMM, single-CTA tiles, [k, n] weight: columns per tile (64, 128
+                        // or 256).  Short problems with few 256-wide tiles are cut into
+                        // narrower ones so that more SMs stream their own columns of B.
   unsigned long long wait_limit_ns;
 };
 
@@ -284,6 +287,12 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     return (len + kBlockK - 1) / kBlockK;
   };
   const int stages = p.stages;
+  // Output columns per tile: a compile-time constant except in the GEMM form, where
+  // single-CTA tiles may be narrower and then load fewer 64-column slabs of B per stage.
+  int tile_cols = T::kOutCols;
+  int b_slabs = T::kBSlabs;
+  if constexpr (kForm == FORM_GEMM) tile_cols = p.acc_cols;
+  if constexpr (kForm == FORM_GEMM && kCtaGroup == 1) b_slabs = tile_cols / 64;
 
   // ---- shared memory carve-up (offsets identical in both CTAs of a pair) ----
   extern __shared__ uint8_t smem_raw[];
@@ -350,9 +359,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters) {
         const TileCoord tc = shifted_tile(t / splits);
         const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
-        const int n0 = tc.n * T::kOutCols;
+        const int n0 = tc.n * tile_cols;
         const int num_kb = unit_kb(t);
         const int k_base = unit_k0(t);
+        const uint32_t stage_tx =
+            static_cast<uint32_t>(T::kAStageBytes + b_slabs * T::kBSlabBytes);
         for (int kb = 0; kb < num_kb; ++kb) {
           SGL_PROF_BEGIN(tp0);
           if (!ptx::mbar_wait(bar_empty + 8 * s, ph ^ 1u, limit, abort_flag)) {
@@ -363,7 +374,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           SGL_PROF_END(prof_pe, tp0);
           const uint32_t full_local = bar_full + 8 * s;
           const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
-          ptx::mbar_arrive_expect_tx_cluster(full, T::kStageBytes);
+          ptx::mbar_arrive_expect_tx_cluster(full, stage_tx);
           const int k0 = k_base + kb * kBlockK;
           const uint32_t a_dst = sA + s * T::kAStageBytes;
           if (p.a_mnmajor) {
@@ -404,6 +415,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           } else {
 #pragma unroll
             for (int j = 0; j < T::kBSlabs; ++j) {
+              if (j >= b_slabs) break;
               // Slab index inside the 256 accumulator columns of the cluster tile.
               const int g = static_cast<int>(rank) * T::kBSlabs + j;
               int col;
@@ -432,7 +444,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
     if (rank == 0 && lane == 0) {
-      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM * kCtaGroup, kAccCols,
+      const uint32_t idesc = ptx::make_idesc_bf16(kBlockM * kCtaGroup,
+                                                  kForm == FORM_GEMM ? tile_cols : kAccCols,
                                                   /*a_mn_major=*/p.a_mnmajor != 0,
                                                   /*b_mn_major=*/p.b_kmajor == 0);
       const bool b_kmajor = p.b_kmajor != 0;
@@ -522,7 +535,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const int i = g / T::kChunksPerTile;
       const int c = g - i * T::kChunksPerTile;
       const TileCoord tc = shifted_tile((cluster_id + i * num_clusters) / splits);
-      x = tc.n * T::kOutCols + c * kChunkCols;
+      x = tc.n * tile_cols + c * kChunkCols;
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
     };
 
@@ -646,8 +659,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           yy = y + ((cluster_id + i * num_clusters) % splits) * p.slot_rows;
         }
         uint32_t nbuf = out_buf0;
+        const int units32 = tile_cols / 32;
 #pragma unroll 1
-        for (int u = 0; u < kAccCols / 32; ++u) {
+        for (int u = 0; u < units32; ++u) {
           const bool first = f32 || (u & 1) == 0;   // first 32-column unit of a staging buffer
           const bool last = f32 || (u & 1) == 1;    // buffer complete after this unit
           if (first) {
@@ -658,7 +672,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           float acc[32];
           ptx::tmem_ld_32x32b_x32(t_row + u * 32, acc);
           ptx::tmem_ld_wait();
-          if (u == kAccCols / 32 - 1) {
+          if (u == units32 - 1) {
             ptx::tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);

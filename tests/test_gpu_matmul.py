@@ -174,3 +174,25 @@ def test_reduce_scatter_rejects_bad_row_blocks():
         matmul_bf16_reduce_scatter(a, b, [buf.data_ptr()], 100, 64, dst_f32=True)   # not % 32
     with pytest.raises(ValueError):
         matmul_bf16_reduce_scatter(a, b, [buf.data_ptr()], 128, 64, dst_f32=True)   # does not cover M
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 14336, 4096), (16, 4096, 1024), (128, 2048, 520),
+                                    (100, 1024, 200), (128, 512, 8192)])
+def test_short_problems_use_narrow_tiles_and_stay_exact(M, K, N):
+    """Up to 128 rows the default configuration runs single-CTA tiles, and when 256-column
+    tiles would leave most SMs idle the launcher narrows them (down to 64 columns).  The result
+    must not depend on the tile width: same accumulation order per element, so the CTA-pair
+    kernel (always 256 wide) gives the same bits."""
+    a, b = problem(M, K, N, seed=M + K + N + 1)
+    ref32 = orc.matmul_f32(a, b)
+    ad, bd = a.to(DEV), b.to(DEV)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = big[1:M + 1, 8:8 + N]
+    matmul_bf16(ad, bd, out=out)                       # default: cta_group 1, narrowed tiles
+    rep = orc.compare(out.cpu(), ref32.to(torch.bfloat16), ref32)
+    assert rep.ok, str(rep)
+    wide = matmul_bf16(ad, bd, config=TileConfig(2, 64, 0, 8))
+    assert torch.equal(out.contiguous().view(torch.int16), wide.view(torch.int16))
+    guard = big.clone()
+    guard[1:M + 1, 8:8 + N] = float("nan")
+    assert torch.isnan(guard).all(), "wrote outside the output"
