@@ -154,6 +154,8 @@ int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N,
  * sgl_matmul_bf16 with either operand stored transposed, read in place (no transpose copy):
  *   a_transposed != 0: a is stored [K, M] (row pitch lda >= M, M a multiple of 8);
  *   b_transposed != 0: b is stored [N, K] (row pitch ldb >= K).
+ * K must be a multiple of 8 except with a_transposed != 0 and b_transposed == 0, where K only
+ * counts rows of both operands and may be any value >= 1 (a ragged token count).
  * These are the two GEMMs of the backward pass over the packed weight W[K, 2N]:
  *   grad_x[M, K]  = grad_preact[M, 2N] @ W^T   -> b = W,  b_transposed = 1
  *   grad_W[K, 2N] = x^T @ grad_preact          -> a = x,  a_transposed = 1

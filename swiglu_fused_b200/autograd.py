@@ -24,6 +24,17 @@ class FusedSwiGLUFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_h: torch.Tensor):
         x, w, factors = ctx.saved_tensors
+        # grad_preact overwrites the saved factors (no second [M, 2N] buffer).  The write goes
+        # through a raw pointer, which autograd's version counter cannot see, so a second
+        # backward over the same graph would silently multiply dy into factors that already
+        # hold dy: refuse it instead.  (The reference writes grad_de to a new tensor and then
+        # frees the saved ones, swiglu/triton/impls.py:3107-3116.)
+        if getattr(ctx, "_factors_consumed", False):
+            raise RuntimeError(
+                "FusedSwiGLUFunction.backward ran twice over one forward: the saved factors "
+                "were overwritten in place by the first backward (retain_graph=True is not "
+                "supported; run the forward again)")
+        ctx._factors_consumed = True
         grad_preact = swiglu_grad_preact(grad_h.contiguous(), factors, out=factors)  # in place
         grad_x = matmul_bf16(grad_preact, w, transpose_b=True) if ctx.needs_input_grad[0] else None
         grad_w = matmul_bf16(x, grad_preact, transpose_a=True) if ctx.needs_input_grad[1] else None

@@ -760,8 +760,14 @@ int validate_matmul(const void* a, const void* b, const void* c, int64_t M, int6
 int64_t sgl_matmul_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int64_t K, int splits) {
   if (validate_shape(M, N, K)) return SGL_ERR_BAD_SHAPE;
   SplitPlan plan;
-  // The automatic choice depends on the SM count; size for a B200 (148 SMs).
-  int rc = plan_splitk(M, N, K, splits, 148, &plan);
+  // The automatic choice depends on the SM count: the current device's, as the launch will
+  // use; where no device can be asked (a host without a GPU) a B200's 148.
+  int sm_count = 148;
+  int dev = 0;
+  DeviceInfo* info = nullptr;
+  if (device_info(&dev, &info) == SGL_OK && info->sm_count > 0) sm_count = info->sm_count;
+  cudaGetLastError();
+  int rc = plan_splitk(M, N, K, splits, sm_count, &plan);
   if (rc) return rc;
   return plan.scratch_bytes;
 }
@@ -775,7 +781,7 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
   SplitPlan plan;
-  if ((rc = plan_splitk(M, N, K, splits, 148, &plan))) return rc;
+  if ((rc = plan_splitk(M, N, K, splits, info->sm_count, &plan))) return rc;
   if (scratch_bytes < plan.scratch_bytes)
     return fail(SGL_ERR_BAD_ARGUMENT, "scratch holds %lld bytes, %lld needed (%d K ranges)",
                 static_cast<long long>(scratch_bytes), static_cast<long long>(plan.scratch_bytes),
@@ -823,7 +829,7 @@ int sgl_matmul_bf16_splitk_static(const void* a, const void* b, void* c, int64_t
   DeviceInfo* info = nullptr;
   if ((rc = check_device(&info))) return rc;
   SplitPlan plan;
-  if ((rc = plan_splitk(M, N, K, splits, 148, &plan, kStaticScratchBytes))) return rc;
+  if ((rc = plan_splitk(M, N, K, splits, info->sm_count, &plan, kStaticScratchBytes))) return rc;
   if (plan.scratch_bytes > kStaticScratchBytes)
     return fail(SGL_ERR_BAD_ARGUMENT,
                 "this problem needs %lld bytes of split-K scratch (%d K ranges x %d rows x %lld "
@@ -947,7 +953,12 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   int rc;
   if ((rc = validate_ptr(a, "a")) || (rc = validate_ptr(b, "b")) || (rc = validate_ptr(c, "c")))
     return rc;
-  if ((rc = validate_shape(M, N, K))) return rc;
+  // With a stored [K, M] and b stored [K, N] the reduction index is only a ROW count of both
+  // operands: no row pitch depends on it and rows past K read as zero, so any K >= 1 is fine
+  // (the weight gradient x^T @ g of a ragged token count).  In every other layout K is the
+  // contiguous extent of a row and must keep it 16-byte sized.
+  const bool k_is_row_count = a_transposed && !b_transposed;
+  if ((rc = validate_shape(M, N, k_is_row_count ? (K + 7) / 8 * 8 : K))) return rc;
   if (a_transposed && M % 8 != 0)
     return fail(SGL_ERR_BAD_SHAPE, "M=%lld must be a multiple of 8 when a is stored [K, M]",
                 static_cast<long long>(M));

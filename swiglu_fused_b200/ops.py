@@ -18,6 +18,7 @@ Differences, all on purpose:
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
 import os
 
@@ -74,6 +75,18 @@ def _stream_handle(stream, device) -> int:
     if isinstance(stream, torch.cuda.Stream):
         return stream.cuda_stream
     return int(stream)
+
+
+def stream_context(stream, device):
+    """Context manager that makes ``stream`` torch's current stream on ``device`` (a no-op for
+    ``None``).  Work that torch itself enqueues around a launch - allocator bookkeeping of a
+    temporary, ``zero_()``, a symmetric-memory barrier - is ordered with the launch only if it
+    runs on the same stream, so callers that accept ``stream=`` wrap such work in this."""
+    if stream is None:
+        return contextlib.nullcontext()
+    if not isinstance(stream, torch.cuda.Stream):
+        stream = torch.cuda.ExternalStream(int(stream), device=device)
+    return torch.cuda.stream(stream)
 
 
 def _pick_config(form: int, config: TileConfig | None, M: int, N: int, K: int):
@@ -292,7 +305,10 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
     K2, N = (B.shape[1], B.shape[0]) if transpose_b else B.shape
     if K2 != K:
         raise ValueError(f"K mismatch: op(A).K={K} vs op(B).K={K2}")
-    if K % 8 or N % 8 or (transpose_a and M % 8):
+    # K is a contiguous extent (16-byte rows) unless both operands are stored [K, *], where it
+    # only counts rows: the weight gradient x^T @ g then takes any token count.
+    k_is_row_count = transpose_a and not transpose_b
+    if (K % 8 and not k_is_row_count) or N % 8 or (transpose_a and M % 8):
         raise ValueError(f"K={K}, N={N} (and M={M} when A is transposed) must be multiples of 8")
     dev = _same_device(("A", A), ("B", B))
     if M == 0:
@@ -336,7 +352,10 @@ def matmul_bf16_splitk(A, B, *, out=None, splits: int = 0, scratch=None, stream=
     c = _prep_out(out, M, N, dev)
     need = splitk_scratch_bytes(M, N, K, splits)
     if scratch is None:
-        scratch = torch.empty(need, dtype=torch.uint8, device=dev)
+        # allocate on the launch stream: the caching allocator then hands the block to somebody
+        # else only after the kernels queued on that stream have run
+        with stream_context(stream, dev):
+            scratch = torch.empty(need, dtype=torch.uint8, device=dev)
     if scratch.dtype != torch.uint8 or not scratch.is_cuda or scratch.device != dev \
             or not scratch.is_contiguous():
         raise ValueError("scratch must be a contiguous uint8 CUDA tensor on the operands' device")

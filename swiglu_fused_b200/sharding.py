@@ -108,19 +108,22 @@ def fused_swiglu_n_sharded_fused_gather(x: torch.Tensor, w: torch.Tensor, out: S
     nobody reads before every peer's stores have landed.  Returns ``out.tensor``
     (the full ``[M, N]``) on every rank.
     """
-    from .ops import matmul_fused_swiglu_multi_dst
+    from .ops import matmul_fused_swiglu_multi_dst, stream_context
 
     N = n_total if n_total is not None else w.shape[1] // 2
     rank, world = out.rank, out.world
     mine = col_shard(N, world, rank)
-    out.barrier()
-    if mine.count > 0:
-        order = [rank] + [r for r in range(world) if r != rank]
-        dsts = [out.ptrs[r] + 2 * mine.begin for r in order]
-        matmul_fused_swiglu_multi_dst(x, w, dsts, out.tensor.stride(0), up_col0=mine.begin,
-                                      gate_col0=N + mine.begin, n_out=mine.count,
-                                      stream=stream, config=config)
-    out.barrier()
+    # the two barriers run on torch's current stream: make that the launch stream
+    with stream_context(stream, x.device):
+        out.barrier()
+        if mine.count > 0:
+            # peers after this rank, nearest first: ranks start on different NVLink ports
+            order = [(rank + i) % world for i in range(world)]
+            dsts = [out.ptrs[r] + 2 * mine.begin for r in order]
+            matmul_fused_swiglu_multi_dst(x, w, dsts, out.tensor.stride(0), up_col0=mine.begin,
+                                          gate_col0=N + mine.begin, n_out=mine.count,
+                                          stream=stream, config=config)
+        out.barrier()
     return out.tensor
 
 
@@ -192,25 +195,29 @@ def down_proj_row_parallel(h_local: torch.Tensor, w_down_local: torch.Tensor, bu
       Single pass and, with a bf16 buffer, the fastest form, but every contribution rounds to
       bf16 and the order of additions (hence the last bit) varies from run to run.
     """
-    from .ops import matmul_bf16_reduce_scatter, sum_bf16_slots
+    from .ops import matmul_bf16_reduce_scatter, stream_context, sum_bf16_slots
 
-    if isinstance(bufs, RowParallelSlots):
-        slot_bytes = bufs.rows_per_rank * bufs.N * 2
-        dsts = [p + bufs.rank * slot_bytes for p in bufs.ptrs]
-        bufs.barrier()                 # owners have finished reading the previous contents
-        matmul_bf16_reduce_scatter(h_local, w_down_local, dsts, bufs.rows_per_rank, bufs.N,
-                                   dst_f32=False, accumulate=False,
+    # zero_() and the barriers run on torch's current stream: make that the launch stream, so
+    # that they are ordered with the peer stores and additions of the kernel
+    with stream_context(stream, h_local.device):
+        if isinstance(bufs, RowParallelSlots):
+            slot_bytes = bufs.rows_per_rank * bufs.N * 2
+            dsts = [p + bufs.rank * slot_bytes for p in bufs.ptrs]
+            bufs.barrier()                 # owners have finished reading the previous contents
+            matmul_bf16_reduce_scatter(h_local, w_down_local, dsts, bufs.rows_per_rank, bufs.N,
+                                       dst_f32=False, accumulate=False,
+                                       first_dst=(bufs.rank + 1) % bufs.world, stream=stream,
+                                       config=config)
+            bufs.barrier()                 # every rank's tiles have landed
+            return sum_bf16_slots(bufs.tensor, out, rows=bufs.my_rows, stream=stream)
+        bufs.tensor.zero_()
+        bufs.barrier()                     # every buffer is zero before anybody adds into it
+        matmul_bf16_reduce_scatter(h_local, w_down_local, bufs.ptrs, bufs.rows_per_rank,
+                                   bufs.tensor.stride(0),
+                                   dst_f32=bufs.tensor.dtype == torch.float32, accumulate=True,
                                    first_dst=(bufs.rank + 1) % bufs.world, stream=stream,
                                    config=config)
-        bufs.barrier()                 # every rank's tiles have landed
-        return sum_bf16_slots(bufs.tensor, out, rows=bufs.my_rows, stream=stream)
-    bufs.tensor.zero_()
-    bufs.barrier()                     # every buffer is zero before anybody adds into it
-    matmul_bf16_reduce_scatter(h_local, w_down_local, bufs.ptrs, bufs.rows_per_rank,
-                               bufs.tensor.stride(0), dst_f32=bufs.tensor.dtype == torch.float32,
-                               accumulate=True, first_dst=(bufs.rank + 1) % bufs.world,
-                               stream=stream, config=config)
-    bufs.barrier()                     # every rank's additions have landed
+        bufs.barrier()                     # every rank's additions have landed
     return bufs.tensor[:bufs.my_rows]
 
 

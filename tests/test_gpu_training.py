@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import swiglu_oracle as orc
-from swiglu_fused_b200 import TileConfig, _lib, matmul_fused_swiglu
+from swiglu_fused_b200 import TileConfig, _lib, matmul_bf16, matmul_fused_swiglu
 from swiglu_fused_b200.autograd import fused_swiglu
 from swiglu_fused_b200.ops import matmul_fused_swiglu_save_factors, swiglu_grad_preact
 from swiglu_fused_b200.workloads import make_inputs
@@ -79,6 +79,56 @@ def test_autograd_matches_fp32_autograd():
         err = (got.float() - want).abs().max().item()
         scale = want.abs().max().item()
         assert err <= 2e-2 * scale, f"{name}: max err {err} vs scale {scale}"
+
+
+def test_autograd_with_a_ragged_token_count():
+    """M = 200 tokens: the weight gradient x^T @ grad_preact has K = 200, which only counts
+    rows of both operands and need not be a multiple of 8."""
+    M, K, N = 200, 256, 384
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=15)
+    x = inp["x"].to(DEV).requires_grad_(True)
+    w = inp["w"].to(DEV).requires_grad_(True)
+    gen = torch.Generator().manual_seed(16)
+    dy = torch.randn((M, N), generator=gen).to(torch.bfloat16).to(DEV)
+    fused_swiglu(x, w).backward(dy)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    xf = inp["x"].float().to(DEV).requires_grad_(True)
+    wf = inp["w"].float().to(DEV).requires_grad_(True)
+    gu = xf @ wf
+    (torch.nn.functional.silu(gu[:, N:]) * gu[:, :N]).backward(dy.float())
+    for got, want, name in ((x.grad, xf.grad, "grad_x"), (w.grad, wf.grad, "grad_w")):
+        err = (got.float() - want).abs().max().item()
+        scale = want.abs().max().item()
+        assert err <= 2e-2 * scale, f"{name}: max err {err} vs scale {scale}"
+    # and an odd row count straight through the GEMM entry point
+    a = torch.randn((203, 264), generator=gen).to(torch.bfloat16).to(DEV)     # stored [K, M]
+    b = torch.randn((203, 136), generator=gen).to(torch.bfloat16).to(DEV)     # stored [K, N]
+    got = matmul_bf16(a, b, transpose_a=True)
+    ref32 = a.float().t() @ b.float()
+    assert orc.compare(got.cpu(), ref32.to(torch.bfloat16).cpu(), ref32.cpu()).ok
+    with pytest.raises(ValueError):           # every other layout keeps the 16-byte rule
+        matmul_bf16(a.t().contiguous(), b)
+
+
+def test_second_backward_over_one_forward_is_refused():
+    """The backward overwrites the saved factors in place; a second pass over the same graph
+    would use factors that already hold dy, so it raises instead of returning wrong numbers."""
+    M, K, N = 256, 128, 256
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=25)
+    x = inp["x"].to(DEV).requires_grad_(True)
+    w = inp["w"].to(DEV).requires_grad_(True)
+    dy = torch.ones((M, N), dtype=torch.bfloat16, device=DEV)
+    h = fused_swiglu(x, w)
+    h.backward(dy, retain_graph=True)
+    first = x.grad.clone()
+    with pytest.raises(RuntimeError, match="ran twice"):
+        h.backward(dy)
+    assert torch.equal(x.grad.view(torch.int16), first.view(torch.int16))
+    # a fresh forward is fine
+    x.grad = None
+    fused_swiglu(x, w).backward(dy)
+    assert torch.equal(x.grad.view(torch.int16), first.view(torch.int16))
 
 
 def test_module_forward_and_training_step():

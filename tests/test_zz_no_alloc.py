@@ -79,6 +79,37 @@ def test_static_scratch_entry_point_matches_caller_scratch_twice_in_a_row():
     _lib.device_status()
 
 
+def test_automatic_split_count_gives_way_to_the_fixed_scratch():
+    """splits = 0 lets the library choose.  For 128 x 4096 x 14336 the wave-filling choice is
+    9 ranges (18.9 MB of partial tiles), which the 8 MiB array cannot hold: the automatic
+    choice must come down to the 4 ranges that fit exactly, and give the same bits as the
+    caller-scratch entry point told to use 4.  The driver's view of device memory must not
+    move either (a cudaMalloc inside the library would not show in torch's own counters)."""
+    lib = _lib.load()
+    M, K, N = 128, 14336, 4096
+    assert lib.sgl_matmul_bf16_splitk_scratch_bytes(M, N, K, 0) > STATIC_BYTES   # unconstrained
+    assert lib.sgl_matmul_bf16_splitk_scratch_bytes(M, N, K, 4) == STATIC_BYTES
+    a_h, b_h = _problem(M, K, N, 303)
+    a, b = a_h.to(DEV), b_h.to(DEV)
+    want = torch.empty((M, N), dtype=torch.bfloat16, device=DEV)
+    assert _call_with_scratch(lib, a, b, want, 4) == 0, lib.sgl_last_error()
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    _call_static(lib, a, b, got, 0)          # first use resolves the array's address
+    torch.cuda.synchronize()
+    got.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    rc = _call_static(lib, a, b, got, 0)
+    assert rc == 0, lib.sgl_last_error()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    ref32 = orc.matmul_f32(a_h, b_h)
+    assert orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32).ok
+    _lib.device_status()
+
+
 def test_static_scratch_entry_point_rejects_what_does_not_fit():
     lib = _lib.load()
     M, K, N, splits = 256, 4096, 4096, 8          # 8 x 256 x 4096 x 4 = 32 MiB > 8 MiB
