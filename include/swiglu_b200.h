@@ -327,7 +327,8 @@ int sgl_set_wait_limit_ns(uint64_t ns);
  *            the copies do not overlap.  copy_weight = 0 reuses the weight copied by an earlier
  *            run.  Not re-entrant: one run at a time per pipeline.
  *   query    bytes moved and kernels launched per run, device bytes held.
- *   destroy  frees everything create made; NULL is accepted.
+ *   destroy  frees everything create made; NULL is accepted.  The caller's current device is
+ *            restored by run and destroy.
  * These are the only functions of the library that allocate device memory or block the host.
  */
 typedef struct sgl_host_pipeline sgl_host_pipeline;
@@ -337,11 +338,36 @@ enum {
   SGL_PIPE_D2H_BYTES = 2,
   SGL_PIPE_LAUNCHES = 3,            /* kernels per run with copy_weight = 1 */
   SGL_PIPE_LAUNCHES_NO_WEIGHT = 4,
-  SGL_PIPE_DEVICE_BYTES = 5
+  SGL_PIPE_DEVICE_BYTES = 5,
+  SGL_PIPE_PEER_BYTES = 6           /* shared weight: bytes this rank pushes to peers per run */
 };
 int sgl_host_pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t first_rows,
                              int64_t block_rows, int windows, const sgl_config* cfg,
                              sgl_host_pipeline** out);
+/*
+ * The pipeline for several GPUs (one process each) that run the SAME weight on different rows:
+ * the weight crosses the host link once per group instead of once per rank.  Rank r copies only
+ * its column slice of the weight (sgl_shard_range(N, 256, world, r); for fused_swiglu the up and
+ * the gate columns of that range) from w_host, pushes it into the other ranks' weight buffers
+ * with peer copies over NVLink and then stores a flag word there; a launch over another
+ * rank's slice is preceded by a one-thread kernel that waits for that flag, for at most the
+ * library's wait limit (a time-out makes run return SGL_ERR_DEVICE_STATUS, nothing hangs).
+ * Each rank computes its first rows slice by slice as the slices arrive (its own first), the
+ * remaining rows over all columns.
+ *
+ * regions[q], q in [0, world): device address, valid in THIS process, of rank q's region of
+ * sgl_host_pipeline_shared_bytes(form, N, K) bytes (two weight copies, used alternately, and
+ * the flag words) - e.g. one symmetric-memory allocation per rank, or buffers of one process
+ * with peer access enabled.  The regions must be zero when the pipelines are created, stay
+ * valid until they are destroyed, and are not freed by destroy.  Every rank must call run the
+ * same number of times with the same copy_weight arguments, and each rank passes its own rows
+ * of x and the WHOLE w_host (only its slice of it is read).  No counterpart in the reference.
+ */
+int64_t sgl_host_pipeline_shared_bytes(int form, int64_t N, int64_t K);
+int sgl_host_pipeline_create_shared(int form, int64_t M, int64_t N, int64_t K, int64_t first_rows,
+                                    int64_t block_rows, int windows, const sgl_config* cfg,
+                                    int world, int rank, void* const* regions,
+                                    sgl_host_pipeline** out);
 int sgl_host_pipeline_run(sgl_host_pipeline* p, const void* x_host, int64_t ldx,
                           const void* w_host, int64_t ldw, const void* up_host, int64_t ldup,
                           void* h_host, int64_t ldh, int copy_weight);

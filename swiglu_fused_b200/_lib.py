@@ -32,6 +32,7 @@ PIPE_D2H_BYTES = 2
 PIPE_LAUNCHES = 3
 PIPE_LAUNCHES_NO_WEIGHT = 4
 PIPE_DEVICE_BYTES = 5
+PIPE_PEER_BYTES = 6
 
 # Every symbol include/swiglu_b200.h declares.
 EXPORTED_SYMBOLS = (
@@ -59,6 +60,8 @@ EXPORTED_SYMBOLS = (
     "sgl_selftest_wait_timeout",
     "sgl_set_wait_limit_ns",
     "sgl_host_pipeline_create",
+    "sgl_host_pipeline_shared_bytes",
+    "sgl_host_pipeline_create_shared",
     "sgl_host_pipeline_run",
     "sgl_host_pipeline_query",
     "sgl_host_pipeline_destroy",
@@ -206,6 +209,11 @@ def load() -> C.CDLL:
         lib.sgl_host_pipeline_create.restype = ip
         lib.sgl_host_pipeline_create.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp,
                                                  C.POINTER(vp)]
+        lib.sgl_host_pipeline_shared_bytes.restype = i64
+        lib.sgl_host_pipeline_shared_bytes.argtypes = [ip, i64, i64]
+        lib.sgl_host_pipeline_create_shared.restype = ip
+        lib.sgl_host_pipeline_create_shared.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp, ip,
+                                                        ip, C.POINTER(vp), C.POINTER(vp)]
         lib.sgl_host_pipeline_run.restype = ip
         lib.sgl_host_pipeline_run.argtypes = [vp, vp, i64, vp, i64, vp, i64, vp, i64, ip]
         lib.sgl_host_pipeline_query.restype = ip

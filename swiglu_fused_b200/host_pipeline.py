@@ -43,15 +43,22 @@ class _NativePipeline:
         self._handle = C.c_void_p()
         cfg = C.byref(config.to_c()) if config is not None else None
         with torch.cuda.device(self.device):
-            _lib.check(self._lib.sgl_host_pipeline_create(
-                self.form, M, N, K, first_rows, block_rows, windows, cfg,
-                C.byref(self._handle)))
+            self._create(first_rows, block_rows, windows, cfg)
+        self._read_counters()
+
+    def _create(self, first_rows, block_rows, windows, cfg) -> None:
+        _lib.check(self._lib.sgl_host_pipeline_create(
+            self.form, self.M, self.N, self.K, first_rows, block_rows, windows, cfg,
+            C.byref(self._handle)))
+
+    def _read_counters(self) -> None:
         self.h2d_bytes = self._query(_lib.PIPE_H2D_BYTES)
         self.h2d_bytes_no_weight = self._query(_lib.PIPE_H2D_BYTES_NO_WEIGHT)
         self.d2h_bytes = self._query(_lib.PIPE_D2H_BYTES)
         self.launches_per_run = self._query(_lib.PIPE_LAUNCHES)
         self.launches_per_run_no_weight = self._query(_lib.PIPE_LAUNCHES_NO_WEIGHT)
         self.device_bytes = self._query(_lib.PIPE_DEVICE_BYTES)
+        self.peer_bytes = self._query(_lib.PIPE_PEER_BYTES)
 
     def _query(self, what: int) -> int:
         out = C.c_int64()
@@ -98,6 +105,47 @@ class HostPipeline(_NativePipeline):
         """One pass.  Host tensors should be pinned so the copies are asynchronous.
         Returns ``h_host`` after the last device->host copy has completed."""
         return self._run(x_host, w_host, None, h_host, copy_weight)
+
+
+class SharedWeightHostPipeline(HostPipeline):
+    """``HostPipeline`` for a process group whose ranks run the same weight on different rows
+    (the M-sharded launch, one process per GPU).  Collective: every rank constructs it, with its
+    own row count ``M``, and every rank calls ``run`` the same number of times.  Each rank copies
+    only its 1/world column slice of ``w_host`` over PCIe; the slices travel on to the other
+    ranks' weight buffers over NVLink (``sgl_host_pipeline_create_shared``), so the weight
+    crosses the host link once per group.  The weight buffers are one symmetric-memory
+    allocation per rank (``torch.distributed._symmetric_memory``, no multicast object)."""
+
+    def __init__(self, M: int, K: int, N: int, *, device="cuda:0", group=None, **kw):
+        import os
+
+        import torch.distributed as dist
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        nbytes = _lib.load().sgl_host_pipeline_shared_bytes(self.form, N, K)
+        if nbytes < 0:
+            _lib.check(int(nbytes))
+        self._region = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=torch.device(device))
+        self._region.zero_()
+        self._symm = symm_mem.rendezvous(self._region, self.group)
+        self.rank, self.world = self._symm.rank, self._symm.world_size
+        self._ptrs = [int(p) for p in self._symm.buffer_ptrs]
+        torch.cuda.synchronize(torch.device(device))
+        dist.barrier(group=self.group)          # every region is zero before anybody signals
+        super().__init__(M, K, N, device=device, **kw)
+        dist.barrier(group=self.group)
+
+    def _create(self, first_rows, block_rows, windows, cfg) -> None:
+        arr = (C.c_void_p * self.world)(*self._ptrs)
+        _lib.check(self._lib.sgl_host_pipeline_create_shared(
+            self.form, self.M, self.N, self.K, first_rows, block_rows, windows, cfg,
+            self.world, self.rank, arr, C.byref(self._handle)))
+
+    def close(self) -> None:
+        super().close()          # the native pipeline first: it borrows the regions
+        self._region = None
 
 
 class HostPipelineSiluMul(_NativePipeline):

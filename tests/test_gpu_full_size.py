@@ -68,3 +68,35 @@ def test_full_size_properties(name):
     assert torch.equal(bits(hp), bits(h[:2048][perm]))
     torch.cuda.synchronize()
     _lib.device_status()
+
+
+@pytest.mark.parametrize("M", [64, 256, 1024])
+def test_c4_tile_tail_shapes_against_the_oracle(M):
+    """Configuration 4's tile tail at its own K and N (M in {64, 256, 1024}, K = 4096,
+    N = 14336, weights N(0, 0.02)): rows against the fp32 CPU oracle (all of them for M = 64,
+    a spread of 64 otherwise, the first and the last included), and the tail result must be a
+    bit-exact slice of the same rows computed inside a taller problem (a different tile
+    schedule, the same per-element arithmetic).  The reference rejects M = 64
+    (swiglu/matmul_silu_mul.py:101-111)."""
+    K, N = 4096, 14336
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn((2048, K), device=DEV, dtype=torch.bfloat16, generator=g)
+    w = torch.empty((K, 2 * N), device=DEV, dtype=torch.bfloat16).normal_(0.0, 0.02, generator=g)
+    h = matmul_fused_swiglu(x[:M], w)
+    torch.cuda.synchronize()
+    _lib.device_status()
+    assert h.shape == (M, N) and bool(torch.isfinite(h.float()).all())
+    rows = torch.arange(M) if M <= 64 else torch.unique(torch.linspace(0, M - 1, 64).long())
+    xs = x[rows.to(DEV)].cpu()
+    ref32 = orc.fused_swiglu_f32(xs, w.cpu())
+    rep = orc.compare(h[rows.to(DEV)].cpu(), ref32.to(torch.bfloat16), ref32)
+    assert rep.ok, f"M={M}: {rep}"
+    tall = matmul_fused_swiglu(x, w)
+    assert torch.equal(bits(tall[:M]), bits(h))
+    # guard band: an output buffer with extra rows and columns keeps its sentinel
+    buf = torch.full((M + 32, N + 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    matmul_fused_swiglu(x[:M], w, out=buf[:M, :N])
+    assert torch.equal(bits(buf[:M, :N]), bits(h))
+    assert bool(torch.isnan(buf[M:].float()).all()) and bool(torch.isnan(buf[:, N:].float()).all())
+    torch.cuda.synchronize()
+    _lib.device_status()

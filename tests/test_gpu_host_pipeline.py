@@ -121,3 +121,54 @@ def test_pipeline_argument_errors():
     pipe.close()
     with pytest.raises(RuntimeError):
         pipe.run(x, w, h)
+
+
+def test_shared_weight_pipeline_with_a_group_of_one():
+    """The shared-weight form with world = 1: the region is caller memory (here a torch tensor
+    standing in for a symmetric allocation), the double-buffered weight alternates between runs,
+    nothing is pushed or waited for, and the result is the device operator's, bit for bit."""
+    import ctypes as C
+
+    M, K, N = 3000, 264, 1288
+    x, w = fused_problem(M, K, N, seed=77)
+    want = matmul_fused_swiglu(x.to(DEV), w.to(DEV)).cpu()
+    lib = _lib.load()
+    nbytes = lib.sgl_host_pipeline_shared_bytes(_lib.FORM_FUSED_SWIGLU, N, K)
+    assert nbytes >= 2 * (2 * K * 2 * N)
+    region = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    handle = C.c_void_p()
+    ptrs = (C.c_void_p * 1)(region.data_ptr())
+    _lib.check(lib.sgl_host_pipeline_create_shared(_lib.FORM_FUSED_SWIGLU, M, N, K, 0, 0, 0, None,
+                                                   1, 0, ptrs, C.byref(handle)))
+    xh, wh = x.pin_memory(), w.pin_memory()
+    hh = torch.full((M, N), float("nan"), dtype=torch.bfloat16).pin_memory()
+    try:
+        # copy_weight = 0 before any weight was copied is refused
+        rc = lib.sgl_host_pipeline_run(handle, xh.data_ptr(), K, None, 0, None, 0, hh.data_ptr(),
+                                       N, 0)
+        assert rc == -10, lib.sgl_last_error()
+        for i in range(3):                       # parities 0, 1, 0
+            hh.fill_(float("nan"))
+            _lib.check(lib.sgl_host_pipeline_run(handle, xh.data_ptr(), K, wh.data_ptr(), 2 * N,
+                                                 None, 0, hh.data_ptr(), N, 1))
+            assert same_bits(hh, want), i
+        hh.fill_(float("nan"))
+        _lib.check(lib.sgl_host_pipeline_run(handle, xh.data_ptr(), K, None, 0, None, 0,
+                                             hh.data_ptr(), N, 0))
+        assert same_bits(hh, want)
+    finally:
+        lib.sgl_host_pipeline_destroy(handle)
+
+
+def test_pipeline_calls_leave_the_current_device_alone():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs to tell the devices apart")
+    M, K, N = 1024, 128, 256
+    x, w = fused_problem(M, K, N, seed=5)
+    pipe = HostPipeline(M, K, N, device="cuda:1")
+    hh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    torch.cuda.set_device(0)
+    pipe.run(x.pin_memory(), w.pin_memory(), hh)
+    assert torch.cuda.current_device() == 0
+    pipe.close()
+    assert torch.cuda.current_device() == 0

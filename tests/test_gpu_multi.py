@@ -86,6 +86,38 @@ def _worker(rank, world, port, M, K, N, results):
         if prev is not None:                      # deterministic: identical on the second run
             ok_g = ok_g and same(prev, y16)
         prev = y16.clone()
+    # the fused gather and the reduce-scatter on a side stream: barriers, zeroing and launch
+    # must all be ordered on that stream
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    sym.tensor.zero_()
+    side.wait_stream(torch.cuda.current_stream(dev))
+    got = sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym, stream=side)
+    y_side = sharding.down_proj_row_parallel(
+        full_ref[:, cols.begin:cols.end].contiguous(),
+        w_down[cols.begin:cols.end].contiguous(), slots, stream=side)
+    side.synchronize()
+    ok_g = ok_g and same(got, full_ref) and same(y_side, prev)
+
+    # host-buffer pipeline with the weight shared by the group: every rank copies only its
+    # slice of W from the host, the rest arrives from the peers; result = the device operator's
+    from swiglu_fused_b200.host_pipeline import SharedWeightHostPipeline
+    pipe = SharedWeightHostPipeline(rows.count, K, N, device=dev)
+    xh = x[rows.begin:rows.end].cpu().pin_memory()
+    wh = w.cpu().pin_memory()
+    hh = torch.empty((rows.count, N), dtype=torch.bfloat16).pin_memory()
+    ok_p = pipe.h2d_bytes < 2 * (rows.count * K + K * 2 * N)
+    for i in range(3):
+        hh.fill_(float("nan"))
+        pipe.run(xh, wh, hh)
+        ok_p = ok_p and same(hh.to(dev), full_ref[rows.begin:rows.end])
+    hh.fill_(float("nan"))
+    pipe.run(xh, None, hh, copy_weight=False)
+    ok_p = ok_p and same(hh.to(dev), full_ref[rows.begin:rows.end])
+    dist.barrier()
+    pipe.close()
+    ok_g = ok_g and ok_p
+
     torch.cuda.synchronize()
     _lib.device_status()
     flags = torch.tensor([int(ok_m), int(ok_n), int(ok_g)], dtype=torch.int64, device=dev)

@@ -42,7 +42,7 @@ def test_reference_bench_py_validates_and_times_the_drop_in_operator():
     assert len(lines) == 2, out
     for ln in lines:
         assert ln.rstrip().endswith("OK"), ln
-    fused = [float(v) for v in re.findall(r"fused\s+:\s+([0-9.]+) ms", out)]
+    fused = [float(v) for v in re.findall(r"(?m)^\s*fused\s+:\s+([0-9.]+) ms", out)]
     assert len(fused) == 2 and all(v > 0 for v in fused), out
     print(out)
 
