@@ -361,10 +361,13 @@ def leg_c4(dev, act_fused, peaks) -> dict:
         matmul_fused_swiglu(x, w, out=h)
         torch.cuda.synchronize()
         rows = torch.arange(m) if m <= 256 else torch.linspace(0, m - 1, 96).long()
-        ref32 = orc.fused_swiglu_f32(x[rows.to(dev)].cpu(), w_cpu)
-        rep = orc.compare(h[rows.to(dev)].cpu(), ref32.to(torch.bfloat16), ref32)
+        xs = x[rows.to(dev)].cpu()
+        ref64 = orc.fused_swiglu_exact(xs, w_cpu)          # K = 4096: measure against float64
+        rep = orc.compare(h[rows.to(dev)].cpu(), ref64.to(torch.bfloat16), ref64)
+        rep32 = orc.compare(orc.fused_swiglu(xs, w_cpu), ref64.to(torch.bfloat16), ref64)
         res["parity_ok"] = bool(rep.ok)
-        res["parity"] = f"{len(rows)} rows x {N} columns vs the fp32 CPU oracle: {rep}"
+        res["parity"] = (f"{len(rows)} rows x {N} columns vs the float64 CPU oracle: {rep}; the "
+                         f"reference's own fp32 check expression against the same: {rep32}")
         out["c4_fused" if m == M else f"c4_tail_m{m}"] = res
     _lib.device_status()
     return out

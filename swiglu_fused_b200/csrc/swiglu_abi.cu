@@ -338,7 +338,17 @@ struct LaunchSpec {
   int out_f32 = 0;
   int reduce_rows = 0, reduce_add = 0, first_dst = 0;     // reduce-scatter epilogue
   int splits = 1, k_per_split = 0, slot_rows = 0;         // split-K
+  int a_rows = sgl::kBlockM;                              // rows of the A box (see a_box_rows)
 };
+
+// Rows of the A operand's TMA box.  A problem shorter than one 128-row tile loads only the rows
+// it has (rounded up to the 8-row swizzle atom): the rest of the tile's rows in shared memory
+// keep whatever they held, the MMA turns them into accumulator rows nobody stores, and the
+// SM is spared fetching zero fill for them on every k-block.
+int a_box_rows(int64_t M, int cta_group) {
+  if (cta_group == 1 && M < sgl::kBlockM) return static_cast<int>((M + 7) / 8 * 8);
+  return sgl::kBlockM;
+}
 
 // Clusters of this variant that can be resident at once (1 CTA or CTA pair per SM).
 int query_max_clusters(const Variant& v, int cta_group, int sm_count) {
@@ -433,6 +443,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.splits = s.splits;
   p.k_per_split = s.k_per_split;
   p.slot_rows = s.slot_rows;
+  p.a_rows = s.a_rows;
   p.m_shift = 0;
   if (s.reduce_rows > 0 && s.first_dst > 0) {
     // start at the first tile row owned by destination first_dst
@@ -501,7 +512,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
   CUtensorMap tx, tw, tup;
   sgl::OutMaps th;
   std::memset(&th, 0, sizeof(th));
-  if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  if ((rc = make_map(&tx, x, M, K, ldx, a_box_rows(M, c.cta_group), 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "x")) ||
       (rc = make_map(&tw, w_gate, K, N, ldw, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "w_gate")) ||
@@ -517,6 +528,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
   spec.M = M;
   spec.N = N;
   spec.K = K;
+  spec.a_rows = a_box_rows(M, c.cta_group);
   return launch(spec, c, info, stream);
 }
 
@@ -556,7 +568,7 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
   CUtensorMap tx, tw;
   sgl::OutMaps th;
   std::memset(&th, 0, sizeof(th));
-  if ((rc = make_map(&tx, x, M, K, ldx, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  if ((rc = make_map(&tx, x, M, K, ldx, a_box_rows(M, c.cta_group), 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "x")) ||
       (rc = w_is_nk ? make_map(&tw, w, w_span, K, ldw, 128, 64,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "w")
@@ -596,6 +608,7 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
   spec.col1 = gate_col0;
   spec.n_dst = n_dsts;
   spec.b_kmajor = w_is_nk;
+  spec.a_rows = a_box_rows(M, c.cta_group);
   return launch(spec, c, info, stream);
 }
 
@@ -707,7 +720,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   CUtensorMap ta, tb;
   sgl::OutMaps tc;
   std::memset(&tc, 0, sizeof(tc));
-  if ((rc = make_map(&ta, a, M, K, lda, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  if ((rc = make_map(&ta, a, M, K, lda, a_box_rows(M, cf.cta_group), 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "a")) ||
       (rc = make_map(&tb, b, K, N, ldb, cf.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "b")) ||
@@ -727,6 +740,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   spec.splits = plan.splits;
   spec.k_per_split = plan.k_per_split;
   spec.slot_rows = plan.slot_rows;
+  spec.a_rows = a_box_rows(M, cf.cta_group);
   if ((rc = launch(spec, cf, info, stream))) return rc;
   const int64_t vecs = M * (N / 8);
   int64_t blocks = (vecs + 255) / 256;
@@ -908,7 +922,7 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
   CUtensorMap ta, tb;
   sgl::OutMaps tc;
   std::memset(&tc, 0, sizeof(tc));
-  if ((rc = make_map(&ta, a, M, K, lda, sgl::kBlockM, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  if ((rc = make_map(&ta, a, M, K, lda, a_box_rows(M, c.cta_group), 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      "a")) ||
       (rc = make_map(&tb, b, K, N, ldb, c.block_k, 64, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")))
     return rc;
@@ -938,6 +952,7 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
   spec.reduce_rows = static_cast<int>(reduce_rows);
   spec.reduce_add = accumulate;
   spec.first_dst = first_dst;
+  spec.a_rows = a_box_rows(M, c.cta_group);
   return launch(spec, c, info, stream);
 }
 
@@ -974,7 +989,7 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   std::memset(&tc, 0, sizeof(tc));
   if ((rc = a_transposed ? make_map(&ta, a, K, M, lda, cf.block_k, 64,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "a")
-                         : make_map(&ta, a, M, K, lda, sgl::kBlockM, 64,
+                         : make_map(&ta, a, M, K, lda, a_box_rows(M, cf.cta_group), 64,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "a")) ||
       (rc = b_transposed ? make_map(&tb, b, N, K, ldb, 128, 64,
                                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")
@@ -993,6 +1008,7 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   spec.K = K;
   spec.a_mnmajor = a_transposed ? 1 : 0;
   spec.b_kmajor = b_transposed ? 1 : 0;
+  spec.a_rows = a_transposed ? sgl::kBlockM : a_box_rows(M, cf.cta_group);
   return launch(spec, cf, info, stream);
 }
 

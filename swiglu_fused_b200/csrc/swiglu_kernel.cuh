@@ -127,6 +127,9 @@ struct KernelParams {
   int acc_cols;         // FORM_GEMM, single-CTA tiles, [k, n] weight: columns per tile (64, 128
                         // or 256).  Short problems with few 256-wide tiles are cut into
                         // narrower ones so that more SMs stream their own columns of B.
+  int a_rows;           // rows of the A box actually loaded per CTA and k-block: kBlockM, or the
+                        // (8-aligned) row count of a problem shorter than one tile, whose
+                        // missing rows would otherwise be fetched as zero fill at full cost
   unsigned long long wait_limit_ns;
 };
 
@@ -362,8 +365,10 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int n0 = tc.n * tile_cols;
         const int num_kb = unit_kb(t);
         const int k_base = unit_k0(t);
-        const uint32_t stage_tx =
-            static_cast<uint32_t>(T::kAStageBytes + b_slabs * T::kBSlabBytes);
+        // (A stored [k, m] is loaded as whole 64-column slabs; otherwise only a_rows rows)
+        const uint32_t a_tx = p.a_mnmajor ? static_cast<uint32_t>(T::kAStageBytes)
+                                          : static_cast<uint32_t>(p.a_rows * kBlockK * 2);
+        const uint32_t stage_tx = a_tx + static_cast<uint32_t>(b_slabs * T::kBSlabBytes);
         for (int kb = 0; kb < num_kb; ++kb) {
           SGL_PROF_BEGIN(tp0);
           if (!ptx::mbar_wait(bar_empty + 8 * s, ph ^ 1u, limit, abort_flag)) {

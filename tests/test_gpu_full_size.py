@@ -88,8 +88,10 @@ def test_c4_tile_tail_shapes_against_the_oracle(M):
     assert h.shape == (M, N) and bool(torch.isfinite(h.float()).all())
     rows = torch.arange(M) if M <= 64 else torch.unique(torch.linspace(0, M - 1, 64).long())
     xs = x[rows.to(DEV)].cpu()
-    ref32 = orc.fused_swiglu_f32(xs, w.cpu())
-    rep = orc.compare(h[rows.to(DEV)].cpu(), ref32.to(torch.bfloat16), ref32)
+    # K = 4096: against the float64 value (the fp32 check expression has accumulation error
+    # of its own on near-zero outputs at this depth; it must itself sit within the tolerance)
+    ref64 = orc.fused_swiglu_exact(xs, w.cpu())
+    rep = orc.compare(h[rows.to(DEV)].cpu(), ref64.to(torch.bfloat16), ref64)
     assert rep.ok, f"M={M}: {rep}"
     tall = matmul_fused_swiglu(x, w)
     assert torch.equal(bits(tall[:M]), bits(h))
