@@ -101,11 +101,12 @@ class ClockSampler(threading.Thread):
         0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
     }
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.002):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.mask, self.max_mhz = [], 0, None
         self._stop_evt = threading.Event()
+        self.ready = threading.Event()      # NVML is up: samples from now on
         self.error = None
 
     def run(self):
@@ -114,12 +115,19 @@ class ClockSampler(threading.Thread):
             pynvml.nvmlInit()
             h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            self.ready.set()
             while not self._stop_evt.is_set():
                 self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
                 self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
                 time.sleep(self.period)
         except Exception as e:  # NVML missing: report, do not fail the benchmark
             self.error = repr(e)
+            self.ready.set()
+
+    def begin(self) -> None:
+        """Called right before the timed region: wait for NVML, drop what was sampled before."""
+        self.ready.wait(timeout=10)
+        self.samples, self.mask = [], 0
 
     def stop(self) -> dict:
         self._stop_evt.set()
@@ -419,20 +427,39 @@ def leg_c5(rank: int, world: int, dev, peaks) -> dict:
         x, w, rank=rank, world=world, out=local), iters, dev, dist)
     t_nccl = timed_ranks(lambda: sharding.fused_swiglu_n_sharded(
         x, w, rank=rank, world=world, gather=True, out=full), iters, dev, dist)
-    sym.tensor.zero_()
-    t_fused = timed_ranks(lambda: sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym), iters,
-                          dev, dist)
-    torch.cuda.synchronize()
+    # the gather inside the kernel, three ways to move the tiles (see
+    # sharding.fused_swiglu_n_sharded_fused_gather); each checked against the single launch
+    ok_fused, t_modes = True, {}
+    for mode in ("tma", "stores"):
+        sym.tensor.zero_()
+        t_modes[mode] = timed_ranks(lambda: sharding.fused_swiglu_n_sharded_fused_gather(
+            x, w, sym, mode=mode), iters, dev, dist)
+        torch.cuda.synchronize()
+        ok_fused = ok_fused and same_bits(sym.tensor, single)
     ok_block = all_true(same_bits(local, single[:, cols.begin:cols.end]), dev, dist)
     ok_nccl = all_true(same_bits(full, single), dev, dist)
-    ok_fused = all_true(same_bits(sym.tensor, single), dev, dist)
+    ok_fused = all_true(ok_fused, dev, dist)
+    if ok_fused and not os.environ.get("SWIGLU_B200_NO_MULTICAST"):
+        # through the NVSwitch multicast mapping, where the fabric offers one; only after the
+        # plain modes have passed on every rank
+        del sym
+        sym = sharding.SymmetricOutput(M, N, dev, multicast=True)
+        if all_true(bool(sym.multicast_ptr), dev, dist):
+            sym.tensor.zero_()
+            t_modes["multicast"] = timed_ranks(lambda: sharding.fused_swiglu_n_sharded_fused_gather(
+                x, w, sym, mode="multicast"), iters, dev, dist)
+            torch.cuda.synchronize()
+            ok_fused = all_true(same_bits(sym.tensor, single), dev, dist)
+    best = min(t_modes, key=t_modes.get)
+    t_fused = t_modes[best]
     gather_bytes = 2.0 * M * (N - cols.count)              # received per GPU
     out = {
         "workload": f"c5: matmul_fused_swiglu {M}x{K}x{N}, {N // world} output columns per GPU, "
                     "x replicated, unsplit packed weight addressed through column windows",
         "world": world, "iters": iters,
         "compute_only_ms": t_compute, "compute_only_tflops": flops / (t_compute * 1e-3) / 1e12,
-        "nccl_gather_ms": t_nccl, "fused_gather_ms": t_fused,
+        "nccl_gather_ms": t_nccl, "fused_gather_ms": t_fused, "fused_gather_mode": best,
+        "fused_gather_ms_by_mode": t_modes,
         "fused_gather_over_compute_only": t_fused / t_compute,
         "gather_bytes_in_per_gpu": gather_bytes,
         "nvlink_floor_ms": gather_bytes / 770e9 * 1e3,
@@ -576,6 +603,7 @@ def run_ours(args) -> None:
     launches0 = _lib.kernel_launches()
     events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     barrier()
+    sampler.begin()
     events[0].record()
     for i in range(args.steps):
         step()
@@ -622,6 +650,22 @@ def run_ours(args) -> None:
                 dist.all_reduce(te, op=dist.ReduceOp.MAX)
             return te.item(), _lib.kernel_launches() - n0
 
+        # what the host side of this box gives with every rank copying at once: bare pinned
+        # copies of this rank's h (out) and x (in), the floor the pipeline works against
+        def link_rate(dst, src):
+            dst.copy_(src, non_blocking=True)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize()
+            dt = torch.tensor([(time.perf_counter() - t0) / 3], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+            return src.numel() * 2 / dt.item() / 1e9
+
+        d2h_gbs = link_rate(h_host, h)
+        h2d_gbs = link_rate(x, x_host)
         h_host.zero_()
         e2e_s, e2e_launches = e2e_time(True)
         e2e_same = same_bits(h_host.to(dev), h)
@@ -635,6 +679,11 @@ def run_ours(args) -> None:
                "h2d_bytes_per_step": pipe.h2d_bytes, "d2h_bytes_per_step": pipe.d2h_bytes,
                "ms_per_step": e2e_s * 1e3, "steps": e2e_steps, "launches": e2e_launches,
                "matches_device_run": e2e_same,
+               "host_link": {"d2h_gbs_per_gpu": d2h_gbs, "h2d_gbs_per_gpu": h2d_gbs,
+                             "floor_ms": (pipe.d2h_bytes / d2h_gbs / 1e6),
+                             "note": "bare pinned copies, one direction at a time, all ranks "
+                                     "copying at once (slowest rank); floor_ms = this rank's h "
+                                     "bytes at that device-to-host rate"},
                "host_bytes_per_step_all_ranks": world * (pipe.h2d_bytes + pipe.d2h_bytes)
                if world > 1 else pipe.h2d_bytes + pipe.d2h_bytes,
                "weight_resident": {

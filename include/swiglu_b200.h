@@ -143,6 +143,29 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
                                       int64_t gate_col0, const sgl_config* cfg, void* stream);
 
 /*
+ * sgl_matmul_fused_swiglu whose epilogue also delivers every finished tile to other GPUs: the
+ * all-gather of a column-parallel launch inside the kernel, by ordinary stores instead of the
+ * TMA stores of sgl_matmul_fused_swiglu_multi_dst.  (TMA stores to a peer queue up behind the
+ * link in the same per-SM unit that fetches the operands, and the mainloop then waits with
+ * them; stores issued by the epilogue warps only ever hold up those warps.)
+ *   h_local      element (0, 0) of this launch's [M, N] block in THIS GPU's buffer (TMA store);
+ *   h_peers[i]   the same element in peer i's buffer, mapped into this process, i < n_peers <= 8:
+ *                each tile is copied there with 16-byte stores over NVLink;
+ *   h_multicast  if not NULL, h_peers is ignored: the address of that element in an NVSwitch
+ *                multicast mapping of all the buffers (this GPU's included).  Each tile is then
+ *                stored ONCE with multimem.st and the switch replicates it, so the sender's
+ *                link carries 1/world of the gathered bytes; h_local is not written separately.
+ * All destinations share the row pitch ldh.  The caller owns the buffers and synchronises the
+ * ranks before and after (nobody may still read a buffer that is being overwritten, nobody
+ * reads before every rank's stores have landed).  The reference is single-GPU; no counterpart.
+ */
+int sgl_matmul_fused_swiglu_gather(const void* x, const void* w, void* h_local,
+                                   void* const* h_peers, int n_peers, void* h_multicast,
+                                   int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                                   int64_t ldh, int64_t up_col0, int64_t gate_col0,
+                                   const sgl_config* cfg, void* stream);
+
+/*
  * c[M,N] = a[M,K] @ b[K,N], bf16 in, fp32 accumulate, bf16 out: the down projection
  * y = h @ W_down that consumes the stage's output, on the same TMA/tcgen05 pipeline.
  * The reference stops at h; no counterpart there.

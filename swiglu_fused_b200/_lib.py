@@ -42,6 +42,7 @@ EXPORTED_SYMBOLS = (
     "sgl_matmul_fused_swiglu_save_factors",
     "sgl_swiglu_grad_preact",
     "sgl_matmul_fused_swiglu_multi_dst",
+    "sgl_matmul_fused_swiglu_gather",
     "sgl_matmul_bf16",
     "sgl_matmul_bf16_ex",
     "sgl_matmul_bf16_splitk_scratch_bytes",
@@ -168,6 +169,9 @@ def load() -> C.CDLL:
         lib.sgl_matmul_fused_swiglu_multi_dst.restype = ip
         lib.sgl_matmul_fused_swiglu_multi_dst.argtypes = [vp, vp, C.POINTER(vp), ip, i64, i64,
                                                           i64, i64, i64, i64, i64, i64, cfgp, vp]
+        lib.sgl_matmul_fused_swiglu_gather.restype = ip
+        lib.sgl_matmul_fused_swiglu_gather.argtypes = [vp, vp, vp, C.POINTER(vp), ip, vp, i64, i64,
+                                                       i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_matmul_bf16.restype = ip
         lib.sgl_matmul_bf16.argtypes = [vp, vp, vp, i64, i64, i64, i64, i64, i64, cfgp, vp]
         lib.sgl_matmul_bf16_ex.restype = ip

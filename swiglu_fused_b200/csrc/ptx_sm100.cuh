@@ -177,6 +177,25 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x,
       : "memory");
 }
 
+// 16-byte store to global memory that may belong to a peer GPU (mapped into this process).
+__device__ __forceinline__ void st_global_v4(void* addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+
+// 16-byte store to a MULTICAST address (an NVSwitch multicast object that maps the same
+// offset of every member GPU's buffer): the switch replicates the data to all members, so the
+// sender's link carries it once.  The address must come from a multicast mapping.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint32_t a, uint32_t b, uint32_t c,
+                                               uint32_t d) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "f"(__uint_as_float(a)), "f"(__uint_as_float(b)), "f"(__uint_as_float(c)),
+               "f"(__uint_as_float(d))
+               : "memory");
+}
+
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

@@ -339,6 +339,9 @@ struct LaunchSpec {
   int reduce_rows = 0, reduce_add = 0, first_dst = 0;     // reduce-scatter epilogue
   int splits = 1, k_per_split = 0, slot_rows = 0;         // split-K
   int a_rows = sgl::kBlockM;                              // rows of the A box (see a_box_rows)
+  int peer_mode = 0, n_peer = 0;                          // gather by thread stores
+  int64_t peer_ld = 0;
+  const void* peer_ptr[sgl::kMaxDst] = {};
 };
 
 // Rows of the A operand's TMA box.  A problem shorter than one 128-row tile loads only the rows
@@ -444,6 +447,11 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.k_per_split = s.k_per_split;
   p.slot_rows = s.slot_rows;
   p.a_rows = s.a_rows;
+  p.peer_mode = s.peer_mode;
+  p.n_peer = s.n_peer;
+  p.peer_ld = s.peer_ld;
+  for (int d = 0; d < sgl::kMaxDst; ++d)
+    p.peer_ptr[d] = reinterpret_cast<unsigned long long>(s.peer_ptr[d]);
   p.m_shift = 0;
   if (s.reduce_rows > 0 && s.first_dst > 0) {
     // start at the first tile row owned by destination first_dst
@@ -532,10 +540,17 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
   return launch(spec, c, info, stream);
 }
 
+struct PeerStores {
+  int mode = 0;                 // 1 = ordinary stores to n raw pointers, 2 = one multicast pointer
+  int n = 0;
+  void* const* ptrs = nullptr;
+};
+
 static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* const* h_dsts,
                             int n_dsts, void* factors, int64_t ldf, int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
                             int64_t ldh, int64_t up_col0, int64_t gate_col0,
-                            const sgl_config* cfg, void* stream) {
+                            const sgl_config* cfg, void* stream,
+                            const PeerStores* peers = nullptr) {
   int rc;
   if ((rc = validate_ptr(x, "x")) || (rc = validate_ptr(w, "w"))) return rc;
   for (int d = 0; d < n_dsts; ++d) {
@@ -609,6 +624,15 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
   spec.n_dst = n_dsts;
   spec.b_kmajor = w_is_nk;
   spec.a_rows = a_box_rows(M, c.cta_group);
+  if (peers && peers->mode != 0) {
+    for (int d = 0; d < peers->n; ++d) {
+      if ((rc = validate_ptr(peers->ptrs[d], "peer destination"))) return rc;
+      spec.peer_ptr[d] = peers->ptrs[d];
+    }
+    spec.peer_mode = peers->mode;
+    spec.n_peer = peers->n;
+    spec.peer_ld = ldh;
+  }
   return launch(spec, c, info, stream);
 }
 
@@ -892,6 +916,31 @@ int sgl_matmul_fused_swiglu_multi_dst(const void* x, const void* w, void* const*
     return fail(SGL_ERR_BAD_ARGUMENT, "n_dsts=%d outside [1, %d]", n_dsts, sgl::kMaxDst);
   return fused_swiglu_impl(x, w, 0, h_dsts, n_dsts, nullptr, 0, M, N, K, ldx, ldw, ldh, up_col0, gate_col0,
                            cfg, stream);
+}
+
+int sgl_matmul_fused_swiglu_gather(const void* x, const void* w, void* h_local,
+                                   void* const* h_peers, int n_peers, void* h_multicast,
+                                   int64_t M, int64_t N, int64_t K, int64_t ldx, int64_t ldw,
+                                   int64_t ldh, int64_t up_col0, int64_t gate_col0,
+                                   const sgl_config* cfg, void* stream) {
+  if (n_peers < 0 || n_peers > sgl::kMaxDst)
+    return fail(SGL_ERR_BAD_ARGUMENT, "n_peers=%d outside [0, %d]", n_peers, sgl::kMaxDst);
+  if (n_peers > 0 && !h_peers && !h_multicast)
+    return fail(SGL_ERR_NULL_POINTER, "h_peers is NULL");
+  void* dst[1] = {h_local};
+  PeerStores ps;
+  void* mc[1] = {h_multicast};
+  if (h_multicast) {
+    ps.mode = 2;
+    ps.n = 1;
+    ps.ptrs = mc;
+  } else if (n_peers > 0) {
+    ps.mode = 1;
+    ps.n = n_peers;
+    ps.ptrs = h_peers;
+  }
+  return fused_swiglu_impl(x, w, 0, dst, 1, nullptr, 0, M, N, K, ldx, ldw, ldh, up_col0,
+                           gate_col0, cfg, stream, &ps);
 }
 
 static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_dsts,

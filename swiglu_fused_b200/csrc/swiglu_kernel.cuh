@@ -127,6 +127,17 @@ struct KernelParams {
   int acc_cols;         // FORM_GEMM, single-CTA tiles, [k, n] weight: columns per tile (64, 128
                         // or 256).  Short problems with few 256-wide tiles are cut into
                         // narrower ones so that more SMs stream their own columns of B.
+  // Gather by thread stores (fused form): besides the TMA store into OutMaps.m[0], every
+  // finished chunk is copied from the staging buffer to n_peer raw destinations with ordinary
+  // 16-byte stores (peer_mode 1; peers' buffers over NVLink), or once to a multicast address
+  // (peer_mode 2; the switch replicates it into every member's buffer, this GPU's included, and
+  // the TMA store is skipped).  TMA stores to peers share the SM's TMA queue with the operand
+  // loads, and a store held up by the link then holds up the mainloop; thread stores only
+  // ever stall the epilogue warps, which have slack.
+  int peer_mode;        // 0 = off
+  int n_peer;
+  long long peer_ld;    // row pitch of the raw destinations, elements
+  unsigned long long peer_ptr[kMaxDst];   // element (0, 0) of this launch's block in each
   int a_rows;           // rows of the A box actually loaded per CTA and k-block: kBlockM, or the
                         // (8-aligned) row count of a problem shorter than one tile, whose
                         // missing rows would otherwise be fetched as zero fill at full cost
@@ -816,7 +827,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (x < p.N && y < p.M) {
+          if (x < p.N && y < p.M && p.peer_mode != 2) {
             // One store per destination buffer (local, then peers over NVLink), all
             // reading the same staging buffer; they form one bulk group.
             for (int d = 0; d < p.n_dst; ++d) ptx::tma_store_2d(&tm_h.m[d], x, y, obuf, pol_h);
@@ -827,6 +838,35 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             if (up_issued < total_chunks) {
               issue_up(up_issued);
               ++up_issued;
+            }
+          }
+        }
+        if constexpr (kForm == FORM_FUSED) {
+          if (p.peer_mode != 0) {
+            // Copy the chunk out of the staging buffer with thread stores: 8 lanes cover one
+            // 128-byte row, a warp instruction four rows; eight instructions per chunk and
+            // destination.  (The buffer is refilled two chunks later, after a __syncwarp.)
+            const int sub_row = lane >> 3, piece = lane & 7;
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int r = it * 4 + sub_row;
+              const uint32_t addr =
+                  obuf + static_cast<uint32_t>(r) * 128u +
+                  ((static_cast<uint32_t>(piece) ^ static_cast<uint32_t>(r & 7)) << 4);
+              uint32_t v0, v1, v2, v3;
+              asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                           : "=r"(v0), "=r"(v1), "=r"(v2), "=r"(v3)
+                           : "r"(addr));
+              const int grow = y + r, gcol = x + piece * 8;
+              if (grow < p.M && gcol < p.N) {
+                const long long off = (static_cast<long long>(grow) * p.peer_ld + gcol) * 2;
+                if (p.peer_mode == 2) {
+                  ptx::multimem_st_v4(reinterpret_cast<char*>(p.peer_ptr[0]) + off, v0, v1, v2, v3);
+                } else {
+                  for (int d = 0; d < p.n_peer; ++d)
+                    ptx::st_global_v4(reinterpret_cast<char*>(p.peer_ptr[d]) + off, v0, v1, v2, v3);
+                }
+              }
             }
           }
         }

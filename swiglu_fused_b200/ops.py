@@ -238,6 +238,38 @@ def matmul_fused_swiglu_multi_dst(A, W, dst_ptrs, ldh: int, *, up_col0: int, gat
     _lib.check(rc)
 
 
+def matmul_fused_swiglu_gather(A, W, local_ptr: int, peer_ptrs, ldh: int, *, up_col0: int,
+                               gate_col0: int, n_out: int, multicast_ptr: int | None = None,
+                               stream=None, config: TileConfig | None = None):
+    """Fused SwiGLU whose epilogue also hands every finished tile to other GPUs with ordinary
+    stores (``peer_ptrs``: element (0, 0) of this launch's block in each peer's buffer), or,
+    given ``multicast_ptr`` (that element in an NVSwitch multicast mapping of all the buffers),
+    with one ``multimem.st`` per 16 bytes that the switch replicates to every member.
+    ``local_ptr`` is the element in this GPU's own buffer.  The caller owns the buffers and the
+    cross-rank synchronisation (``sharding.fused_swiglu_n_sharded_fused_gather`` does both)."""
+    _check_matrix(A, "A")
+    _check_matrix(W, "W")
+    M, K = A.shape
+    if W.shape[0] != K:
+        raise ValueError(f"K mismatch: A.K={K} vs W.K={W.shape[0]}")
+    N = int(n_out)
+    if N < 1 or up_col0 < 0 or gate_col0 < 0 or max(up_col0, gate_col0) + N > W.shape[1]:
+        raise ValueError("column windows outside W")
+    if len(peer_ptrs) > 8:
+        raise ValueError(f"at most 8 peer destinations, got {len(peer_ptrs)}")
+    dev = _same_device(("A", A), ("W", W))
+    cfg = _pick_config(_lib.FORM_FUSED_SWIGLU, config, M, N, K)
+    cfg_c = cfg.to_c() if cfg is not None else None
+    arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[int(p) for p in peer_ptrs])
+    with torch.cuda.device(dev):
+        rc = _lib.load().sgl_matmul_fused_swiglu_gather(
+            A.data_ptr(), W.data_ptr(), int(local_ptr), arr, len(peer_ptrs),
+            int(multicast_ptr) if multicast_ptr else None, M, N, K, _ld(A), _ld(W), int(ldh),
+            int(up_col0), int(gate_col0), C.byref(cfg_c) if cfg_c is not None else None,
+            _stream_handle(stream, dev))
+    _lib.check(rc)
+
+
 def matmul_fused_swiglu_save_factors(A, W, *, out=None, factors=None, stream=None,
                                      config: TileConfig | None = None):
     """Training forward: returns ``(h, factors)`` with ``h`` as ``matmul_fused_swiglu`` and

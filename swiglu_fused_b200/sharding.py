@@ -80,17 +80,28 @@ class SymmetricOutput:
     objects are not requested - peers are reached with plain stores).  Collective:
     every rank of ``group`` constructs it with the same shape."""
 
-    def __init__(self, M: int, N: int, device, group=None):
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    def __init__(self, M: int, N: int, device, group=None, multicast: bool = False):
+        """``multicast=True`` also asks for an NVSwitch multicast mapping of the buffers
+        (``multicast_ptr``, 0 where the fabric offers none); the fused gather then sends every
+        tile once and the switch replicates it."""
         import torch.distributed._symmetric_memory as symm_mem
 
         self.M, self.N = M, N
         self.group = group if group is not None else dist.group.WORLD
-        self.tensor = symm_mem.empty((M, N), dtype=torch.bfloat16, device=device)
-        self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        before = os.environ.get("TORCH_SYMM_MEM_DISABLE_MULTICAST")
+        os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "0" if multicast else "1"
+        try:
+            self.tensor = symm_mem.empty((M, N), dtype=torch.bfloat16, device=device)
+            self.handle = symm_mem.rendezvous(self.tensor, self.group)
+        finally:
+            if before is None:
+                os.environ.pop("TORCH_SYMM_MEM_DISABLE_MULTICAST", None)
+            else:
+                os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = before
         self.rank = self.handle.rank
         self.world = self.handle.world_size
         self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0) if multicast else 0
 
     def barrier(self) -> None:
         """Device-side barrier across the ranks on the current stream."""
@@ -98,31 +109,56 @@ class SymmetricOutput:
 
 
 def fused_swiglu_n_sharded_fused_gather(x: torch.Tensor, w: torch.Tensor, out: SymmetricOutput, *,
-                                        n_total: int | None = None, stream=None, config=None):
+                                        n_total: int | None = None, stream=None, config=None,
+                                        mode: str = "auto"):
     """Column-parallel fused SwiGLU with the all-gather of ``h`` inside the kernel.
 
-    Every rank computes its column block and its epilogue stores each finished tile into
-    that column window of EVERY rank's ``out`` buffer (its own, then the peers' over
-    NVLink), so the transfer overlaps the remaining tiles.  Two device-side barriers
-    bracket the launch: nobody overwrites a buffer a peer may still be reading, and
-    nobody reads before every peer's stores have landed.  Returns ``out.tensor``
-    (the full ``[M, N]``) on every rank.
-    """
-    from .ops import matmul_fused_swiglu_multi_dst, stream_context
+    Every rank computes its column block and its epilogue delivers each finished tile into
+    that column window of EVERY rank's ``out`` buffer, so the transfer overlaps the remaining
+    tiles.  ``mode`` selects how the tiles travel:
 
+    * ``"multicast"``: one ``multimem.st`` per 16 bytes to the NVSwitch multicast mapping of
+      the buffers (``SymmetricOutput(..., multicast=True)``); the switch replicates, the
+      sender's link carries each byte once;
+    * ``"stores"``: the tile goes into this rank's buffer by TMA store and into each peer's by
+      ordinary 16-byte stores over NVLink;
+    * ``"tma"``: one TMA store per destination (the stores share the SM's TMA queue with the
+      operand loads, so a busy link slows the mainloop; kept for comparison);
+    * ``"auto"``: multicast where ``out`` has a mapping, else stores.
+
+    Two device-side barriers bracket the launch: nobody overwrites a buffer a peer may still
+    be reading, and nobody reads before every peer's stores have landed.  Returns
+    ``out.tensor`` (the full ``[M, N]``) on every rank; bit-identical in every mode.
+    """
+    from .ops import matmul_fused_swiglu_gather, matmul_fused_swiglu_multi_dst, stream_context
+
+    if mode not in ("auto", "multicast", "stores", "tma"):
+        raise ValueError(f"unknown gather mode {mode!r}")
+    if mode == "auto":
+        mode = "multicast" if out.multicast_ptr else "stores"
+    if mode == "multicast" and not out.multicast_ptr:
+        raise ValueError("this SymmetricOutput has no multicast mapping (construct it with "
+                         "multicast=True on a fabric that offers one)")
     N = n_total if n_total is not None else w.shape[1] // 2
     rank, world = out.rank, out.world
     mine = col_shard(N, world, rank)
+    ld = out.tensor.stride(0)
     # the two barriers run on torch's current stream: make that the launch stream
     with stream_context(stream, x.device):
         out.barrier()
         if mine.count > 0:
             # peers after this rank, nearest first: ranks start on different NVLink ports
             order = [(rank + i) % world for i in range(world)]
-            dsts = [out.ptrs[r] + 2 * mine.begin for r in order]
-            matmul_fused_swiglu_multi_dst(x, w, dsts, out.tensor.stride(0), up_col0=mine.begin,
-                                          gate_col0=N + mine.begin, n_out=mine.count,
-                                          stream=stream, config=config)
+            kw = dict(up_col0=mine.begin, gate_col0=N + mine.begin, n_out=mine.count,
+                      stream=stream, config=config)
+            if mode == "tma":
+                dsts = [out.ptrs[r] + 2 * mine.begin for r in order]
+                matmul_fused_swiglu_multi_dst(x, w, dsts, ld, **kw)
+            else:
+                peers = [out.ptrs[r] + 2 * mine.begin for r in order[1:]]
+                mc = out.multicast_ptr + 2 * mine.begin if mode == "multicast" else None
+                matmul_fused_swiglu_gather(x, w, out.ptrs[rank] + 2 * mine.begin, peers, ld,
+                                           multicast_ptr=mc, **kw)
         out.barrier()
     return out.tensor
 

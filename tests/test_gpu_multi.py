@@ -54,6 +54,13 @@ def _worker(rank, world, port, M, K, N, results):
         torch.cuda.synchronize()
         ok_f = ok_f and same(got, full_ref)
     ok_g = ok_g and ok_f
+    # the same gather by ordinary stores, by TMA stores, and (where the fabric offers a
+    # multicast mapping) by multimem stores that the switch replicates
+    for mode in ("stores", "tma"):
+        sym.tensor.zero_()
+        got = sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym, mode=mode)
+        torch.cuda.synchronize()
+        ok_g = ok_g and same(got, full_ref)
 
     # down projection with the reduce-scatter fused into the GEMM: y = h @ W_down from the
     # column-sharded h, every rank ends with the complete rows it owns
@@ -122,6 +129,26 @@ def _worker(rank, world, port, M, K, N, results):
     _lib.device_status()
     flags = torch.tensor([int(ok_m), int(ok_n), int(ok_g)], dtype=torch.int64, device=dev)
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    if flags.cpu().tolist() == [1, 1, 1]:
+        # Last, and only when every rank has passed everything above: the gather through an
+        # NVSwitch multicast mapping (skipped where the fabric offers none).  The mapping is
+        # released before the ranks leave.
+        sym_mc = sharding.SymmetricOutput(M, N, dev, multicast=True)
+        has_mc = torch.tensor([int(bool(sym_mc.multicast_ptr))], dtype=torch.int64, device=dev)
+        dist.all_reduce(has_mc, op=dist.ReduceOp.MIN)
+        if has_mc.item():
+            ok_mc = True
+            for _ in range(2):
+                sym_mc.tensor.zero_()
+                got = sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym_mc, mode="multicast")
+                torch.cuda.synchronize()
+                ok_mc = ok_mc and same(got, full_ref)
+            _lib.device_status()
+            mc = torch.tensor([int(ok_mc)], dtype=torch.int64, device=dev)
+            dist.all_reduce(mc, op=dist.ReduceOp.MIN)
+            flags[2] = mc[0]
+        dist.barrier()
+        del sym_mc
     if rank == 0:
         results.put(flags.cpu().tolist())
     dist.barrier()

@@ -394,3 +394,35 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
     ref32 = orc.fused_swiglu_f32(inp["x"], inp["w"])
     h = matmul_fused_swiglu(inp["x"].to(DEV), inp["w"].to(DEV))
     assert orc.compare(h.cpu(), ref32.to(torch.bfloat16), ref32).ok
+
+
+@pytest.mark.parametrize("M,K,N,window", [(512, 256, 1024, (256, 384)), (200, 136, 264, (64, 136)),
+                                          (1000, 264, 1160, (384, 392))])
+def test_gather_epilogues_write_every_destination(M, K, N, window):
+    """The column-parallel gather on one GPU: the "peers" are further buffers of this GPU.
+    Every destination (TMA stores to each, or TMA store + ordinary 16-byte stores) must hold
+    the column block, bit for bit, in its window of a full-width buffer, and nothing else may
+    be touched (NaN sentinels around the window stay)."""
+    from swiglu_fused_b200.ops import matmul_fused_swiglu_gather, matmul_fused_swiglu_multi_dst
+
+    c0, n = window
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + N)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    want = matmul_fused_swiglu(x, w, up_col0=c0, gate_col0=N + c0, n_out=n)
+    for mode in ("tma", "stores"):
+        bufs = [torch.full((M + 8, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+                for _ in range(4)]
+        ptrs = [b.data_ptr() + 2 * c0 for b in bufs]
+        kw = dict(up_col0=c0, gate_col0=N + c0, n_out=n)
+        if mode == "tma":
+            matmul_fused_swiglu_multi_dst(x, w, ptrs, N, **kw)
+        else:
+            matmul_fused_swiglu_gather(x, w, ptrs[0], ptrs[1:], N, **kw)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        for i, b in enumerate(bufs):
+            assert torch.equal(b[:M, c0:c0 + n].contiguous().view(torch.int16),
+                               want.view(torch.int16)), (mode, i)
+            rest = b.clone()
+            rest[:M, c0:c0 + n] = float("nan")
+            assert bool(torch.isnan(rest.float()).all()), (mode, i)
