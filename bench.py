@@ -104,7 +104,7 @@ class ClockSampler(threading.Thread):
     def __init__(self, index: int, period_s: float = 0.002):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
-        self.samples, self.mask, self.max_mhz = [], 0, None
+        self.samples, self.max_mhz = [], None
         self._stop_evt = threading.Event()
         self.ready = threading.Event()      # NVML is up: samples from now on
         self.error = None
@@ -117,25 +117,42 @@ class ClockSampler(threading.Thread):
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
             self.ready.set()
             while not self._stop_evt.is_set():
-                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
-                self.mask |= int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                self.samples.append((time.perf_counter(), mhz, mask))
                 time.sleep(self.period)
         except Exception as e:  # NVML missing: report, do not fail the benchmark
             self.error = repr(e)
             self.ready.set()
 
     def begin(self) -> None:
-        """Called right before the timed region: wait for NVML, drop what was sampled before."""
+        """Called right before the timed region: wait for NVML and note the time."""
         self.ready.wait(timeout=10)
-        self.samples, self.mask = [], 0
+        self.t_begin = time.perf_counter()
 
     def stop(self) -> dict:
+        """Called right after the timed region.  Reports the samples taken inside it; a region
+        shorter than one NVML query (several ranks querying at once take milliseconds each) may
+        hold none, and then the samples next to it, taken while the same kernel ran as warm-up
+        or just after, stand in and the record says so."""
+        t_end = time.perf_counter()
         self._stop_evt.set()
         self.join(timeout=2)
-        s = sorted(self.samples)
-        reasons = [n for b, n in self.REASONS.items() if self.mask & b and n != "gpu_idle"]
+        t0 = getattr(self, "t_begin", 0.0)
+        inside = [v for v in self.samples if t0 <= v[0] <= t_end]
+        used, where = inside, "inside the timed region"
+        if not inside:
+            before = [v for v in self.samples if v[0] < t0][-2:]
+            after = [v for v in self.samples if v[0] > t_end][:1]
+            used, where = before + after, "adjacent to the timed region (shorter than one query)"
+        s = sorted(v[1] for v in used)
+        mask = 0
+        for v in used:
+            mask |= v[2]
+        reasons = [n for b, n in self.REASONS.items() if mask & b and n != "gpu_idle"]
         out = {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
-               "sm_min_mhz": s[0] if s else None, "reasons": reasons, "samples": len(s)}
+               "sm_min_mhz": s[0] if s else None, "reasons": reasons, "samples": len(s),
+               "sampled": where}
         if self.error:
             out["error"] = self.error
         return out

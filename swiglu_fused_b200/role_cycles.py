@@ -2,6 +2,8 @@
 
     python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|fused_swiglu_save|silu_mul] [--rows M]
                                             [--block-k 64|128] [--group-m G]
+    torchrun --nproc-per-node W -m swiglu_fused_b200.role_cycles --k 8192 --n 28672 \
+             --gather none|tma|stores|multicast      # column-parallel over W GPUs, rank 0 reports
 
 Builds a second copy of the library with ``-DSGL_PROFILE`` (``libswiglu_b200_prof.so``, next to
 the normal one), in which every role of ``swiglu_kernel`` adds up, per CTA, the SM cycles it
@@ -45,6 +47,10 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=12288)
     ap.add_argument("--block-k", type=int, default=0, help="0 = the default configuration")
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--gather", choices=("none", "tma", "stores", "multicast"), default=None,
+                    help="column-parallel launch over the ranks of a torchrun group: each rank "
+                         "computes N / world columns; 'none' keeps them local, the others "
+                         "gather h into every rank inside the kernel by that mode")
     args = ap.parse_args()
 
     os.environ["SWIGLU_B200_LIB"] = build_profile_library()
@@ -54,7 +60,13 @@ def main() -> None:
     from . import _lib
     from .ops import matmul_fused_swiglu, matmul_fused_swiglu_save_factors, matmul_silu_mul
 
+    rank, world, sym = 0, 1, None
     dev = torch.device("cuda:0")
+    if args.gather is not None:
+        from . import sharding
+        rank, world, local_rank = sharding.init_from_env("nccl")
+        dev = torch.device("cuda", local_rank)
+        torch.cuda.set_device(dev)
     M, K, N = args.rows, args.k, args.n
     g = torch.Generator(device=dev).manual_seed(0)
     x = torch.randn((M, K), device=dev, dtype=torch.bfloat16, generator=g)
@@ -66,7 +78,21 @@ def main() -> None:
     if args.block_k or args.group_m:
         cfg = _lib.TileConfig(cfg.cta_group, args.block_k or cfg.block_k, 0,
                               args.group_m or cfg.group_m)
-    if args.form == "fused_swiglu":
+    if args.gather is not None:
+        import torch.distributed as dist
+        cols = sharding.col_shard(N, world, rank)
+        cfg = _lib.default_config(form, M, cols.count, K)
+        if args.gather == "none":
+            local = torch.empty((M, cols.count), device=dev, dtype=torch.bfloat16)
+
+            def run():
+                sharding.fused_swiglu_n_sharded(x, w, rank=rank, world=world, out=local, config=cfg)
+        else:
+            sym = sharding.SymmetricOutput(M, N, dev, multicast=args.gather == "multicast")
+
+            def run():
+                sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym, mode=args.gather, config=cfg)
+    elif args.form == "fused_swiglu":
         def run():
             matmul_fused_swiglu(x, w, out=out, config=cfg)
     elif args.form == "fused_swiglu_save":
@@ -87,6 +113,9 @@ def main() -> None:
     for _ in range(20):
         run()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+        torch.cuda.synchronize()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
     run()
@@ -100,9 +129,16 @@ def main() -> None:
     loop = lead[:, 2]
     tiles = np.maximum(lead[:, 7], 1)
     kblocks = tiles * (-(-K // 64))
-    print(f"{args.form} {M}x{K}x{N} {cfg}: {t0.elapsed_time(t1):.3f} ms")
-    print(f"  MMA loop {loop.mean():.0f} clk per CTA; {(loop / kblocks).mean():.0f} clk per 64-k "
-          f"block (tensor-core ideal 512)")
+    if rank != 0:
+        dist.barrier()
+        dist.destroy_process_group()
+        return
+    what = args.form if args.gather is None else \
+        f"column-parallel x{world} (gather: {args.gather}), {N // world} columns per GPU,"
+    ms = t0.elapsed_time(t1)
+    print(f"{what} {M}x{K}x{N} {cfg}: {ms:.3f} ms")
+    print(f"  MMA loop {loop.mean():.0f} clk per CTA = {loop.mean() / (ms * 1e3):.0f} MHz x the "
+          f"launch time; {(loop / kblocks).mean():.0f} clk per 64-k block (tensor-core ideal 512)")
     print(f"  MMA issuer waits: free accumulator {100 * (lead[:, 0] / loop).mean():.1f} %, "
           f"operands {100 * (lead[:, 1] / loop).mean():.1f} %")
     print(f"  TMA producer waits for a ring slot {100 * p[:, 3].mean() / loop.mean():.1f} %")
@@ -111,6 +147,9 @@ def main() -> None:
           f"{100 * p[:, 6].mean() / loop.mean():.1f} %")
     print(f"  load balance: slowest / mean CTA = {loop.max() / loop.mean():.4f}, "
           f"tiles per CTA {int(tiles.min())}..{int(tiles.max())}")
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
