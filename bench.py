@@ -83,7 +83,7 @@ def profiled_traffic(form_name: str, M: int, N: int, K: int, cfg) -> float | Non
     if not os.path.exists(TRAFFIC_PROFILE):
         return None
     key = (f"{form_name}:{M}x{N}x{K} cta_group={cfg.cta_group} block_k={cfg.block_k} "
-           f"group_m={cfg.group_m}")
+           f"group_m={cfg.group_m}" + (f" group_n={cfg.group_n}" if cfg.group_n else ""))
     with open(TRAFFIC_PROFILE) as f:
         for ln in f:
             m = re.match(r"\s*`?traffic\[(.+?)\]\s*=\s*([0-9.eE+]+)", ln)
@@ -567,7 +567,8 @@ def run_ours(args) -> None:
         m_total, k_dim, n_out = (int(v) for v in args.shape.lower().split("x"))
     if args.rows:
         m_total = args.rows
-    headline = (m_total, k_dim, n_out) == (M_TOTAL, K_DIM, N_OUT) and args.form == "fused_swiglu"
+    headline = (m_total, k_dim, n_out) == (M_TOTAL, K_DIM, N_OUT) and \
+        args.form == "fused_swiglu" and not args.tile_config
     rows = sharding.row_shard(m_total, world, rank)
     # Same global tensors on every rank (seeded CUDA generator); each keeps its rows.
     inp = make_inputs(m_total, k_dim, n_out, form="fused_swiglu", seed=0, device=dev,
@@ -593,6 +594,11 @@ def run_ours(args) -> None:
         del h_single
     del x_full, inp
 
+    pinned = None
+    if args.tile_config:
+        v = [int(t) for t in args.tile_config.split(",")]
+        pinned = _lib.TileConfig(v[0], v[1], 0, v[2], 0, v[3] if len(v) > 3 else 0,
+                                 v[4] if len(v) > 4 else 0)
     if args.form == "silu_mul":
         # Profiling aid: time the reference's other operator instead (W_gate = right half of
         # the packed weight, up = x @ W_up precomputed outside the timed region).
@@ -602,12 +608,12 @@ def run_ours(args) -> None:
         form_id, form_name = _lib.FORM_SILU_MUL, "silu_mul"
 
         def step():
-            matmul_silu_mul(x, w_gate, up, out=h)
+            matmul_silu_mul(x, w_gate, up, out=h, config=pinned)
     else:
         form_id, form_name = _lib.FORM_FUSED_SWIGLU, "fused_swiglu"
 
         def step():
-            matmul_fused_swiglu(x, w, out=h)
+            matmul_fused_swiglu(x, w, out=h, config=pinned)
 
     warmup = max(args.warmup, 3)
     for _ in range(warmup):
@@ -727,7 +733,7 @@ def run_ours(args) -> None:
     burst = region_s < 1.0
     peak = peaks["tflops_burst"] if burst else peaks["tflops_sustained"]
     achieved = flops_local / (elapsed_ms / args.steps * 1e-3) / 1e12   # this rank's kernel
-    cfg_used = tile_table.lookup(form_id, rows.count, n_out, k_dim) or \
+    cfg_used = pinned or tile_table.lookup(form_id, rows.count, n_out, k_dim) or \
         _lib.default_config(form_id, rows.count, n_out, k_dim)
     if headline:
         workload = WORKLOAD
@@ -746,7 +752,8 @@ def run_ours(args) -> None:
                    "rows_per_gpu": rows.count,
                    "parallelism": f"M-sharded x{world}, weights replicated, no collective",
                    "tile_config": {"cta_group": cfg_used.cta_group, "block_k": cfg_used.block_k,
-                                   "group_m": cfg_used.group_m, "l2_hints": cfg_used.l2_hints},
+                                   "group_m": cfg_used.group_m, "l2_hints": cfg_used.l2_hints,
+                                   "group_n": cfg_used.group_n},
                    "l2": "inputs+output larger than L2 (x+W+h per GPU = "
                          f"{(x.numel() + w.numel() + h.numel()) * 2 / 1e6:.0f} MB > 126 MB), no flush"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak,
@@ -828,6 +835,9 @@ def main() -> None:
                          "weights N(0, 0.02)); the JSON line then says so and carries no legs")
     ap.add_argument("--form", choices=("fused_swiglu", "silu_mul"), default="fused_swiglu",
                     help="operator to time; silu_mul is a profiling aid, the headline is fused_swiglu")
+    ap.add_argument("--tile-config", default="",
+                    help="cta_group,block_k,group_m,l2_hints,group_n: pin the tile configuration "
+                         "of the timed operator (profiling aid; default = tile table / library)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-gpu-baselines", action="store_true",
                     help="skip the cuBLAS (+ eager / compiled activation) comparisons and the "

@@ -67,7 +67,11 @@ typedef struct sgl_config {
   int32_t l2_hints;  /* L2 eviction priorities, 2 bits each: bits 0-1 x loads, 2-3 weight
                         loads, 4-5 h stores, 6-7 `up` loads; 0 normal, 1 evict-first,
                         2 evict-last.  0 = all normal. */
-  int32_t reserved[2];
+  int32_t group_n;   /* column slabs of the tile order, in tiles: the tile columns are walked in
+                        slabs of group_n, all row bands of one slab before the next slab, so
+                        that a slab of the weight stays in L2 while x streams past it;
+                        0 = one slab (plain GROUP_SIZE_M order) */
+  int32_t reserved;  /* must be 0 */
 } sgl_config;
 
 /*
@@ -292,6 +296,9 @@ int sgl_config_smem_bytes(int form, const sgl_config* cfg);
  */
 int sgl_tile_coord(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m, int64_t* tile_m,
                    int64_t* tile_n);
+/* The same with column slabs of group_n tiles (sgl_config.group_n; 0 = one slab). */
+int sgl_tile_coord_slabs(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m,
+                         int64_t group_n, int64_t* tile_m, int64_t* tile_n);
 
 /* Queries about the current device (no counterpart in the reference). */
 enum {

@@ -55,6 +55,7 @@ EXPORTED_SYMBOLS = (
     "sgl_config_default",
     "sgl_config_smem_bytes",
     "sgl_tile_coord",
+    "sgl_tile_coord_slabs",
     "sgl_query",
     "sgl_shard_range",
     "sgl_device_status",
@@ -85,7 +86,8 @@ class SglConfig(C.Structure):
         ("group_m", C.c_int32),
         ("max_ctas", C.c_int32),
         ("l2_hints", C.c_int32),
-        ("reserved", C.c_int32 * 2),
+        ("group_n", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -103,14 +105,16 @@ class TileConfig:
     group_m: int = 8
     max_ctas: int = 0
     l2_hints: int = 0   # see sgl_config.l2_hints: 2 bits each for x, weight, h, up
+    group_n: int = 0    # column slabs of the tile order, in tiles (0 = one slab)
 
     def to_c(self) -> SglConfig:
         return SglConfig(self.cta_group, self.block_k, self.stages, self.group_m, self.max_ctas,
-                         self.l2_hints, (C.c_int32 * 2)(0, 0))
+                         self.l2_hints, self.group_n, 0)
 
     @staticmethod
     def from_c(c: SglConfig) -> "TileConfig":
-        return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas, c.l2_hints)
+        return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas, c.l2_hints,
+                          c.group_n)
 
 
 class SglError(RuntimeError):
@@ -200,6 +204,9 @@ def load() -> C.CDLL:
         lib.sgl_config_smem_bytes.argtypes = [ip, cfgp]
         lib.sgl_tile_coord.restype = ip
         lib.sgl_tile_coord.argtypes = [i64, i64, i64, i64, C.POINTER(i64), C.POINTER(i64)]
+        lib.sgl_tile_coord_slabs.restype = ip
+        lib.sgl_tile_coord_slabs.argtypes = [i64, i64, i64, i64, i64, C.POINTER(i64),
+                                             C.POINTER(i64)]
         lib.sgl_query.restype = ip
         lib.sgl_query.argtypes = [ip, C.POINTER(i64)]
         lib.sgl_shard_range.restype = ip
@@ -289,8 +296,13 @@ def config_smem_bytes(form: int, cfg: TileConfig) -> int:
     return n
 
 
-def tile_coord(t: int, tiles_m: int, tiles_n: int, group_m: int) -> tuple[int, int]:
+def tile_coord(t: int, tiles_m: int, tiles_n: int, group_m: int,
+               group_n: int = 0) -> tuple[int, int]:
     m, n = C.c_int64(), C.c_int64()
+    if group_n:
+        check(load().sgl_tile_coord_slabs(t, tiles_m, tiles_n, group_m, group_n, C.byref(m),
+                                          C.byref(n)))
+        return m.value, n.value
     check(load().sgl_tile_coord(t, tiles_m, tiles_n, group_m, C.byref(m), C.byref(n)))
     return m.value, n.value
 

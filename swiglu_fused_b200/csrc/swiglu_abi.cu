@@ -176,18 +176,19 @@ const Variant& variant(int form, int cta_group, int block_k) {
 bool config_fields_ok(const sgl_config& c) {
   return (c.cta_group == 1 || c.cta_group == 2) && (c.block_k == 64 || c.block_k == 128) &&
          c.stages >= 0 && c.stages <= sgl::kMaxStages && c.group_m >= 1 && c.max_ctas >= 0 &&
+         c.group_n >= 0 && c.reserved == 0 &&
          c.l2_hints >= 0 && c.l2_hints < 256 && (c.l2_hints & 3) != 3 &&
          ((c.l2_hints >> 2) & 3) != 3 && ((c.l2_hints >> 4) & 3) != 3 && ((c.l2_hints >> 6) & 3) != 3;
 }
 
 // Built-in tile table (cta_group, block_k, stages (0 = deepest), group_m, max_ctas, l2_hints).
 const sgl_config kTable[] = {
-    {2, 64, 0, 8, 0, 0, {0, 0}},  {2, 64, 0, 4, 0, 0, {0, 0}},  {2, 64, 0, 16, 0, 0, {0, 0}},
-    {2, 64, 0, 1, 0, 0, {0, 0}},  {2, 64, 0, 32, 0, 0, {0, 0}}, {2, 128, 0, 8, 0, 0, {0, 0}},
-    {2, 128, 0, 16, 0, 0, {0, 0}}, {1, 64, 0, 8, 0, 0, {0, 0}}, {1, 64, 0, 16, 0, 0, {0, 0}},
-    {1, 64, 0, 1, 0, 0, {0, 0}},  {1, 128, 0, 8, 0, 0, {0, 0}},
+    {2, 64, 0, 8, 0, 0, 0, 0},  {2, 64, 0, 4, 0, 0, 0, 0},  {2, 64, 0, 16, 0, 0, 0, 0},
+    {2, 64, 0, 1, 0, 0, 0, 0},  {2, 64, 0, 32, 0, 0, 0, 0}, {2, 128, 0, 8, 0, 0, 0, 0},
+    {2, 128, 0, 16, 0, 0, 0, 0}, {1, 64, 0, 8, 0, 0, 0, 0}, {1, 64, 0, 16, 0, 0, 0, 0},
+    {1, 64, 0, 1, 0, 0, 0, 0},  {1, 128, 0, 8, 0, 0, 0, 0},
     // x loads evict-last + output stores evict-first (l2_hints = 2 | 1 << 4)
-    {2, 128, 0, 16, 0, 18, {0, 0}}, {2, 64, 0, 16, 0, 18, {0, 0}}, {2, 128, 0, 12, 0, 18, {0, 0}},
+    {2, 128, 0, 16, 0, 18, 0, 0}, {2, 64, 0, 16, 0, 18, 0, 0}, {2, 128, 0, 12, 0, 18, 0, 0},
 };
 constexpr int kTableSize = static_cast<int>(sizeof(kTable) / sizeof(kTable[0]));
 
@@ -434,6 +435,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.tiles_m = static_cast<int>(tiles_m);
   p.tiles_n = static_cast<int>(tiles_n);
   p.group_m = cfg.group_m;
+  p.group_n = cfg.group_n;
   p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
   p.n_dst = s.n_dst;
@@ -1123,6 +1125,20 @@ int sgl_tile_coord(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m,
     return fail(SGL_ERR_BAD_ARGUMENT, "tile index or grid out of range");
   sgl::TileCoord c = sgl::tile_coord(static_cast<int>(t), static_cast<int>(tiles_m),
                                      static_cast<int>(tiles_n), static_cast<int>(group_m));
+  *tile_m = c.m;
+  *tile_n = c.n;
+  return SGL_OK;
+}
+
+int sgl_tile_coord_slabs(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m,
+                         int64_t group_n, int64_t* tile_m, int64_t* tile_n) {
+  if (!tile_m || !tile_n) return fail(SGL_ERR_NULL_POINTER, "output pointer is NULL");
+  if (tiles_m < 1 || tiles_n < 1 || group_m < 1 || group_n < 0 || t < 0 ||
+      t >= tiles_m * tiles_n || tiles_m * tiles_n > 0x7fffffffll)
+    return fail(SGL_ERR_BAD_ARGUMENT, "tile index or grid out of range");
+  sgl::TileCoord c = sgl::tile_coord(static_cast<int>(t), static_cast<int>(tiles_m),
+                                     static_cast<int>(tiles_n), static_cast<int>(group_m),
+                                     static_cast<int>(group_n > tiles_n ? 0 : group_n));
   *tile_m = c.m;
   *tile_n = c.n;
   return SGL_OK;

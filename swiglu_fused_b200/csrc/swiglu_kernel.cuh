@@ -107,6 +107,7 @@ struct KernelParams {
   int b_col1;           // fused form: first gate column of the packed weight
   int tiles_m, tiles_n; // tile grid in cluster-tile units
   int group_m;          // GROUP_SIZE_M
+  int group_n;          // column slabs of the tile order (0 = one slab)
   int stages;           // shared-memory ring depth actually used
   int l2_hints;         // 2 bits each: x loads, weight loads, h stores, up loads
   int n_dst;            // destinations in OutMaps actually used (>= 1)
@@ -192,15 +193,29 @@ struct TileCoord {
 // fastest inside a band, so concurrently running tiles share x rows and weight
 // columns in L2.  Equivalent in purpose to swiglu/_matmul_silu_mul.cu:357-384,
 // applied to the persistent schedule's linear tile index.
-__host__ __device__ inline TileCoord tile_coord(int t, int tiles_m, int tiles_n, int group_m) {
-  const int per_band = group_m * tiles_n;
+//
+// group_n > 0 adds an outer level: the tile columns are cut into slabs of group_n tiles and all
+// row bands of one slab are walked before the next slab.  A slab of the weight (group_n tile
+// columns, every k) then stays in L2 while the bands of x stream past it, instead of the whole
+// weight being fetched from DRAM again for every band.
+__host__ __device__ inline TileCoord tile_coord(int t, int tiles_m, int tiles_n, int group_m,
+                                                int group_n = 0) {
+  int first_n = 0, cols = tiles_n;
+  if (group_n > 0 && group_n < tiles_n) {
+    const int per_slab = tiles_m * group_n;
+    const int slab = t / per_slab;
+    first_n = slab * group_n;
+    cols = (tiles_n - first_n) < group_n ? (tiles_n - first_n) : group_n;
+    t -= slab * per_slab;
+  }
+  const int per_band = group_m * cols;
   const int band = t / per_band;
   const int first_m = band * group_m;
   const int rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
   const int in_band = t - band * per_band;
   TileCoord c;
   c.m = first_m + in_band % rows;
-  c.n = in_band / rows;
+  c.n = first_n + in_band / rows;
   return c;
 }
 
@@ -284,7 +299,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const int splits = (kForm == FORM_GEMM) ? p.splits : 1;
   const int total_tiles = p.tiles_m * p.tiles_n * splits;
   auto shifted_tile = [&](int t) {
-    TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m);
+    TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m, p.group_n);
     tc.m += p.m_shift;
     if (tc.m >= p.tiles_m) tc.m -= p.tiles_m;
     return tc;

@@ -2,7 +2,7 @@
 
     python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|fused_swiglu_save|silu_mul] [--rows M]
                                             [--block-k 64|128] [--group-m G]
-    torchrun --nproc-per-node W -m swiglu_fused_b200.role_cycles --k 8192 --n 28672 \
+    torchrun --nproc-per-node W -m swiglu_fused_b200.role_cycles --k 8192 --cols 28672 \
              --gather none|tma|stores|multicast      # column-parallel over W GPUs, rank 0 reports
 
 Builds a second copy of the library with ``-DSGL_PROFILE`` (``libswiglu_b200_prof.so``, next to
@@ -44,7 +44,7 @@ def main() -> None:
                     default="fused_swiglu")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--k", type=int, default=3072)
-    ap.add_argument("--n", type=int, default=12288)
+    ap.add_argument("--n", "--cols", dest="n", type=int, default=12288)
     ap.add_argument("--block-k", type=int, default=0, help="0 = the default configuration")
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--gather", choices=("none", "tma", "stores", "multicast"), default=None,

@@ -139,6 +139,30 @@ def test_tile_order_is_a_bijection_and_matches_the_model(tiles_m, tiles_n, group
         _lib.tile_coord(tiles_m * tiles_n, tiles_m, tiles_n, group_m)
 
 
+def model_tile_coord_slabs(t, tiles_m, tiles_n, group_m, group_n):
+    """Independent model of the slab order: column slabs outermost, then row bands."""
+    order = []
+    for n0 in range(0, tiles_n, group_n):
+        cols = range(n0, min(tiles_n, n0 + group_n))
+        for m0 in range(0, tiles_m, group_m):
+            rows = range(m0, min(tiles_m, m0 + group_m))
+            order += [(m, n) for n in cols for m in rows]
+    return order[t]
+
+
+@pytest.mark.parametrize("tiles_m,tiles_n,group_m,group_n", [
+    (128, 96, 16, 48), (128, 96, 16, 32), (7, 5, 4, 2), (9, 3, 16, 2), (10, 7, 3, 3), (5, 1, 2, 1),
+    (4, 9, 2, 9), (4, 9, 2, 20),
+])
+def test_slab_tile_order_is_a_bijection_and_matches_the_model(tiles_m, tiles_n, group_m, group_n):
+    seen = set()
+    for t in range(tiles_m * tiles_n):
+        mn = _lib.tile_coord(t, tiles_m, tiles_n, group_m, group_n)
+        assert mn == model_tile_coord_slabs(t, tiles_m, tiles_n, group_m, min(group_n, tiles_n))
+        seen.add(mn)
+    assert len(seen) == tiles_m * tiles_n
+
+
 def test_tile_order_keeps_a_band_of_rows_together():
     # the first group_m*tiles_n tiles touch only the first group_m tile rows
     tiles_m, tiles_n, g = 128, 96, 8
