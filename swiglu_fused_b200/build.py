@@ -48,6 +48,24 @@ def is_stale() -> bool:
     return any(os.path.getmtime(p) > built for p in SOURCES + HEADERS if os.path.exists(p))
 
 
+DEBUG_LIB_PATH = os.path.join(PKG_DIR, "libswiglu_b200_debug.so")
+
+
+def build_debug_library(force: bool = False) -> str:
+    """The self-checking build (``-DSGL_DEBUG``): every TMA coordinate is checked before the
+    copy is issued and every kernel role counts its work; violations are recorded in the
+    status words, nothing traps.  Load it with ``SWIGLU_B200_LIB=<path>``."""
+    srcs = [p for p in SOURCES + HEADERS if os.path.exists(p)]
+    if not force and os.path.exists(DEBUG_LIB_PATH) and \
+            all(os.path.getmtime(p) <= os.path.getmtime(DEBUG_LIB_PATH) for p in srcs):
+        return DEBUG_LIB_PATH
+    cmd = [find_nvcc(), *NVCC_FLAGS, "-DSGL_DEBUG", "-o", DEBUG_LIB_PATH, *SOURCES]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({proc.returncode}):\n{proc.stdout}\n{proc.stderr}")
+    return DEBUG_LIB_PATH
+
+
 def build_library(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if it is missing or stale; return its path."""
     if not force and not is_stale():

@@ -70,6 +70,7 @@ enum : unsigned {
   kErrMmaTmemEmptyWait = 0x103,
   kErrEpiTmemFullWait = 0x104,
   kErrEpiUpWait = 0x105,
+  kErrDebugCoord = 0x301,     // -DSGL_DEBUG builds: a TMA coordinate failed its check
   kErrSelfTestWait = 0x1ff,   // the deliberate timeout of wait_timeout_selftest_kernel
 };
 
@@ -99,6 +100,28 @@ __device__ unsigned long long g_prof[512][8];
 #define SGL_PROF_BEGIN(t)
 #define SGL_PROF_END(acc, t)
 #define SGL_PROF_STORE(slot, v)
+#endif
+
+// Self-checking build (-DSGL_DEBUG; compute-sanitizer is not available everywhere): every TMA
+// coordinate is checked against the 16-byte rule and the tensor's extent before the copy is
+// issued, and every role counts what it did.  A violation is RECORDED (g_status, code
+// kErrDebugCoord) and the copy skipped - nothing traps - and the host compares the role
+// counters afterwards (sgl_debug_counts): k-blocks produced must equal k-blocks consumed, tiles
+// finished by the epilogue must equal tiles issued.  The normal library carries none of this.
+#ifdef SGL_DEBUG
+__device__ unsigned long long g_debug_counts[512][4];   // [cta]: produced, consumed, tiles, stores
+#define SGL_DBG_COUNT(slot, v) g_debug_counts[blockIdx.x & 511][slot] = static_cast<unsigned long long>(v)
+#define SGL_DBG_CHECK_COORD(ok_expr, detail)                                  \
+  if (!(ok_expr)) {                                                           \
+    if (atomicCAS(&g_status[0], 0u, 0x301u) == 0u) {                          \
+      g_status[1] = blockIdx.x;                                               \
+      g_status[2] = static_cast<unsigned>(detail);                            \
+    }                                                                         \
+    atomicAdd(&g_status[3], 1u);                                              \
+  }
+#else
+#define SGL_DBG_COUNT(slot, v)
+#define SGL_DBG_CHECK_COORD(ok_expr, detail)
 #endif
 
 struct KernelParams {
@@ -139,6 +162,10 @@ struct KernelParams {
   int n_peer;
   long long peer_ld;    // row pitch of the raw destinations, elements
   unsigned long long peer_ptr[kMaxDst];   // element (0, 0) of this launch's block in each
+  int a_stage_bytes;    // bytes one ring stage reserves for the A tile: kBlockM * kBlockK * 2, or
+                        // a_rows * kBlockK * 2 when a short problem gives the room to more stages
+  int out_bufs;         // staging buffers per epilogue warp, fused form: 2, or 1 when every CTA
+                        // has a single tile (nothing to overlap) and the room goes to the ring
   int a_rows;           // rows of the A box actually loaded per CTA and k-block: kBlockM, or the
                         // (8-aligned) row count of a problem shorter than one tile, whose
                         // missing rows would otherwise be fetched as zero fill at full cost
@@ -327,9 +354,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = smem_base;
-  const uint32_t sB = sA + stages * T::kAStageBytes;
+  const uint32_t a_stage = static_cast<uint32_t>(p.a_stage_bytes);
+  const uint32_t sB = sA + stages * a_stage;
   const uint32_t sOut = sB + stages * T::kBStageBytes;
-  const uint32_t sUp = sOut + T::kOutStagingBytes;
+  const uint32_t out_bufs = (kForm == FORM_FUSED) ? static_cast<uint32_t>(p.out_bufs)
+                                                  : static_cast<uint32_t>(kOutBufs);
+  const uint32_t sUp =
+      sOut + ((kForm == FORM_FUSED) ? kEpiWarps * out_bufs * kChunkBytes : T::kOutStagingBytes);
   const uint32_t sBar = sUp + T::kUpStagingBytes;
   const uint32_t bar_full = sBar;                       // [kMaxStages]
   const uint32_t bar_empty = bar_full + 8 * kMaxStages; // [kMaxStages]
@@ -385,6 +416,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
+#ifdef SGL_DEBUG
+      unsigned long long dbg_produced = 0;
+#endif
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters) {
         const TileCoord tc = shifted_tile(t / splits);
         const int m0 = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM;
@@ -407,7 +441,14 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
           ptx::mbar_arrive_expect_tx_cluster(full, stage_tx);
           const int k0 = k_base + kb * kBlockK;
-          const uint32_t a_dst = sA + s * T::kAStageBytes;
+          SGL_DBG_CHECK_COORD(k0 >= 0 && k0 < p.K && (k0 & 7) == 0 && m0 >= 0 &&
+                                  m0 < p.tiles_m * kCtaGroup * kBlockM && n0 >= 0 && (n0 & 7) == 0 &&
+                                  ((p.b_col0 | p.b_col1) & 7) == 0,
+                              kb);
+#ifdef SGL_DEBUG
+          ++dbg_produced;
+#endif
+          const uint32_t a_dst = sA + s * a_stage;
           if (p.a_mnmajor) {
             // A stored [k, m]: two slabs of 64 m-columns x kBlockK k-rows, like the weight.
 #pragma unroll
@@ -418,8 +459,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockK / 64; ++j) {
-              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64,
-                                               m0, full, pol_x);
+              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (a_stage / (kBlockK / 64)), &tm_x,
+                                               k0 + j * 64, m0, full, pol_x);
             }
           }
           const uint32_t b_dst = sB + s * T::kBStageBytes;
@@ -466,6 +507,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
       }
       SGL_PROF_STORE(3, prof_pe);
+      SGL_DBG_COUNT(0, dbg_produced);
       if (!ok) {
         // Give loads that are still in flight time to land before the CTA exits.
         const uint64_t t0 = ptx::globaltimer_ns();
@@ -486,6 +528,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       uint32_t ph = 0;
       bool ok = true;
       int i = 0;
+#ifdef SGL_DEBUG
+      unsigned long long dbg_consumed = 0;
+#endif
       SGL_PROF_DECL(prof_te);
       SGL_PROF_DECL(prof_fu);
       SGL_PROF_DECL(prof_tot);
@@ -512,7 +557,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
           SGL_PROF_END(prof_fu, tm1);
           ptx::tc_fence_after_sync();
-          const uint32_t a_base = sA + s * T::kAStageBytes;
+          const uint32_t a_base = sA + s * a_stage;
           const uint32_t b_base = sB + s * T::kBStageBytes;
 #pragma unroll
           for (int kk = 0; kk < kBlockK / 16; ++kk) {
@@ -522,7 +567,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const uint64_t a_desc =
                 a_mnmajor ? ptx::smem_desc_sw128(a_base + kk * 16 * 128, kBlockK * 128, 1024)
                           : ptx::smem_desc_sw128(
-                                a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
+                                a_base + (kk >> 2) * (a_stage / (kBlockK / 64)) + (kk & 3) * 32, 16,
+                                1024);
             // weight tile, [k, n] storage: N-major slabs [kBlockK rows][64 cols], 16 k = 16
             // rows; [n, k] storage: K-major like x, rows = n, 16 k = 32 bytes.
             const uint64_t b_desc =
@@ -533,6 +579,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                                       (kb > 0 || kk > 0) ? 1u : 0u);
           }
           ptx::umma_commit<kCtaGroup>(bar_empty + 8 * s, mask);
+#ifdef SGL_DEBUG
+          ++dbg_consumed;
+#endif
           if (++s == stages) {
             s = 0;
             ph ^= 1u;
@@ -544,12 +593,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_STORE(0, prof_te);
       SGL_PROF_STORE(1, prof_fu);
       SGL_PROF_STORE(2, prof_tot);
+      SGL_DBG_COUNT(1, dbg_consumed);
     }
   } else {
     // =========================== epilogue ===========================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t out_buf0 =
-        sOut + q * (kForm == FORM_FUSED_SAVE ? 3 * T::kSaveBufBytes : T::kNumOutBufs * kChunkBytes);
+        sOut + q * (kForm == FORM_FUSED_SAVE ? 3 * T::kSaveBufBytes : out_bufs * kChunkBytes);
     const uint32_t up_buf0 = sUp + q * (kUpBufs * kChunkBytes);
     const uint32_t my_bar_up = bar_up + 8 * (q * kUpBufs);
     const uint32_t tempty_leader_base = (kCtaGroup == 2) ? ptx::mapa(bar_tempty, 0) : bar_tempty;
@@ -568,6 +618,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const TileCoord tc = shifted_tile((cluster_id + i * num_clusters) / splits);
       x = tc.n * tile_cols + c * kChunkCols;
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
+      SGL_DBG_CHECK_COORD(x >= 0 && (x & 7) == 0 && y >= 0 && (y & 31) == 0 &&
+                              x < p.tiles_n * tile_cols && y < p.tiles_m * kCtaGroup * kBlockM,
+                          g);
     };
 
     const uint64_t pol_h = ptx::make_l2_policy((p.l2_hints >> 4) & 3);
@@ -757,7 +810,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         int x, y;
         chunk_xy(g, x, y);
         const uint32_t ubuf = up_buf0 + (g % kUpBufs) * kChunkBytes;
-        const uint32_t obuf = kInPlace ? ubuf : out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
+        const uint32_t obuf =
+            kInPlace ? ubuf : out_buf0 + (static_cast<uint32_t>(g) & (out_bufs - 1)) * kChunkBytes;
 
         if constexpr (kInPlace) {
           // The other buffer is free once the previous chunk's store has read it:
@@ -785,7 +839,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         // The staging buffer is free once the store issued two chunks ago has
         // finished reading it.
         if constexpr (!kInPlace) {
-          if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
+          if (lane == 0) {
+            if (out_bufs == 1) {
+              ptx::bulk_wait_group_read<0>();
+            } else {
+              ptx::bulk_wait_group_read<kOutBufs - 1>();
+            }
+          }
         }
         __syncwarp();
 
@@ -890,6 +950,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_END(prof_busy, te_busy);
     }
     if (lane == 0 && q == 0) {
+      SGL_DBG_COUNT(2, ok ? my_tiles : 0);
       SGL_PROF_STORE(4, prof_tf);
       SGL_PROF_STORE(5, prof_up);
       SGL_PROF_STORE(6, prof_busy);

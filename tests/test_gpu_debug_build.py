@@ -1,0 +1,101 @@
+"""The self-checking build of the library (``-DSGL_DEBUG``), used where compute-sanitizer is not
+available: every TMA coordinate is checked against the 16-byte rule and the tensor's extent
+before the copy is issued, and the kernel's roles count their work.  A violation would be
+RECORDED in the status words (nothing traps or faults); here no launch of the shape ladder may
+record one, the role counters must balance (k-blocks produced = k-blocks consumed = what the
+schedule says, tiles finished by the epilogue = tiles of the schedule), and the results must
+equal the normal library's bit for bit.  Runs in a child process because a process loads one
+copy of the library.
+"""
+import os
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+CHILD = textwrap.dedent('''
+    import ctypes as C, sys
+    import numpy as np, torch
+    from swiglu_fused_b200 import _lib, matmul_bf16, matmul_fused_swiglu, matmul_silu_mul, TileConfig
+    from swiglu_fused_b200.workloads import make_inputs
+    lib = _lib.load()
+    has_counts = hasattr(lib, "sgl_debug_counts")
+    if has_counts:
+        lib.sgl_debug_counts.restype = C.c_int
+        lib.sgl_debug_counts.argtypes = [C.POINTER(C.c_ulonglong)]
+    dev = "cuda:0"
+    sms = _lib.query(_lib.QUERY_SM_COUNT)
+    out = {}
+    shapes = [(64, 64, 128), (200, 136, 264), (1000, 264, 1160), (512, 1024, 2048), (2048, 512, 640)]
+    for (M, K, N) in shapes:
+        for cg, bk in ((1, 64), (2, 128), (2, 64), (1, 128)):
+            if cg == 2 and M <= 128:
+                continue
+            cfg = TileConfig(cg, bk, 0, 4)
+            inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + N)
+            x, w = inp["x"].to(dev), inp["w"].to(dev)
+            h = matmul_fused_swiglu(x, w, config=cfg)
+            torch.cuda.synchronize()
+            _lib.device_status()              # raises if a coordinate check (or a wait) failed
+            if has_counts:
+                buf = (C.c_ulonglong * (512 * 4))()
+                _lib.check(lib.sgl_debug_counts(buf))
+                c = np.frombuffer(buf, dtype=np.uint64).reshape(512, 4)
+                tiles = -(-M // (128 * cg)) * -(-N // 128)
+                clusters = min(sms // cg, tiles)
+                kb = -(-K // bk)
+                for cl in range(clusters):
+                    mine = len(range(cl, tiles, clusters))
+                    lead = cl * cg
+                    assert c[lead, 1] == mine * kb, ("consumed", M, K, N, cg, bk, cl, c[lead])
+                    for r in range(cg):
+                        assert c[lead + r, 0] == mine * kb, ("produced", M, K, N, cg, bk, cl, r)
+                        assert c[lead + r, 2] == mine, ("tiles", M, K, N, cg, bk, cl, r)
+            out[(M, K, N, cg, bk)] = h.cpu()
+        inp = make_inputs(M, K, N, form="silu_mul", seed=M)
+        x, wg = inp["x"].to(dev), inp["w_gate"].to(dev)
+        up = (x @ inp["w_up"].to(dev))
+        out[(M, K, N, "silu_mul")] = matmul_silu_mul(x, wg, up).cpu()
+        out[(M, K, N, "gemm")] = matmul_bf16(x, wg).cpu()
+        torch.cuda.synchronize()
+        _lib.device_status()
+    torch.save(out, sys.argv[1])
+    print("counts" if has_counts else "plain", len(out))
+''')
+
+
+def _run(lib_path, out_path):
+    env = dict(os.environ)
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    if lib_path:
+        env["SWIGLU_B200_LIB"] = lib_path
+    else:
+        env.pop("SWIGLU_B200_LIB", None)
+    proc = subprocess.run([sys.executable, "-c", CHILD, out_path], env=env, capture_output=True,
+                          text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-1500:] + proc.stderr[-3000:]
+    return proc.stdout
+
+
+def test_debug_build_records_nothing_and_matches_the_normal_library(tmp_path):
+    import torch
+
+    from swiglu_fused_b200 import build
+
+    debug_lib = build.DEBUG_LIB_PATH
+    if not os.path.exists(debug_lib):
+        try:
+            build.build_debug_library()
+        except RuntimeError as e:
+            pytest.skip(f"debug library not built and no compiler here: {e}")
+    a, b = str(tmp_path / "debug.pt"), str(tmp_path / "normal.pt")
+    assert _run(debug_lib, a).startswith("counts")
+    assert _run(None, b).startswith("plain")
+    da, db = torch.load(a), torch.load(b)
+    assert da.keys() == db.keys() and len(da) > 20
+    for k in da:
+        assert torch.equal(da[k].view(torch.int16), db[k].view(torch.int16)), k
