@@ -139,10 +139,6 @@ struct Variant {
   int out_cols;
   int max_stages;
   int (*smem_bytes)(int);
-  int a_stage_bytes;      // full-height A tile of one ring stage
-  int b_stage_bytes;
-  int fixed_bytes;        // alignment slack + barriers + `up` staging
-  int out_staging_bytes;  // output staging with the standard two buffers per epilogue warp
 };
 
 template <int F, int G, int BK>
@@ -158,10 +154,6 @@ Variant make_variant() {
   v.out_cols = T::kOutCols;
   v.max_stages = T::max_stages();
   v.smem_bytes = smem_bytes_of<F, G, BK>;
-  v.a_stage_bytes = T::kAStageBytes;
-  v.b_stage_bytes = T::kBStageBytes;
-  v.fixed_bytes = T::kAlignSlack + T::kBarrierBytes + T::kUpStagingBytes;
-  v.out_staging_bytes = T::kOutStagingBytes;
   return v;
 }
 
@@ -397,32 +389,7 @@ int query_max_clusters(const Variant& v, int cta_group, int sm_count) {
 int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int vi = s.form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
   const Variant& v = variant(s.form, cfg.cta_group, cfg.block_k);
-  int stages = cfg.stages;
-  int smem = v.smem_bytes(stages);
-  int a_stage_bytes = v.a_stage_bytes;
-  int out_bufs = sgl::kOutBufs;
-  // A problem of at most 64 rows is bound by the bytes of the weight it keeps in flight (the
-  // ring), and its A tile fills half a stage or less.  When the ring depth was left to the
-  // library (it equals the variant's deepest), give the unused half of every A stage - and, in
-  // the fused form with at most one tile per CTA, where there is no next tile for the epilogue
-  // to overlap with, one of the two staging buffers per warp - to more stages.
-  if (!s.a_mnmajor && s.a_rows <= sgl::kBlockM / 2 && cfg.stages == v.max_stages) {
-    a_stage_bytes = s.a_rows * cfg.block_k * 2;
-    int staging = v.out_staging_bytes;
-    const int64_t tiles_guess =
-        ((s.M + sgl::kBlockM * cfg.cta_group - 1) / (sgl::kBlockM * cfg.cta_group)) *
-        ((s.N + v.out_cols - 1) / v.out_cols);
-    if (s.form == SGL_FORM_FUSED_SWIGLU && tiles_guess <= info->sm_count / cfg.cta_group) {
-      out_bufs = 1;
-      staging = v.out_staging_bytes / sgl::kOutBufs;
-    }
-    const int per_stage = a_stage_bytes + v.b_stage_bytes;
-    int deeper = (227 * 1024 - v.fixed_bytes - staging) / per_stage;
-    if (deeper > sgl::kMaxStages) deeper = sgl::kMaxStages;
-    if (deeper < stages) deeper = stages;
-    stages = deeper;
-    smem = v.fixed_bytes + staging + stages * per_stage;
-  }
+  const int smem = v.smem_bytes(cfg.stages);
   if (smem > info->max_smem_optin)
     return fail(SGL_ERR_BAD_CONFIG, "configuration needs %d bytes of shared memory, device has %d",
                 smem, info->max_smem_optin);
@@ -448,8 +415,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
     // First launch of this variant on this device: raise its dynamic shared-memory limit to
     // the deepest ring and ask how many clusters fit.
     std::lock_guard<std::mutex> lock(g_dev_mutex);
-    int smem_max = v.smem_bytes(v.max_stages);
-    if (smem_max < 227 * 1024 && 227 * 1024 <= info->max_smem_optin) smem_max = 227 * 1024;
+    const int smem_max = v.smem_bytes(v.max_stages);
     if (info->smem_set[vi] < smem_max) {
       e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
                                cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
@@ -476,9 +442,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.tiles_n = static_cast<int>(tiles_n);
   p.group_m = cfg.group_m;
   p.group_n = cfg.group_n;
-  p.stages = stages;
-  p.a_stage_bytes = a_stage_bytes;
-  p.out_bufs = out_bufs;
+  p.stages = cfg.stages;
   p.l2_hints = cfg.l2_hints;
   p.n_dst = s.n_dst;
   p.a_mnmajor = s.a_mnmajor;

@@ -162,10 +162,6 @@ struct KernelParams {
   int n_peer;
   long long peer_ld;    // row pitch of the raw destinations, elements
   unsigned long long peer_ptr[kMaxDst];   // element (0, 0) of this launch's block in each
-  int a_stage_bytes;    // bytes one ring stage reserves for the A tile: kBlockM * kBlockK * 2, or
-                        // a_rows * kBlockK * 2 when a short problem gives the room to more stages
-  int out_bufs;         // staging buffers per epilogue warp, fused form: 2, or 1 when every CTA
-                        // has a single tile (nothing to overlap) and the room goes to the ring
   int a_rows;           // rows of the A box actually loaded per CTA and k-block: kBlockM, or the
                         // (8-aligned) row count of a problem shorter than one tile, whose
                         // missing rows would otherwise be fetched as zero fill at full cost
@@ -354,13 +350,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = smem_base;
-  const uint32_t a_stage = static_cast<uint32_t>(p.a_stage_bytes);
-  const uint32_t sB = sA + stages * a_stage;
+  const uint32_t sB = sA + stages * T::kAStageBytes;
   const uint32_t sOut = sB + stages * T::kBStageBytes;
-  const uint32_t out_bufs = (kForm == FORM_FUSED) ? static_cast<uint32_t>(p.out_bufs)
-                                                  : static_cast<uint32_t>(kOutBufs);
-  const uint32_t sUp =
-      sOut + ((kForm == FORM_FUSED) ? kEpiWarps * out_bufs * kChunkBytes : T::kOutStagingBytes);
+  const uint32_t sUp = sOut + T::kOutStagingBytes;
   const uint32_t sBar = sUp + T::kUpStagingBytes;
   const uint32_t bar_full = sBar;                       // [kMaxStages]
   const uint32_t bar_empty = bar_full + 8 * kMaxStages; // [kMaxStages]
@@ -448,7 +440,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 #ifdef SGL_DEBUG
           ++dbg_produced;
 #endif
-          const uint32_t a_dst = sA + s * a_stage;
+          const uint32_t a_dst = sA + s * T::kAStageBytes;
           if (p.a_mnmajor) {
             // A stored [k, m]: two slabs of 64 m-columns x kBlockK k-rows, like the weight.
 #pragma unroll
@@ -459,8 +451,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           } else {
 #pragma unroll
             for (int j = 0; j < kBlockK / 64; ++j) {
-              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (a_stage / (kBlockK / 64)), &tm_x,
-                                               k0 + j * 64, m0, full, pol_x);
+              ptx::tma_load_2d<kCtaGroup == 2>(a_dst + j * (kBlockM * 128), &tm_x, k0 + j * 64,
+                                               m0, full, pol_x);
             }
           }
           const uint32_t b_dst = sB + s * T::kBStageBytes;
@@ -557,7 +549,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
           SGL_PROF_END(prof_fu, tm1);
           ptx::tc_fence_after_sync();
-          const uint32_t a_base = sA + s * a_stage;
+          const uint32_t a_base = sA + s * T::kAStageBytes;
           const uint32_t b_base = sB + s * T::kBStageBytes;
 #pragma unroll
           for (int kk = 0; kk < kBlockK / 16; ++kk) {
@@ -567,8 +559,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             const uint64_t a_desc =
                 a_mnmajor ? ptx::smem_desc_sw128(a_base + kk * 16 * 128, kBlockK * 128, 1024)
                           : ptx::smem_desc_sw128(
-                                a_base + (kk >> 2) * (a_stage / (kBlockK / 64)) + (kk & 3) * 32, 16,
-                                1024);
+                                a_base + (kk >> 2) * (kBlockM * 128) + (kk & 3) * 32, 16, 1024);
             // weight tile, [k, n] storage: N-major slabs [kBlockK rows][64 cols], 16 k = 16
             // rows; [n, k] storage: K-major like x, rows = n, 16 k = 32 bytes.
             const uint64_t b_desc =
@@ -599,7 +590,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     // =========================== epilogue ===========================
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     const uint32_t out_buf0 =
-        sOut + q * (kForm == FORM_FUSED_SAVE ? 3 * T::kSaveBufBytes : out_bufs * kChunkBytes);
+        sOut + q * (kForm == FORM_FUSED_SAVE ? 3 * T::kSaveBufBytes : T::kNumOutBufs * kChunkBytes);
     const uint32_t up_buf0 = sUp + q * (kUpBufs * kChunkBytes);
     const uint32_t my_bar_up = bar_up + 8 * (q * kUpBufs);
     const uint32_t tempty_leader_base = (kCtaGroup == 2) ? ptx::mapa(bar_tempty, 0) : bar_tempty;
@@ -810,8 +801,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         int x, y;
         chunk_xy(g, x, y);
         const uint32_t ubuf = up_buf0 + (g % kUpBufs) * kChunkBytes;
-        const uint32_t obuf =
-            kInPlace ? ubuf : out_buf0 + (static_cast<uint32_t>(g) & (out_bufs - 1)) * kChunkBytes;
+        const uint32_t obuf = kInPlace ? ubuf : out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
 
         if constexpr (kInPlace) {
           // The other buffer is free once the previous chunk's store has read it:
@@ -839,13 +829,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         // The staging buffer is free once the store issued two chunks ago has
         // finished reading it.
         if constexpr (!kInPlace) {
-          if (lane == 0) {
-            if (out_bufs == 1) {
-              ptx::bulk_wait_group_read<0>();
-            } else {
-              ptx::bulk_wait_group_read<kOutBufs - 1>();
-            }
-          }
+          if (lane == 0) ptx::bulk_wait_group_read<kOutBufs - 1>();
         }
         __syncwarp();
 
