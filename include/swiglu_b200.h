@@ -71,7 +71,10 @@ typedef struct sgl_config {
                         slabs of group_n, all row bands of one slab before the next slab, so
                         that a slab of the weight stays in L2 while x streams past it;
                         0 = one slab (plain GROUP_SIZE_M order) */
-  int32_t reserved;  /* must be 0 */
+  int32_t wide;      /* 1 = tiles of 256 output columns instead of 128 (fused_swiglu form with
+                        cta_group 2, block_k 64 and the [K, 2N] weight layout only): half the x
+                        traffic per output and half as many tiles, for problems of a few
+                        hundred rows; one accumulator stage, so no epilogue overlap.  0 = off */
 } sgl_config;
 
 /*

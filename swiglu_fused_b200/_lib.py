@@ -87,7 +87,7 @@ class SglConfig(C.Structure):
         ("max_ctas", C.c_int32),
         ("l2_hints", C.c_int32),
         ("group_n", C.c_int32),
-        ("reserved", C.c_int32),
+        ("wide", C.c_int32),
     ]
 
 
@@ -106,15 +106,16 @@ class TileConfig:
     max_ctas: int = 0
     l2_hints: int = 0   # see sgl_config.l2_hints: 2 bits each for x, weight, h, up
     group_n: int = 0    # column slabs of the tile order, in tiles (0 = one slab)
+    wide: int = 0       # 1 = 256-column tiles (fused form, cta_group 2, block_k 64)
 
     def to_c(self) -> SglConfig:
         return SglConfig(self.cta_group, self.block_k, self.stages, self.group_m, self.max_ctas,
-                         self.l2_hints, self.group_n, 0)
+                         self.l2_hints, self.group_n, self.wide)
 
     @staticmethod
     def from_c(c: SglConfig) -> "TileConfig":
         return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas, c.l2_hints,
-                          c.group_n)
+                          c.group_n, c.wide)
 
 
 class SglError(RuntimeError):

@@ -141,25 +141,30 @@ struct Variant {
   int (*smem_bytes)(int);
 };
 
-template <int F, int G, int BK>
+template <int F, int G, int BK, bool W = false>
 int smem_bytes_of(int stages) {
-  return sgl::KernelTraits<F, G, BK>::smem_bytes(stages);
+  return sgl::KernelTraits<F, G, BK, W>::smem_bytes(stages);
 }
 
-template <int F, int G, int BK>
+template <int F, int G, int BK, bool W = false>
 Variant make_variant() {
-  using T = sgl::KernelTraits<F, G, BK>;
+  using T = sgl::KernelTraits<F, G, BK, W>;
   Variant v;
-  v.fn = sgl::swiglu_kernel<F, G, BK>;
+  v.fn = sgl::swiglu_kernel<F, G, BK, W>;
   v.out_cols = T::kOutCols;
   v.max_stages = T::max_stages();
-  v.smem_bytes = smem_bytes_of<F, G, BK>;
+  v.smem_bytes = smem_bytes_of<F, G, BK, W>;
   return v;
 }
 
-// Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128).
-constexpr int kNumVariants = 16;
-const Variant& variant(int form, int cta_group, int block_k) {
+// Index: form * 4 + (cta_group - 1) * 2 + (block_k == 128); 16 = the wide-tile fused variant.
+constexpr int kNumVariants = 17;
+constexpr int kWideVariant = 16;
+int variant_index(int form, int cta_group, int block_k, int wide = 0) {
+  if (wide) return kWideVariant;
+  return form * 4 + (cta_group - 1) * 2 + (block_k == 128 ? 1 : 0);
+}
+const Variant& variant(int form, int cta_group, int block_k, int wide = 0) {
   static const Variant table[kNumVariants] = {
       make_variant<sgl::FORM_SILU_MUL, 1, 64>(),  make_variant<sgl::FORM_SILU_MUL, 1, 128>(),
       make_variant<sgl::FORM_SILU_MUL, 2, 64>(),  make_variant<sgl::FORM_SILU_MUL, 2, 128>(),
@@ -169,14 +174,15 @@ const Variant& variant(int form, int cta_group, int block_k) {
       make_variant<sgl::FORM_GEMM, 2, 64>(),      make_variant<sgl::FORM_GEMM, 2, 128>(),
       make_variant<sgl::FORM_FUSED_SAVE, 1, 64>(), make_variant<sgl::FORM_FUSED_SAVE, 1, 128>(),
       make_variant<sgl::FORM_FUSED_SAVE, 2, 64>(), make_variant<sgl::FORM_FUSED_SAVE, 2, 128>(),
+      make_variant<sgl::FORM_FUSED, 2, 64, true>(),
   };
-  return table[form * 4 + (cta_group - 1) * 2 + (block_k == 128 ? 1 : 0)];
+  return table[variant_index(form, cta_group, block_k, wide)];
 }
 
 bool config_fields_ok(const sgl_config& c) {
   return (c.cta_group == 1 || c.cta_group == 2) && (c.block_k == 64 || c.block_k == 128) &&
          c.stages >= 0 && c.stages <= sgl::kMaxStages && c.group_m >= 1 && c.max_ctas >= 0 &&
-         c.group_n >= 0 && c.reserved == 0 &&
+         c.group_n >= 0 && (c.wide == 0 || c.wide == 1) &&
          c.l2_hints >= 0 && c.l2_hints < 256 && (c.l2_hints & 3) != 3 &&
          ((c.l2_hints >> 2) & 3) != 3 && ((c.l2_hints >> 4) & 3) != 3 && ((c.l2_hints >> 6) & 3) != 3;
 }
@@ -207,8 +213,8 @@ struct DeviceInfo {
   int sm_count = 0;
   int cc = 0;
   int max_smem_optin = 0;
-  int max_clusters[16] = {};  // per variant, 0 = not yet queried
-  int smem_set[16] = {};      // dynamic smem attribute already raised to
+  int max_clusters[20] = {};  // per variant, 0 = not yet queried
+  int smem_set[20] = {};      // dynamic smem attribute already raised to
 };
 
 std::mutex g_dev_mutex;
@@ -294,9 +300,17 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;
-  } else if (form == SGL_FORM_FUSED_SWIGLU && M >= 512) {
-    // a few tile rows: the BLOCK_K = 128 ring (half as many barrier round trips per tile)
-    // measured 205 against 218 us at 1024 x 4096 x 14336, 123 against 134 us at 512 rows
+  } else if (form == SGL_FORM_FUSED_SWIGLU && M <= 2 * sgl::kBlockM) {
+    // one pair-tile row: tiles of 256 output columns (x fetched once per 256 columns, half as
+    // many tiles to spread over the CTA pairs).  Measured under sustained load at 256 x 4096 x
+    // 14336: 65 us against 69 (BLOCK_K 128) and 79 (BLOCK_K 64) with 128-column tiles.
+    c->cta_group = 2;
+    c->block_k = 64;
+    c->group_m = 8;
+    c->wide = 1;
+  } else if (form == SGL_FORM_FUSED_SWIGLU) {
+    // a few tile rows: the BLOCK_K = 128 ring (half as many barrier round trips per tile);
+    // measured 115 against 148 us at 512 x 4096 x 14336, 195 against 256 us at 1024 rows
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 8;
@@ -322,7 +336,10 @@ int resolve_config(int form, const sgl_config* in, int64_t M, sgl_config* out) {
     return fail(SGL_ERR_BAD_CONFIG,
                 "unsupported tile configuration: cta_group=%d block_k=%d stages=%d group_m=%d",
                 out->cta_group, out->block_k, out->stages, out->group_m);
-  const Variant& v = variant(form, out->cta_group, out->block_k);
+  if (out->wide && (form != SGL_FORM_FUSED_SWIGLU || out->cta_group != 2 || out->block_k != 64))
+    return fail(SGL_ERR_BAD_CONFIG,
+                "wide tiles need the fused_swiglu form with cta_group=2 and block_k=64");
+  const Variant& v = variant(form, out->cta_group, out->block_k, out->wide);
   if (out->stages == 0) out->stages = v.max_stages;
   if (out->stages < 2 || out->stages > v.max_stages)
     return fail(SGL_ERR_BAD_CONFIG, "stages=%d outside [2, %d] for cta_group=%d block_k=%d",
@@ -387,8 +404,9 @@ int query_max_clusters(const Variant& v, int cta_group, int sm_count) {
 }
 
 int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* stream) {
-  const int vi = s.form * 4 + (cfg.cta_group - 1) * 2 + (cfg.block_k == 128 ? 1 : 0);
-  const Variant& v = variant(s.form, cfg.cta_group, cfg.block_k);
+  const int wide = (cfg.wide && !s.b_kmajor) ? 1 : 0;   // the [n, k] layout has no wide form
+  const int vi = variant_index(s.form, cfg.cta_group, cfg.block_k, wide);
+  const Variant& v = variant(s.form, cfg.cta_group, cfg.block_k, wide);
   const int smem = v.smem_bytes(cfg.stages);
   if (smem > info->max_smem_optin)
     return fail(SGL_ERR_BAD_CONFIG, "configuration needs %d bytes of shared memory, device has %d",
@@ -1120,7 +1138,7 @@ int sgl_config_smem_bytes(int form, const sgl_config* cfg) {
   sgl_config c;
   int rc = resolve_config(form, cfg, 1 << 20, &c);
   if (rc) return rc;
-  return variant(form, c.cta_group, c.block_k).smem_bytes(c.stages);
+  return variant(form, c.cta_group, c.block_k, c.wide).smem_bytes(c.stages);
 }
 
 int sgl_tile_coord(int64_t t, int64_t tiles_m, int64_t tiles_n, int64_t group_m, int64_t* tile_m,

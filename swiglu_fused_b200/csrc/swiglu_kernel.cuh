@@ -168,19 +168,30 @@ struct KernelParams {
   unsigned long long wait_limit_ns;
 };
 
-template <int kForm, int kCtaGroup, int kBlockK>
+// kWide (fused form, CTA pairs): one tile is 256 output columns - two MMAs per k-step into two
+// 256-column accumulators, up in TMEM columns [0, 256) and gate in [256, 512) - instead of 128.
+// The x tile is then fetched once per 256 output columns instead of once per 128, and the tile
+// grid is half as long, which is what problems of a few hundred rows need: they are bound by
+// the bytes each SM pulls in and by how evenly few tiles spread over 74 CTA pairs, not by the
+// tensor cores.  The price is a single accumulator stage (all 512 TMEM columns hold one tile),
+// so the epilogue of a tile no longer overlaps the next tile's mainloop.
+template <int kForm, int kCtaGroup, int kBlockK, bool kWide = false>
 struct KernelTraits {
+  static_assert(!kWide || ((kForm == FORM_FUSED) && kCtaGroup == 2 && kBlockK == 64),
+                "wide tiles exist for the fused form on CTA pairs with BLOCK_K 64");
   // silu_mul form: the `up` chunk is overwritten with the result and stored from the same
   // buffer (no separate output staging), which leaves room for one more ring stage.
   static constexpr bool kInPlace = (kForm == FORM_SILU_MUL);
   static constexpr bool kIsFused = (kForm == FORM_FUSED || kForm == FORM_FUSED_SAVE);
-  static constexpr int kOutCols = kIsFused ? 128 : 256;
+  static constexpr int kOutCols = kIsFused ? (kWide ? 256 : 128) : 256;
+  static constexpr int kNumAccStages = kWide ? 1 : kAccStages;
+  static constexpr int kGateCol = kWide ? 256 : 128;   // first TMEM column of the gate block
   // staging per epilogue warp: two 64-column chunk buffers, or for the side-store form three
   // 32-column buffers (h, silu, gate factor) so that a BLOCK_K = 128 ring still fits
   static constexpr int kNumOutBufs = kOutBufs;
   static constexpr int kSaveBufBytes = 32 * 32 * 2;   // 32 rows x 64 B
   static constexpr int kChunksPerTile = kOutCols / kChunkCols;
-  static constexpr int kBColsPerCta = kAccCols / kCtaGroup;
+  static constexpr int kBColsPerCta = (kWide ? 2 * kAccCols : kAccCols) / kCtaGroup;
   static constexpr int kBSlabs = kBColsPerCta / 64;           // 64-column slabs this CTA loads
   static constexpr int kAStageBytes = kBlockM * kBlockK * 2;
   static constexpr int kBSlabBytes = kBlockK * 128;            // [kBlockK rows][64 cols]
@@ -303,12 +314,13 @@ __global__ void wait_timeout_selftest_kernel(unsigned long long limit_ns) {
   }
 }
 
-template <int kForm, int kCtaGroup, int kBlockK>
+template <int kForm, int kCtaGroup, int kBlockK, bool kWide = false>
 __global__ void __launch_bounds__(kNumThreads, 1)
 swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
               const __grid_constant__ CUtensorMap tm_up, const __grid_constant__ OutMaps tm_h,
               const KernelParams p) {
-  using T = KernelTraits<kForm, kCtaGroup, kBlockK>;
+  using T = KernelTraits<kForm, kCtaGroup, kBlockK, kWide>;
+  constexpr int kStagesAcc = T::kNumAccStages;
   constexpr bool kInPlace = T::kInPlace;
   static_assert(kBlockK == 64 || kBlockK == 128, "BLOCK_K is 64 or 128");
   static_assert(kCtaGroup == 1 || kCtaGroup == 2, "CTA group is 1 or 2");
@@ -485,6 +497,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
               int col;
               if constexpr (!T::kIsFused) {
                 col = p.b_col0 + n0 + g * 64;
+              } else if constexpr (kWide) {
+                // this CTA supplies its 128-column half of BOTH MMAs' B operands:
+                // slabs 0, 1 = up columns, slabs 2, 3 = gate columns
+                const int half0 = n0 + static_cast<int>(rank) * 128 + (j & 1) * 64;
+                col = (j < 2) ? (p.b_col0 + half0) : (p.b_col1 + half0);
               } else {
                 col = (g < 2) ? (p.b_col0 + n0 + g * 64) : (p.b_col1 + n0 + (g - 2) * 64);
               }
@@ -528,8 +545,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_DECL(prof_tot);
       SGL_PROF_BEGIN(tm_all);
       for (int t = cluster_id; t < total_tiles && ok; t += num_clusters, ++i) {
-        const int as = i & 1;
-        const uint32_t aph = (i >> 1) & 1u;
+        const int as = i % kStagesAcc;
+        const uint32_t aph = (i / kStagesAcc) & 1u;
         SGL_PROF_BEGIN(tm0);
         if (!ptx::mbar_wait(bar_tempty + 8 * as, aph ^ 1u, limit, abort_flag)) {
           report_error(kErrMmaTmemEmptyWait, i, abort_flag);
@@ -568,6 +585,14 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                          : ptx::smem_desc_sw128(b_base + kk * 16 * 128, T::kBSlabBytes, 1024);
             ptx::umma_bf16<kCtaGroup>(d_tmem, a_desc, b_desc, idesc,
                                       (kb > 0 || kk > 0) ? 1u : 0u);
+            if constexpr (kWide) {
+              // second MMA of the k-step: the gate columns (slabs 2, 3 of the stage)
+              const uint64_t b_desc_gate =
+                  ptx::smem_desc_sw128(b_base + 2 * T::kBSlabBytes + kk * 16 * 128,
+                                       T::kBSlabBytes, 1024);
+              ptx::umma_bf16<kCtaGroup>(d_tmem + T::kGateCol, a_desc, b_desc_gate, idesc,
+                                        (kb > 0 || kk > 0) ? 1u : 0u);
+            }
           }
           ptx::umma_commit<kCtaGroup>(bar_empty + 8 * s, mask);
 #ifdef SGL_DEBUG
@@ -641,8 +666,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     SGL_PROF_DECL(prof_up);
     SGL_PROF_DECL(prof_busy);
     for (int i = 0; i < my_tiles && ok; ++i) {
-      const int as = i & 1;
-      const uint32_t aph = (i >> 1) & 1u;
+      const int as = i % kStagesAcc;
+      const uint32_t aph = (i / kStagesAcc) & 1u;
       {
         SGL_PROF_BEGIN(te0);
         const bool w = ptx::mbar_wait(bar_tfull + 8 * as, aph, limit, abort_flag);
@@ -675,7 +700,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             float gate[32];
             float upv[32];
             ptx::tmem_ld_32x32b_x32(t_row + col, upv);
-            ptx::tmem_ld_32x32b_x32(t_row + 128 + col, gate);
+            ptx::tmem_ld_32x32b_x32(t_row + T::kGateCol + col, gate);
             ptx::tmem_ld_wait();
             if (c == T::kChunksPerTile - 1 && half == 1) {
               ptx::tc_fence_before_sync();
@@ -857,7 +882,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             }
           } else {
             ptx::tmem_ld_32x32b_x32(t_row + col, upv);
-            ptx::tmem_ld_32x32b_x32(t_row + 128 + col, gate);
+            ptx::tmem_ld_32x32b_x32(t_row + T::kGateCol + col, gate);
           }
           ptx::tmem_ld_wait();
           if (c == T::kChunksPerTile - 1 && half == 1) {

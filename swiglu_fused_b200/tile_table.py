@@ -41,7 +41,8 @@ def _load() -> dict[str, TileConfig]:
                 for k, v in raw.get("entries", {}).items():
                     _table[k] = TileConfig(int(v["cta_group"]), int(v["block_k"]),
                                            int(v.get("stages", 0)), int(v["group_m"]), 0,
-                                           int(v.get("l2_hints", 0)), int(v.get("group_n", 0)))
+                                           int(v.get("l2_hints", 0)), int(v.get("group_n", 0)),
+                                           int(v.get("wide", 0)))
         return _table
 
 
@@ -59,7 +60,8 @@ def save(path: str | None = None) -> str:
     path = path or os.environ.get("SWIGLU_B200_TILE_TABLE", TABLE_PATH)
     entries = {
         k: {"cta_group": c.cta_group, "block_k": c.block_k, "stages": c.stages,
-            "group_m": c.group_m, "l2_hints": c.l2_hints, "group_n": c.group_n}
+            "group_m": c.group_m, "l2_hints": c.l2_hints, "group_n": c.group_n,
+            "wide": c.wide}
         for k, c in sorted(_load().items())
     }
     tmp = path + ".tmp"
@@ -87,7 +89,7 @@ def legal_configs(form: int, M: int, N: int, K: int) -> list[TileConfig]:
         rows = 128 * c.cta_group
         tiles_m = -(-M // rows)
         eff_group = min(c.group_m, tiles_m)
-        sig = (c.cta_group, c.block_k, c.stages, eff_group, c.l2_hints, c.group_n)
+        sig = (c.cta_group, c.block_k, c.stages, eff_group, c.l2_hints, c.group_n, c.wide)
         if sig in seen:
             continue
         seen.add(sig)

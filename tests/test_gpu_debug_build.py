@@ -32,10 +32,10 @@ CHILD = textwrap.dedent('''
     out = {}
     shapes = [(64, 64, 128), (200, 136, 264), (1000, 264, 1160), (512, 1024, 2048), (2048, 512, 640)]
     for (M, K, N) in shapes:
-        for cg, bk in ((1, 64), (2, 128), (2, 64), (1, 128)):
+        for cg, bk, wide in ((1, 64, 0), (2, 128, 0), (2, 64, 0), (1, 128, 0), (2, 64, 1)):
             if cg == 2 and M <= 128:
                 continue
-            cfg = TileConfig(cg, bk, 0, 4)
+            cfg = TileConfig(cg, bk, 0, 4, 0, 0, 0, wide)
             inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + N)
             x, w = inp["x"].to(dev), inp["w"].to(dev)
             h = matmul_fused_swiglu(x, w, config=cfg)
@@ -45,7 +45,7 @@ CHILD = textwrap.dedent('''
                 buf = (C.c_ulonglong * (512 * 4))()
                 _lib.check(lib.sgl_debug_counts(buf))
                 c = np.frombuffer(buf, dtype=np.uint64).reshape(512, 4)
-                tiles = -(-M // (128 * cg)) * -(-N // 128)
+                tiles = -(-M // (128 * cg)) * -(-N // (256 if wide else 128))
                 clusters = min(sms // cg, tiles)
                 kb = -(-K // bk)
                 for cl in range(clusters):
@@ -55,7 +55,7 @@ CHILD = textwrap.dedent('''
                     for r in range(cg):
                         assert c[lead + r, 0] == mine * kb, ("produced", M, K, N, cg, bk, cl, r)
                         assert c[lead + r, 2] == mine, ("tiles", M, K, N, cg, bk, cl, r)
-            out[(M, K, N, cg, bk)] = h.cpu()
+            out[(M, K, N, cg, bk, wide)] = h.cpu()
         inp = make_inputs(M, K, N, form="silu_mul", seed=M)
         x, wg = inp["x"].to(dev), inp["w_gate"].to(dev)
         up = (x @ inp["w_up"].to(dev))

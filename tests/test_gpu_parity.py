@@ -426,3 +426,39 @@ def test_gather_epilogues_write_every_destination(M, K, N, window):
             rest = b.clone()
             rest[:M, c0:c0 + n] = float("nan")
             assert bool(torch.isnan(rest.float()).all()), (mode, i)
+
+
+@pytest.mark.parametrize("M,K,N", [(256, 128, 512), (200, 136, 264), (1000, 264, 1160),
+                                   (512, 1024, 2048), (2048, 512, 640), (300, 4096, 1408)])
+def test_wide_tiles_give_the_same_bits(M, K, N):
+    """Tiles of 256 output columns (two MMAs per k-step into one accumulator stage) against
+    the 128-column tiles: same per-element arithmetic in the same order, so identical bits, on
+    aligned and ragged shapes, several tiles per CTA pair included (max_ctas = 8), with column
+    windows, and with the gather epilogue."""
+    from swiglu_fused_b200.ops import matmul_fused_swiglu_gather
+
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + K)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    want = matmul_fused_swiglu(x, w, config=TileConfig(2, 64, 0, 8))
+    for cfg in (TileConfig(2, 64, 0, 8, 0, 0, 0, 1), TileConfig(2, 64, 2, 4, 8, 18, 0, 1),
+                TileConfig(2, 64, 0, 1, 4, 0, 2, 1)):
+        got = matmul_fused_swiglu(x, w, config=cfg)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), cfg
+    ref32 = orc.fused_swiglu_f32(inp["x"], inp["w"])
+    assert orc.compare(want.cpu(), ref32.to(torch.bfloat16), ref32).ok
+    # a column window, delivered to two buffers by the store epilogue
+    c0, n = 128, min(N - 128, 264)
+    win = matmul_fused_swiglu(x, w, up_col0=c0, gate_col0=N + c0, n_out=n,
+                              config=TileConfig(2, 64, 0, 8))
+    bufs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+    matmul_fused_swiglu_gather(x, w, bufs[0].data_ptr() + 2 * c0, [bufs[1].data_ptr() + 2 * c0], N,
+                               up_col0=c0, gate_col0=N + c0, n_out=n,
+                               config=TileConfig(2, 64, 0, 8, 0, 0, 0, 1))
+    torch.cuda.synchronize()
+    _lib.device_status()
+    for b in bufs:
+        assert torch.equal(b[:, c0:c0 + n].contiguous().view(torch.int16), win.view(torch.int16))
+    with pytest.raises(ValueError):       # wide tiles exist for CTA pairs with BLOCK_K 64 only
+        matmul_fused_swiglu(x, w, config=TileConfig(2, 128, 0, 8, 0, 0, 0, 1))
