@@ -388,8 +388,9 @@ def leg_c4(dev, act_fused, peaks) -> dict:
         rows = torch.arange(m) if m <= 256 else torch.linspace(0, m - 1, 96).long()
         xs = x[rows.to(dev)].cpu()
         ref64 = orc.fused_swiglu_exact(xs, w_cpu)          # K = 4096: measure against float64
-        rep = orc.compare(h[rows.to(dev)].cpu(), ref64.to(torch.bfloat16), ref64)
-        rep32 = orc.compare(orc.fused_swiglu(xs, w_cpu), ref64.to(torch.bfloat16), ref64)
+        rep = orc.compare(h[rows.to(dev)].cpu(), ref64.to(torch.bfloat16), ref64, k_depth=K)
+        rep32 = orc.compare(orc.fused_swiglu(xs, w_cpu), ref64.to(torch.bfloat16), ref64,
+                            k_depth=K)
         res["parity_ok"] = bool(rep.ok)
         res["parity"] = (f"{len(rows)} rows x {N} columns vs the float64 CPU oracle: {rep}; the "
                          f"reference's own fp32 check expression against the same: {rep32}")

@@ -97,3 +97,17 @@ def test_compare_flags_errors():
     nan = ref.clone()
     nan[7] = float("nan")
     assert not orc.compare(nan, ref).ok
+
+
+def test_relative_error_floor_grows_with_the_reduction_depth():
+    assert orc.rel_floor_factor(None) == 2.0 ** -7
+    assert orc.rel_floor_factor(1024) == 2.0 ** -7
+    assert orc.rel_floor_factor(4096) == 2.0 ** -6
+    # a deviation of 1.2 % of the base floor on a zero output: outside at K = 1024, inside at 4096
+    ref = torch.full((64, 64), 1.0)
+    ref[0, 0] = 0.0
+    h = ref.clone()
+    h[0, 0] = 0.012 * 2.0 ** -7 * float(ref.mean())
+    hb, rb = h.to(torch.bfloat16), ref.to(torch.bfloat16)
+    assert not orc.compare(hb, rb, ref).ok
+    assert orc.compare(hb, rb, ref, k_depth=4096).ok
