@@ -300,6 +300,9 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;
+    // x and weight loads evict-last, h stores evict-first: 1-3 % at the 32768 x 3072 x 12288
+    // and 16384 x 4096 x 14336 fused problems (the GEMM form keeps the plain policy)
+    if (form == SGL_FORM_FUSED_SWIGLU) c->l2_hints = 2 | (2 << 2) | (1 << 4);
   } else if (form == SGL_FORM_FUSED_SWIGLU && M <= 2 * sgl::kBlockM) {
     // one pair-tile row: tiles of 256 output columns (x fetched once per 256 columns, half as
     // many tiles to spread over the CTA pairs).  Measured under sustained load at 256 x 4096 x
