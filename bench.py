@@ -399,6 +399,75 @@ def leg_c4(dev, act_fused, peaks) -> dict:
     return out
 
 
+def leg_neighbours(dev, peaks) -> dict:
+    """The callers either side of the path (the rows after the hot path itself): the down
+    projection at decode sizes (unsplit, split-K with caller scratch, cuBLAS), the side-store
+    training forward, the backward elementwise kernel and the two backward GEMMs at the
+    headline shape, each beside its library counterpart on the same tensors."""
+    from swiglu_fused_b200 import _lib, matmul_bf16, matmul_fused_swiglu
+    from swiglu_fused_b200.ops import (matmul_bf16_splitk, matmul_fused_swiglu_save_factors,
+                                       splitk_scratch_bytes, swiglu_grad_preact)
+
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(9)
+    # down projection at decode sizes: h[M, 14336] @ W_down[14336, 4096]
+    Kd, Nd = 14336, 4096
+    wd = torch.empty((Kd, Nd), dtype=torch.bfloat16, device=dev).normal_(0, 0.02, generator=g)
+    ha = torch.randn((256, Kd), dtype=torch.bfloat16, device=dev, generator=g)
+    dec = {}
+    for m in (64, 256):
+        a = ha[:m]
+        c = torch.empty((m, Nd), dtype=torch.bfloat16, device=dev)
+        scratch = torch.empty(splitk_scratch_bytes(m, Nd, Kd, 0), dtype=torch.uint8, device=dev)
+        r = rotated_round_robin({
+            "unsplit": lambda: matmul_bf16(a, wd, out=c),
+            "split_k": lambda: matmul_bf16_splitk(a, wd, out=c, splits=0, scratch=scratch),
+            "cublas": lambda: torch.matmul(a, wd, out=c)}, rounds=5, window_s=0.05)
+        want = a.float() @ wd.float()
+        matmul_bf16_splitk(a, wd, out=c, splits=0, scratch=scratch)
+        err = (c.float() - want).abs().max().item() / want.abs().max().item()
+        r["max_err_over_scale"] = err
+        r["hbm_frac"] = 2.0 * Kd * Nd / (r["split_k"]["median"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+        dec[f"m{m}"] = r
+    out["down_proj_decode_14336x4096"] = dec
+    del wd, ha
+
+    # training side at the headline shape
+    import torch.nn.functional as F
+    M, K, N = M_TOTAL, K_DIM, N_OUT
+    x = torch.randn((M, K), dtype=torch.bfloat16, device=dev, generator=g)
+    w = torch.empty((K, 2 * N), dtype=torch.bfloat16, device=dev).normal_(0, K ** -0.5, generator=g)
+    h = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    factors = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=dev)
+    dy = torch.randn((M, N), dtype=torch.bfloat16, device=dev, generator=g)
+    gp = torch.empty((M, 2 * N), dtype=torch.bfloat16, device=dev)
+    gx = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    gw = torch.empty((K, 2 * N), dtype=torch.bfloat16, device=dev)
+    matmul_fused_swiglu_save_factors(x, w, out=h, factors=factors)
+    fwd = rotated_round_robin({
+        "plain_forward": lambda: matmul_fused_swiglu(x, w, out=h),
+        "save_factors_forward": lambda: matmul_fused_swiglu_save_factors(x, w, out=h,
+                                                                         factors=factors)},
+        rounds=3, window_s=0.2)
+    out["save_factors_forward_c3"] = fwd
+    ew = rotated_round_robin({
+        "this_build": lambda: swiglu_grad_preact(dy, factors, out=gp),
+        "torch_eager": lambda: torch.cat((dy * factors[:, :N], dy * factors[:, N:]), dim=1)},
+        rounds=3, window_s=0.1)
+    ew["hbm_frac"] = 10.0 * M * N / (ew["this_build"]["median"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+    out["grad_preact_c3"] = ew
+    swiglu_grad_preact(dy, factors, out=gp)
+    bw = rotated_round_robin({
+        "grad_x_this_build": lambda: matmul_bf16(gp, w, transpose_b=True, out=gx),
+        "grad_x_cublas": lambda: torch.matmul(gp, w.t(), out=gx),
+        "grad_w_this_build": lambda: matmul_bf16(x, gp, transpose_a=True, out=gw),
+        "grad_w_cublas": lambda: torch.matmul(x.t(), gp, out=gw)}, rounds=3, window_s=0.2)
+    out["backward_gemms_c3"] = bw
+    torch.cuda.synchronize()
+    _lib.device_status()
+    return out
+
+
 # --------------------------------------------------------------------------- legs, N > 1
 
 def timed_ranks(fn, iters: int, dev, dist) -> float:
@@ -792,6 +861,8 @@ def run_ours(args) -> None:
                 del x, h
                 torch.cuda.empty_cache()
                 legs.update(leg_c4(dev, act_fused, peaks))
+                torch.cuda.empty_cache()
+                legs["neighbours"] = leg_neighbours(dev, peaks)
             if not args.no_cpu_baseline:
                 line["cpu_baseline"] = {k: v for k, v in
                                         cpu_reference_rate(12.0, os.cpu_count() or 1).items()
