@@ -113,6 +113,34 @@ def test_default_config_uses_pairs_only_when_there_are_two_row_tiles():
         _lib.default_config(_lib.FORM_FUSED_SWIGLU, 32768, 12290, 3072)
 
 
+def test_default_config_by_problem_height():
+    f = _lib.FORM_FUSED_SWIGLU
+    one_row = _lib.default_config(f, 256, 14336, 4096)        # one pair-tile row: wide tiles
+    assert (one_row.cta_group, one_row.block_k, one_row.wide) == (2, 64, 1)
+    few = _lib.default_config(f, 512, 14336, 4096)            # a few tile rows: BLOCK_K 128
+    assert (few.cta_group, few.block_k, few.wide) == (2, 128, 0)
+    tall = _lib.default_config(f, 32768, 12288, 3072)
+    assert (tall.cta_group, tall.block_k, tall.group_m, tall.wide) == (2, 128, 16, 0)
+    assert tall.l2_hints == (2 | 2 << 2 | 1 << 4)             # x, W evict-last; h evict-first
+    assert _lib.default_config(_lib.FORM_SILU_MUL, 256, 14336, 4096).wide == 0
+    # wide tiles exist for the fused form on CTA pairs with BLOCK_K 64 only
+    assert _lib.config_smem_bytes(f, _lib.TileConfig(2, 64, 0, 8, 0, 0, 0, 1)) <= 227 * 1024
+    with pytest.raises(ValueError):
+        _lib.config_smem_bytes(f, _lib.TileConfig(2, 128, 0, 8, 0, 0, 0, 1))
+    with pytest.raises(ValueError):
+        _lib.config_smem_bytes(_lib.FORM_MATMUL, _lib.TileConfig(2, 64, 0, 8, 0, 0, 0, 1))
+
+
+def test_shared_weight_pipeline_region_size():
+    lib = _lib.load()
+    K, N = 3072, 12288
+    n = lib.sgl_host_pipeline_shared_bytes(_lib.FORM_FUSED_SWIGLU, N, K)
+    assert n == 2 * (2 * K * 2 * N) + 1024                    # two weight copies + the flag words
+    assert lib.sgl_host_pipeline_shared_bytes(_lib.FORM_SILU_MUL, N, K) == 2 * (2 * K * N) + 1024
+    assert lib.sgl_host_pipeline_shared_bytes(_lib.FORM_MATMUL, N, K) < 0
+    assert lib.sgl_host_pipeline_shared_bytes(_lib.FORM_FUSED_SWIGLU, N + 4, K) < 0
+
+
 def model_tile_coord(t, tiles_m, tiles_n, group_m):
     """Independent Python model of the GROUP_SIZE_M order."""
     per_band = group_m * tiles_n
