@@ -530,8 +530,12 @@ def leg_c5(rank: int, world: int, dev, peaks) -> dict:
         # through the NVSwitch multicast mapping, where the fabric offers one; only after the
         # plain modes have passed on every rank
         del sym
-        sym = sharding.SymmetricOutput(M, N, dev, multicast=True)
-        if all_true(bool(sym.multicast_ptr), dev, dist):
+        try:
+            sym = sharding.SymmetricOutput(M, N, dev, multicast=True)
+            have_mc = bool(sym.multicast_ptr)
+        except Exception:   # a fabric or driver without multicast objects: the plain modes stand
+            sym, have_mc = None, False
+        if all_true(have_mc, dev, dist):
             sym.tensor.zero_()
             t_modes["multicast"] = timed_ranks(lambda: sharding.fused_swiglu_n_sharded_fused_gather(
                 x, w, sym, mode="multicast"), iters, dev, dist)

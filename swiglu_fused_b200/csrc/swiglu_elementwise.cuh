@@ -106,6 +106,10 @@ sum_slots_f32_kernel(const float4* __restrict__ slots, uint4* __restrict__ out, 
                      int64_t ldo_vec) {
   const int64_t total = static_cast<int64_t>(rows) * n_vec;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // Launched with programmatic stream serialisation right behind the kernel that writes the
+  // slots: this grid may be set up while that kernel is still running, and waits here until it
+  // has finished and its writes are visible (a no-op for an ordinary launch).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += stride) {
     const int64_t row = i / n_vec;

@@ -19,6 +19,7 @@ runs (no factor writes).
 from __future__ import annotations
 
 import math
+import warnings
 
 import torch
 
@@ -35,7 +36,8 @@ class PackedSwiGLULinear(torch.nn.Module):
     """``block_n_half``, ``backward_mode`` and ``parameter_layout`` are the reference
     constructor's tuning switches (``swiglu/triton/impls.py:3388-3408``); they are accepted,
     checked against the same sets and otherwise unused: there is one native forward/backward
-    path and one parameter layout here."""
+    path and one parameter layout here (asking for the ``"packed"`` layout warns and
+    ``parameter_layout`` reads ``"normal"`` afterwards)."""
 
     def __init__(self, in_features: int, hidden_features: int, *, block_n_half=None,
                  backward_mode: str = "save_factors_normal", parameter_layout: str = "normal",
@@ -45,6 +47,17 @@ class PackedSwiGLULinear(torch.nn.Module):
             raise ValueError(f"unknown backward_mode {backward_mode!r}")
         if parameter_layout not in ("packed", "normal"):
             raise ValueError(f"unknown parameter_layout {parameter_layout!r}")
+        if parameter_layout == "packed":
+            # the reference's chunk-interleaved internal layout does not exist here; say so
+            # once instead of silently handing back a differently laid out `weight`
+            warnings.warn(
+                "PackedSwiGLULinear(parameter_layout='packed'): this implementation keeps "
+                "`weight` as [in_features, 2 * hidden_features] = [W_up | W_gate] (the "
+                "reference's 'normal' layout); state dicts are unaffected (nn.Linear layout "
+                "either way)", stacklevel=2)
+        self.block_n_half = block_n_half
+        self.backward_mode = backward_mode
+        self.parameter_layout = "normal"
         if in_features % 8 or hidden_features % 8:
             raise ValueError("in_features and hidden_features must be multiples of 8 "
                              f"(16-byte rows), got {in_features} and {hidden_features}")

@@ -61,8 +61,10 @@ def test_reference_import_path_and_constructor_switches():
     from swiglu.triton.impls import (PackedSwiGLULinear as P, pack_swiglu_linear_weight,
                                      unpack_swiglu_linear_weight)
     assert P is PackedSwiGLULinear
-    m = P(64, 32, block_n_half=64, backward_mode="save_factors", parameter_layout="packed",
-          device="cpu")
+    with pytest.warns(UserWarning, match="parameter_layout='packed'"):
+        m = P(64, 32, block_n_half=64, backward_mode="save_factors", parameter_layout="packed",
+              device="cpu")
+    assert m.parameter_layout == "normal" and m.backward_mode == "save_factors"
     lw = m.linear_weight()
     assert torch.equal(pack_swiglu_linear_weight(lw, 64), m.weight.detach())
     assert torch.equal(unpack_swiglu_linear_weight(m.weight.detach(), 64), lw)
