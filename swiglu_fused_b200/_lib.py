@@ -6,6 +6,7 @@ the operators raise.  Nothing in this package computes on the CPU.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 import os
 import threading
 from dataclasses import dataclass
@@ -109,13 +110,20 @@ class TileConfig:
     wide: int = 0       # 1 = 256-column tiles (fused form, cta_group 2, block_k 64)
 
     def to_c(self) -> SglConfig:
-        return SglConfig(self.cta_group, self.block_k, self.stages, self.group_m, self.max_ctas,
-                         self.l2_hints, self.group_n, self.wide)
+        """The C struct for this entry.  Cached per (immutable) entry: the library only reads
+        it, and building a ctypes struct costs microseconds on a call path that takes a few."""
+        return _config_struct(self)
 
     @staticmethod
     def from_c(c: SglConfig) -> "TileConfig":
         return TileConfig(c.cta_group, c.block_k, c.stages, c.group_m, c.max_ctas, c.l2_hints,
                           c.group_n, c.wide)
+
+
+@functools.lru_cache(maxsize=256)
+def _config_struct(cfg: "TileConfig") -> SglConfig:
+    return SglConfig(cfg.cta_group, cfg.block_k, cfg.stages, cfg.group_m, cfg.max_ctas,
+                     cfg.l2_hints, cfg.group_n, cfg.wide)
 
 
 class SglError(RuntimeError):

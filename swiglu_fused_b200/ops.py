@@ -33,25 +33,56 @@ DTYPE = torch.bfloat16
 def _check_matrix(t: torch.Tensor, name: str, allow_empty_rows: bool = False) -> None:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
-    if t.dim() != 2:
-        raise ValueError(f"{name} must be 2-D, got shape {tuple(t.shape)}")
+    shape = t.shape
+    if len(shape) != 2:
+        raise ValueError(f"{name} must be 2-D, got shape {tuple(shape)}")
     if t.dtype != DTYPE:
         raise TypeError(f"{name} must be torch.bfloat16, got {t.dtype}")
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor (this operator has no CPU path)")
-    if t.shape[1] < 1 or (t.shape[0] < 1 and not allow_empty_rows):
-        raise ValueError(f"{name} must not be empty, got shape {tuple(t.shape)}")
-    if t.shape[0] == 0:
+    rows, cols = shape
+    if cols < 1 or (rows < 1 and not allow_empty_rows):
+        raise ValueError(f"{name} must not be empty, got shape {tuple(shape)}")
+    if rows == 0:
         return
-    if t.stride(1) != 1:
+    s0, s1 = t.stride()
+    if s1 != 1:
         raise ValueError(f"{name} must be row-major with unit column stride, "
-                         f"got strides {t.stride()}")
-    if t.shape[0] > 1 and t.stride(0) < t.shape[1]:
-        raise ValueError(f"{name} has overlapping rows: strides {t.stride()}")
-    if t.stride(0) % 8 != 0 and t.shape[0] > 1:
-        raise ValueError(f"{name}: row stride {t.stride(0)} must be a multiple of 8 elements")
+                         f"got strides {(s0, s1)}")
+    if rows > 1:
+        if s0 < cols:
+            raise ValueError(f"{name} has overlapping rows: strides {(s0, s1)}")
+        if s0 % 8 != 0:
+            raise ValueError(f"{name}: row stride {s0} must be a multiple of 8 elements")
     if t.data_ptr() % 16 != 0:
         raise ValueError(f"{name} must be 16-byte aligned")
+
+
+class _OnDevice:
+    """``with _on_device(dev):`` makes ``dev`` the current CUDA device for the library call and
+    restores the previous one - but only when it is not current already, which on the usual
+    single-device call path saves the several microseconds ``torch.cuda.device`` costs."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, dev: torch.device):
+        self.idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+_on_device = _OnDevice
 
 
 def _ld(t: torch.Tensor) -> int:
@@ -69,8 +100,15 @@ def _same_device(*named: tuple[str, torch.Tensor]) -> torch.device:
     return dev
 
 
+# torch's raw-stream accessor (what its own compiled kernels use) is several times cheaper than
+# building a torch.cuda.Stream object per call; fall back to the public API where it is absent.
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_handle(stream, device) -> int:
     if stream is None:
+        if _raw_current_stream is not None and device.index is not None:
+            return _raw_current_stream(device.index)
         return torch.cuda.current_stream(device).cuda_stream
     if isinstance(stream, torch.cuda.Stream):
         return stream.cuda_stream
@@ -135,7 +173,7 @@ def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig 
     cfg = _pick_config(_lib.FORM_SILU_MUL, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.sgl_matmul_silu_mul(
             A.data_ptr(), B_gate.data_ptr(), up.data_ptr(), h.data_ptr(), M, N, K,
             _ld(A), _ld(B_gate), _ld(up), _ld(h),
@@ -196,7 +234,7 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
     lib = _lib.load()
     ldw = _ld(W) if W.shape[0] > 1 else max(_ld(W), (W.shape[1] + 7) // 8 * 8)
     entry = lib.sgl_matmul_fused_swiglu if w_layout == "kn" else lib.sgl_matmul_fused_swiglu_nk
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = entry(
             A.data_ptr(), W.data_ptr(), h.data_ptr(), M, N, K, _ld(A), ldw, _ld(h),
             c_up, c_gate, C.byref(cfg_c) if cfg_c is not None else None,
@@ -230,7 +268,7 @@ def matmul_fused_swiglu_multi_dst(A, W, dst_ptrs, ldh: int, *, up_col0: int, gat
     cfg_c = cfg.to_c() if cfg is not None else None
     arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
     lib = _lib.load()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = lib.sgl_matmul_fused_swiglu_multi_dst(
             A.data_ptr(), W.data_ptr(), arr, len(dst_ptrs), M, N, K, _ld(A), _ld(W), int(ldh),
             int(up_col0), int(gate_col0), C.byref(cfg_c) if cfg_c is not None else None,
@@ -261,7 +299,7 @@ def matmul_fused_swiglu_gather(A, W, local_ptr: int, peer_ptrs, ldh: int, *, up_
     cfg = _pick_config(_lib.FORM_FUSED_SWIGLU, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
     arr = (C.c_void_p * max(1, len(peer_ptrs)))(*[int(p) for p in peer_ptrs])
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_matmul_fused_swiglu_gather(
             A.data_ptr(), W.data_ptr(), int(local_ptr), arr, len(peer_ptrs),
             int(multicast_ptr) if multicast_ptr else None, M, N, K, _ld(A), _ld(W), int(ldh),
@@ -291,7 +329,7 @@ def matmul_fused_swiglu_save_factors(A, W, *, out=None, factors=None, stream=Non
     f = _prep_out(factors, M, 2 * N, dev, "factors")
     cfg = _pick_config(_lib.FORM_FUSED_SWIGLU_SAVE, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_matmul_fused_swiglu_save_factors(
             A.data_ptr(), W.data_ptr(), h.data_ptr(), f.data_ptr(), M, N, K, _ld(A), _ld(W),
             _ld(h), _ld(f), 0, N, C.byref(cfg_c) if cfg_c is not None else None,
@@ -313,7 +351,7 @@ def swiglu_grad_preact(dy, factors, *, out=None, stream=None):
         raise ValueError(f"N={N} must be a multiple of 8")
     dev = _same_device(("dy", dy), ("factors", factors))
     o = _prep_out(out, M, 2 * N, dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_swiglu_grad_preact(dy.data_ptr(), factors.data_ptr(), o.data_ptr(), M,
                                                 N, _ld(dy), _ld(factors), _ld(o),
                                                 _stream_handle(stream, dev))
@@ -348,7 +386,7 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
     c = _prep_out(out, M, N, dev)
     cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_matmul_bf16_ex(
             A.data_ptr(), B.data_ptr(), c.data_ptr(), M, N, K, _ld(A), _ld(B), _ld(c),
             int(transpose_a), int(transpose_b), C.byref(cfg_c) if cfg_c is not None else None,
@@ -393,7 +431,7 @@ def matmul_bf16_splitk(A, B, *, out=None, splits: int = 0, scratch=None, stream=
         raise ValueError("scratch must be a contiguous uint8 CUDA tensor on the operands' device")
     cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_matmul_bf16_splitk(
             A.data_ptr(), B.data_ptr(), c.data_ptr(), M, N, K, _ld(A), _ld(B), _ld(c), int(splits),
             scratch.data_ptr(), scratch.numel(), C.byref(cfg_c) if cfg_c is not None else None,
@@ -428,7 +466,7 @@ def matmul_bf16_reduce_scatter(A, B, dst_ptrs, rows_per_dst: int, ldc: int, *, d
     cfg = _pick_config(_lib.FORM_MATMUL, config, M, N, K)
     cfg_c = cfg.to_c() if cfg is not None else None
     arr = (C.c_void_p * len(dst_ptrs))(*[int(p) for p in dst_ptrs])
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_matmul_bf16_reduce_scatter(
             A.data_ptr(), B.data_ptr(), arr, len(dst_ptrs), int(rows_per_dst), int(bool(dst_f32)),
             int(bool(accumulate)), int(first_dst), M, N, K, _ld(A), _ld(B), int(ldc), C.byref(cfg_c) if cfg_c is not None else None,
@@ -452,7 +490,7 @@ def sum_bf16_slots(slots, out=None, *, rows: int | None = None, stream=None):
     if r == 0:
         return out if out is not None else torch.empty((0, Ccols), dtype=DTYPE, device=dev)
     o = _prep_out(out, r, Ccols, dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.load().sgl_sum_bf16_slots(slots.data_ptr(), n, R * Ccols, o.data_ptr(), r, Ccols,
                                             Ccols, _ld(o), _stream_handle(stream, dev))
     _lib.check(rc)

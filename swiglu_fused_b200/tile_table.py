@@ -31,6 +31,8 @@ def _key(form: int, M: int, N: int, K: int) -> str:
 
 def _load() -> dict[str, TileConfig]:
     global _table
+    if _table is not None:          # hot path of every operator call: no lock once loaded
+        return _table
     with _lock:
         if _table is None:
             _table = {}
