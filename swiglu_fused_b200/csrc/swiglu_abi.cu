@@ -494,13 +494,17 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   lc.blockDim = dim3(sgl::kNumThreads, 1, 1);
   lc.dynamicSmemBytes = static_cast<size_t>(smem);
   lc.stream = static_cast<cudaStream_t>(stream);
-  cudaLaunchAttribute attrs[1];
+  cudaLaunchAttribute attrs[2];
   attrs[0].id = cudaLaunchAttributeClusterDimension;
   attrs[0].val.clusterDim.x = static_cast<unsigned>(cfg.cta_group);
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
+  // the kernel orders itself behind its predecessor with griddepcontrol.wait, so its set-up
+  // may overlap the predecessor's tail
+  attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[1].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attrs;
-  lc.numAttrs = 1;
+  lc.numAttrs = 2;
   e = cudaLaunchKernelEx(&lc, v.fn, *s.x, *s.w, *s.up, *s.out, p);
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
   g_launches.fetch_add(1);

@@ -408,6 +408,15 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
+  // Programmatic dependent launch (the host launches this kernel with programmatic stream
+  // serialisation allowed).  Everything above touches no global memory, so it may run while
+  // the previous kernel of the stream is still finishing; from here on the previous grid must
+  // be complete and its writes visible.  In turn the next kernel of the stream may be set up
+  // from now on (it waits at the same point).  Both are no-ops when the neighbour in the
+  // stream is an ordinary launch.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
   const uint64_t limit = p.wait_limit_ns;
 
   if (warp == 0) {
@@ -966,7 +975,14 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_STORE(7, my_tiles);
     }
     if (lane == 0) {
-      ptx::bulk_wait_group<0>();
+      // Before the CTA exits its staging buffers must have been READ by the last stores (the
+      // writes themselves are tracked to completion by the memory system, as for any store);
+      // stores or reductions into a peer's memory are waited for in full.
+      if (p.n_dst > 1 || p.reduce_rows > 0 || p.peer_mode != 0) {
+        ptx::bulk_wait_group<0>();
+      } else {
+        ptx::bulk_wait_group_read<0>();
+      }
       if constexpr (kForm == FORM_SILU_MUL) {
         if (!ok) {
           // Drain `up` loads that were issued but never consumed.
