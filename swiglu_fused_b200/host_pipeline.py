@@ -143,9 +143,21 @@ class SharedWeightHostPipeline(HostPipeline):
             self.form, self.M, self.N, self.K, first_rows, block_rows, windows, cfg,
             self.world, self.rank, arr, C.byref(self._handle)))
 
-    def close(self) -> None:
+    def close(self, barrier: bool = True) -> None:
+        """Collective (like the constructor): the ranks meet at a barrier first, because a
+        region may only be released once no peer can still push a weight slice into it."""
+        if self._handle and barrier:
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.group)
         super().close()          # the native pipeline first: it borrows the regions
         self._region = None
+
+    def __del__(self):
+        try:
+            self.close(barrier=False)    # no collective from a finaliser
+        except Exception:
+            pass
 
 
 class HostPipelineSiluMul(_NativePipeline):
