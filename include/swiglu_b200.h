@@ -397,6 +397,23 @@ int sgl_host_pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t 
  * of x and the WHOLE w_host (only its slice of it is read).  No counterpart in the reference.
  */
 int64_t sgl_host_pipeline_shared_bytes(int form, int64_t N, int64_t K);
+/*
+ * The schedule a pipeline of these sizes follows in one run, without creating one (pure host
+ * arithmetic, no device needed): step i computes rows [row0, row1) x output columns
+ * [col0, col1) after copying in x's rows (copies_rows) and the weight's columns of that window
+ * (copies_weight_window); waits_for_rank >= 0 names the rank whose weight slice the step has to
+ * wait for, signals_peers marks the step after which this rank raises its flag on the peers.
+ * world = 1 gives the single-GPU schedule of sgl_host_pipeline_create, world > 1 rank `rank`'s
+ * schedule of sgl_host_pipeline_create_shared; copy_weight as in run.  Writes at most max_steps
+ * entries and returns the number of steps of the schedule (negative sgl_status on bad input).
+ */
+typedef struct sgl_pipe_step {
+  int64_t row0, row1, col0, col1;
+  int32_t copies_rows, copies_weight_window, waits_for_rank, signals_peers;
+} sgl_pipe_step;
+int sgl_host_pipeline_plan(int64_t M, int64_t N, int64_t first_rows, int64_t block_rows,
+                           int windows, int world, int rank, int copy_weight, int max_steps,
+                           sgl_pipe_step* steps);
 int sgl_host_pipeline_create_shared(int form, int64_t M, int64_t N, int64_t K, int64_t first_rows,
                                     int64_t block_rows, int windows, const sgl_config* cfg,
                                     int world, int rank, void* const* regions,

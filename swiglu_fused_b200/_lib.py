@@ -64,6 +64,7 @@ EXPORTED_SYMBOLS = (
     "sgl_set_wait_limit_ns",
     "sgl_host_pipeline_create",
     "sgl_host_pipeline_shared_bytes",
+    "sgl_host_pipeline_plan",
     "sgl_host_pipeline_create_shared",
     "sgl_host_pipeline_run",
     "sgl_host_pipeline_query",
@@ -90,6 +91,14 @@ class SglConfig(C.Structure):
         ("group_n", C.c_int32),
         ("wide", C.c_int32),
     ]
+
+
+class SglPipeStep(C.Structure):
+    """Mirror of ``struct sgl_pipe_step``."""
+
+    _fields_ = [("row0", C.c_int64), ("row1", C.c_int64), ("col0", C.c_int64), ("col1", C.c_int64),
+                ("copies_rows", C.c_int32), ("copies_weight_window", C.c_int32),
+                ("waits_for_rank", C.c_int32), ("signals_peers", C.c_int32)]
 
 
 @dataclass(frozen=True)
@@ -231,6 +240,9 @@ def load() -> C.CDLL:
                                                  C.POINTER(vp)]
         lib.sgl_host_pipeline_shared_bytes.restype = i64
         lib.sgl_host_pipeline_shared_bytes.argtypes = [ip, i64, i64]
+        lib.sgl_host_pipeline_plan.restype = ip
+        lib.sgl_host_pipeline_plan.argtypes = [i64, i64, i64, i64, ip, ip, ip, ip, ip,
+                                               C.POINTER(SglPipeStep)]
         lib.sgl_host_pipeline_create_shared.restype = ip
         lib.sgl_host_pipeline_create_shared.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp, ip,
                                                         ip, C.POINTER(vp), C.POINTER(vp)]
@@ -332,3 +344,18 @@ def device_status() -> list[int]:
 
 def set_wait_limit_ns(ns: int) -> None:
     check(load().sgl_set_wait_limit_ns(ns))
+
+
+def host_pipeline_plan(M: int, N: int, *, first_rows: int = 0, block_rows: int = 0,
+                       windows: int = 0, world: int = 1, rank: int = 0,
+                       copy_weight: bool = True) -> list[dict]:
+    """The step list of the host-buffer pipeline for these sizes (no device needed)."""
+    lib = load()
+    n = lib.sgl_host_pipeline_plan(M, N, first_rows, block_rows, windows, world, rank,
+                                   int(copy_weight), 0, None)
+    if n < 0:
+        check(n)
+    arr = (SglPipeStep * max(n, 1))()
+    check(min(0, lib.sgl_host_pipeline_plan(M, N, first_rows, block_rows, windows, world, rank,
+                                            int(copy_weight), n, arr)))
+    return [{f: getattr(arr[i], f) for f, _ in SglPipeStep._fields_} for i in range(n)]

@@ -160,6 +160,62 @@ constexpr int64_t kPipeFlagBytes = 1024;    // flag words at the end of a shared
 
 int64_t pipe_weight_cols(int form, int64_t N) { return form == SGL_FORM_FUSED_SWIGLU ? 2 * N : N; }
 
+// The schedule of one run: which rows and columns each step computes, what it copies in first
+// and whose weight slice it has to wait for.  Pure host arithmetic (no device), shared by
+// create and by sgl_host_pipeline_plan.
+void build_pipe_plan(int64_t M, int64_t N, int64_t first_rows, int64_t block_rows, int windows,
+                     bool shared, int world, int rank, std::vector<PipeStep>* with_weight,
+                     std::vector<PipeStep>* rows_only, int64_t* own_c0, int64_t* own_c1) {
+  *own_c0 = 0;
+  *own_c1 = N;
+  // Defaults: the first block is 3/16 of the rows (long enough that, per weight window, the
+  // output produced keeps the copy-out leg busy), later blocks 1/16; eight weight windows.
+  if (first_rows == 0) first_rows = round_up((3 * M + 15) / 16, 256);
+  if (block_rows == 0) block_rows = round_up((M + 15) / 16, 256);
+  if (block_rows < 1024) block_rows = 1024;
+  if (first_rows > M) first_rows = M;
+  if (windows == 0) windows = 8;
+
+  // Weight windows of the first block.  Alone: `windows` windows over all columns.  Shared: this
+  // rank's own slice first (cut into windows / world windows, each pushed to the peers as soon
+  // as it is here), then the peers' slices in the order they arrive (every rank pushes to its
+  // successors in turn, so the predecessors' slices land first).
+  if (!shared) {
+    const int64_t wcols = round_up((N + windows - 1) / windows, 256);
+    for (int64_t c = 0; c < N; c += wcols)
+      with_weight->push_back({0, first_rows, c, c + wcols < N ? c + wcols : N, c == 0, true, -1,
+                                false});
+  } else {
+    int64_t c0 = 0, cnt = 0;
+    sgl_shard_range(N, 256, world, rank, &c0, &cnt);
+    *own_c0 = c0;
+    *own_c1 = c0 + cnt;
+    int sub = windows / world;
+    if (sub < 1) sub = 1;
+    const int64_t wcols = cnt > 0 ? round_up((cnt + sub - 1) / sub, 128) : 0;
+    bool first = true;
+    for (int64_t c = c0; c < c0 + cnt; c += wcols) {
+      const int64_t e = c + wcols < c0 + cnt ? c + wcols : c0 + cnt;
+      with_weight->push_back({0, first_rows, c, e, first, true, -1, e == c0 + cnt});
+      first = false;
+    }
+    if (cnt == 0)   // nothing of its own to send: still owes x's first rows and the flags
+      with_weight->push_back({0, first_rows, 0, 0, true, false, -1, true});
+    for (int d = 1; d < world; ++d) {
+      const int q = (rank - d + world) % world;
+      int64_t q0 = 0, qn = 0;
+      sgl_shard_range(N, 256, world, q, &q0, &qn);
+      if (qn > 0) with_weight->push_back({0, first_rows, q0, q0 + qn, false, false, q, false});
+    }
+  }
+  for (int64_t r = first_rows; r < M; r += block_rows)
+    with_weight->push_back({r, r + block_rows < M ? r + block_rows : M, 0, N, true, false, -1,
+                              false});
+  for (int64_t r = 0; r < M; r += block_rows)
+    rows_only->push_back({r, r + block_rows < M ? r + block_rows : M, 0, N, true, false, -1,
+                            false});
+}
+
 int pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t first_rows,
                     int64_t block_rows, int windows, const sgl_config* cfg, int world, int rank,
                     void* const* regions, sgl_host_pipeline** out) {
@@ -200,52 +256,8 @@ int pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t first_row
     p->has_cfg = true;
   }
 
-  // Defaults: the first block is 3/16 of the rows (long enough that, per weight window, the
-  // output produced keeps the copy-out leg busy), later blocks 1/16; eight weight windows.
-  if (first_rows == 0) first_rows = round_up((3 * M + 15) / 16, 256);
-  if (block_rows == 0) block_rows = round_up((M + 15) / 16, 256);
-  if (block_rows < 1024) block_rows = 1024;
-  if (first_rows > M) first_rows = M;
-  if (windows == 0) windows = 8;
-
-  // Weight windows of the first block.  Alone: `windows` windows over all columns.  Shared: this
-  // rank's own slice first (cut into windows / world windows, each pushed to the peers as soon
-  // as it is here), then the peers' slices in the order they arrive (every rank pushes to its
-  // successors in turn, so the predecessors' slices land first).
-  if (!shared) {
-    const int64_t wcols = round_up((N + windows - 1) / windows, 256);
-    for (int64_t c = 0; c < N; c += wcols)
-      p->with_weight.push_back({0, first_rows, c, c + wcols < N ? c + wcols : N, c == 0, true, -1,
-                                false});
-  } else {
-    int64_t c0 = 0, cnt = 0;
-    sgl_shard_range(N, 256, world, rank, &c0, &cnt);
-    p->own_c0 = c0;
-    p->own_c1 = c0 + cnt;
-    int sub = windows / world;
-    if (sub < 1) sub = 1;
-    const int64_t wcols = cnt > 0 ? round_up((cnt + sub - 1) / sub, 128) : 0;
-    bool first = true;
-    for (int64_t c = c0; c < c0 + cnt; c += wcols) {
-      const int64_t e = c + wcols < c0 + cnt ? c + wcols : c0 + cnt;
-      p->with_weight.push_back({0, first_rows, c, e, first, true, -1, e == c0 + cnt});
-      first = false;
-    }
-    if (cnt == 0)   // nothing of its own to send: still owes x's first rows and the flags
-      p->with_weight.push_back({0, first_rows, 0, 0, true, false, -1, true});
-    for (int d = 1; d < world; ++d) {
-      const int q = (rank - d + world) % world;
-      int64_t q0 = 0, qn = 0;
-      sgl_shard_range(N, 256, world, q, &q0, &qn);
-      if (qn > 0) p->with_weight.push_back({0, first_rows, q0, q0 + qn, false, false, q, false});
-    }
-  }
-  for (int64_t r = first_rows; r < M; r += block_rows)
-    p->with_weight.push_back({r, r + block_rows < M ? r + block_rows : M, 0, N, true, false, -1,
-                              false});
-  for (int64_t r = 0; r < M; r += block_rows)
-    p->rows_only.push_back({r, r + block_rows < M ? r + block_rows : M, 0, N, true, false, -1,
-                            false});
+  build_pipe_plan(M, N, first_rows, block_rows, windows, shared, p->world, p->rank,
+                  &p->with_weight, &p->rows_only, &p->own_c0, &p->own_c1);
 
   const int64_t w_cols = pipe_weight_cols(form, N);
   p->w_copy_bytes = round_up(2 * K * w_cols, 256);
@@ -292,6 +304,33 @@ int sgl_host_pipeline_create(int form, int64_t M, int64_t N, int64_t K, int64_t 
                              int64_t block_rows, int windows, const sgl_config* cfg,
                              sgl_host_pipeline** out) {
   return pipeline_create(form, M, N, K, first_rows, block_rows, windows, cfg, 1, 0, nullptr, out);
+}
+
+int sgl_host_pipeline_plan(int64_t M, int64_t N, int64_t first_rows, int64_t block_rows,
+                           int windows, int world, int rank, int copy_weight, int max_steps,
+                           sgl_pipe_step* steps) {
+  if (M < 1 || N < 1 || N % 8 != 0 || first_rows < 0 || block_rows < 0 || windows < 0 ||
+      windows > 64 || world < 1 || world > 64 || rank < 0 || rank >= world || max_steps < 0 ||
+      (max_steps > 0 && !steps))
+    return fail(SGL_ERR_BAD_ARGUMENT, "bad pipeline plan request");
+  std::vector<PipeStep> with_weight, rows_only;
+  int64_t c0 = 0, c1 = 0;
+  // world == 1 plans the single-GPU schedule (column windows over the whole weight)
+  build_pipe_plan(M, N, first_rows, block_rows, windows, world > 1, world, rank, &with_weight,
+                  &rows_only, &c0, &c1);
+  const std::vector<PipeStep>& plan = copy_weight ? with_weight : rows_only;
+  const int n = static_cast<int>(plan.size());
+  for (int i = 0; i < n && i < max_steps; ++i) {
+    steps[i].row0 = plan[i].r0;
+    steps[i].row1 = plan[i].r1;
+    steps[i].col0 = plan[i].c0;
+    steps[i].col1 = plan[i].c1;
+    steps[i].copies_rows = plan[i].copy_rows ? 1 : 0;
+    steps[i].copies_weight_window = plan[i].copy_window ? 1 : 0;
+    steps[i].waits_for_rank = plan[i].wait_owner;
+    steps[i].signals_peers = (plan[i].last_own && world > 1) ? 1 : 0;
+  }
+  return n;
 }
 
 int64_t sgl_host_pipeline_shared_bytes(int form, int64_t N, int64_t K) {
