@@ -13,6 +13,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -20,6 +21,7 @@
 
 #include <cuda.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>   // header-only; a no-op unless a profiler is attached
 
 #include "swiglu_elementwise.cuh"
 #include "swiglu_kernel.cuh"
@@ -29,6 +31,32 @@ namespace {
 thread_local std::string t_last_error;
 std::atomic<int64_t> g_launches{0};
 std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+
+// Tracing, off by default (the reference prints from its tuner and loader unconditionally,
+// swiglu/matmul_silu_mul.py:135,156,159).  SGL_LOG=1 writes one line per kernel launch to
+// stderr; SGL_NVTX=1 wraps every launch in an NVTX range named after the form and the shape,
+// which shows up in timeline profilers.  Both are read once.
+bool env_flag(const char* name) {
+  const char* v = getenv(name);
+  return v && v[0] != '\0' && v[0] != '0';
+}
+bool log_enabled() {
+  static const bool on = env_flag("SGL_LOG");
+  return on;
+}
+bool nvtx_enabled() {
+  static const bool on = env_flag("SGL_NVTX");
+  return on;
+}
+const char* form_name(int form) {
+  switch (form) {
+    case SGL_FORM_SILU_MUL: return "silu_mul";
+    case SGL_FORM_FUSED_SWIGLU: return "fused_swiglu";
+    case SGL_FORM_MATMUL: return "matmul";
+    case SGL_FORM_FUSED_SWIGLU_SAVE: return "fused_swiglu_save";
+    default: return "?";
+  }
+}
 
 int fail(int code, const char* fmt, ...) {
   char buf[512];
@@ -505,7 +533,20 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   attrs[1].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attrs;
   lc.numAttrs = 2;
+  char label[160];
+  if (log_enabled() || nvtx_enabled()) {
+    snprintf(label, sizeof(label),
+             "sgl %s %lldx%lldx%lld cta_group=%d block_k=%d stages=%d group_m=%d group_n=%d "
+             "wide=%d splits=%d n_dst=%d grid=%lld smem=%d",
+             form_name(s.form), static_cast<long long>(s.M), static_cast<long long>(s.N),
+             static_cast<long long>(s.K), cfg.cta_group, cfg.block_k, cfg.stages, cfg.group_m,
+             cfg.group_n, wide, s.splits, s.n_dst, static_cast<long long>(clusters * cfg.cta_group),
+             smem);
+    if (log_enabled()) fprintf(stderr, "[libswiglu_b200] launch %s\n", label);
+    if (nvtx_enabled()) nvtxRangePushA(label);
+  }
   e = cudaLaunchKernelEx(&lc, v.fn, *s.x, *s.w, *s.up, *s.out, p);
+  if (nvtx_enabled()) nvtxRangePop();
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
   g_launches.fetch_add(1);
   return SGL_OK;

@@ -99,3 +99,33 @@ def test_debug_build_records_nothing_and_matches_the_normal_library(tmp_path):
     assert da.keys() == db.keys() and len(da) > 20
     for k in da:
         assert torch.equal(da[k].view(torch.int16), db[k].view(torch.int16)), k
+
+
+def test_launch_tracing_is_off_by_default_and_on_by_environment():
+    """SGL_LOG=1 writes one line per kernel launch to stderr (form, shape, tile entry, grid);
+    SGL_NVTX=1 wraps the launches in NVTX ranges (harmless without a profiler); by default the
+    library prints nothing."""
+    code = textwrap.dedent('''
+        import torch
+        from swiglu_fused_b200 import matmul_fused_swiglu, _lib
+        x = torch.randn((300, 128), device="cuda:0").to(torch.bfloat16)
+        w = torch.randn((128, 512), device="cuda:0").to(torch.bfloat16)
+        matmul_fused_swiglu(x, w)
+        torch.cuda.synchronize()
+        _lib.device_status()
+        print("done")
+    ''')
+    env = dict(os.environ)
+    env["PYTHONPATH"] = ROOT + os.pathsep + env.get("PYTHONPATH", "")
+    for extra, expect in (({}, False), ({"SGL_LOG": "1", "SGL_NVTX": "1"}, True)):
+        e = dict(env)
+        e.pop("SGL_LOG", None)
+        e.pop("SGL_NVTX", None)
+        e.update(extra)
+        proc = subprocess.run([sys.executable, "-c", code], env=e, capture_output=True, text=True,
+                              timeout=300)
+        assert proc.returncode == 0 and "done" in proc.stdout, proc.stderr[-2000:]
+        lines = [ln for ln in proc.stderr.splitlines() if ln.startswith("[libswiglu_b200] launch")]
+        assert bool(lines) == expect, proc.stderr[-2000:]
+        if expect:
+            assert "fused_swiglu 300x256x128" in lines[0] and "grid=" in lines[0], lines[0]
