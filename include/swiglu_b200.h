@@ -56,7 +56,8 @@ enum {
 /*
  * One entry of the tile table.  Replaces the reference's (BN, BK, NS, GSM)
  * tuples, swiglu/matmul_silu_mul.py:30-41 and swiglu/matmul_fused_swiglu.py:34-41.
- * BM is 128 rows per CTA and the accumulator is 256 columns wide in every entry.
+ * BM is 128 rows per CTA and an accumulator is 256 columns wide in every entry (the `wide`
+ * entries of the fused form use two of them per tile).
  */
 typedef struct sgl_config {
   int32_t cta_group; /* 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
