@@ -111,17 +111,21 @@ __device__ unsigned long long g_prof[512][8];
 #ifdef SGL_DEBUG
 __device__ unsigned long long g_debug_counts[512][4];   // [cta]: produced, consumed, tiles, stores
 #define SGL_DBG_COUNT(slot, v) g_debug_counts[blockIdx.x & 511][slot] = static_cast<unsigned long long>(v)
-#define SGL_DBG_CHECK_COORD(ok_expr, detail)                                  \
-  if (!(ok_expr)) {                                                           \
-    if (atomicCAS(&g_status[0], 0u, 0x301u) == 0u) {                          \
-      g_status[1] = blockIdx.x;                                               \
-      g_status[2] = static_cast<unsigned>(detail);                            \
-    }                                                                         \
-    atomicAdd(&g_status[3], 1u);                                              \
+// true (after recording the violation) when the coordinate check fails; the caller skips
+// the copy.  Always false in the normal build, where the compiler drops the branch.
+__device__ __forceinline__ bool debug_coord_bad(bool ok, unsigned detail) {
+  if (ok) return false;
+  if (atomicCAS(&g_status[0], 0u, 0x301u) == 0u) {
+    g_status[1] = blockIdx.x;
+    g_status[2] = detail;
   }
+  atomicAdd(&g_status[3], 1u);
+  return true;
+}
+#define SGL_DBG_COORD_BAD(ok_expr, detail) debug_coord_bad((ok_expr), static_cast<unsigned>(detail))
 #else
 #define SGL_DBG_COUNT(slot, v)
-#define SGL_DBG_CHECK_COORD(ok_expr, detail)
+#define SGL_DBG_COORD_BAD(ok_expr, detail) false
 #endif
 
 struct KernelParams {
@@ -452,12 +456,17 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           SGL_PROF_END(prof_pe, tp0);
           const uint32_t full_local = bar_full + 8 * s;
           const uint32_t full = (kCtaGroup == 2) ? ptx::mapa(full_local, 0) : full_local;
-          ptx::mbar_arrive_expect_tx_cluster(full, stage_tx);
           const int k0 = k_base + kb * kBlockK;
-          SGL_DBG_CHECK_COORD(k0 >= 0 && k0 < p.K && (k0 & 7) == 0 && m0 >= 0 &&
-                                  m0 < p.tiles_m * kCtaGroup * kBlockM && n0 >= 0 && (n0 & 7) == 0 &&
-                                  ((p.b_col0 | p.b_col1) & 7) == 0,
-                              kb);
+          if (SGL_DBG_COORD_BAD(k0 >= 0 && k0 < p.K && (k0 & 7) == 0 && m0 >= 0 &&
+                                    m0 < p.tiles_m * kCtaGroup * kBlockM && n0 >= 0 &&
+                                    (n0 & 7) == 0 && ((p.b_col0 | p.b_col1) & 7) == 0,
+                                kb)) {
+            // no copy is issued with a bad coordinate: raise the abort flag and leave
+            *reinterpret_cast<volatile int*>(abort_flag) = 1;
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx_cluster(full, stage_tx);
 #ifdef SGL_DEBUG
           ++dbg_produced;
 #endif
@@ -643,9 +652,11 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       const TileCoord tc = shifted_tile((cluster_id + i * num_clusters) / splits);
       x = tc.n * tile_cols + c * kChunkCols;
       y = (tc.m * kCtaGroup + static_cast<int>(rank)) * kBlockM + q * 32;
-      SGL_DBG_CHECK_COORD(x >= 0 && (x & 7) == 0 && y >= 0 && (y & 31) == 0 &&
-                              x < p.tiles_n * tile_cols && y < p.tiles_m * kCtaGroup * kBlockM,
-                          g);
+      if (SGL_DBG_COORD_BAD(x >= 0 && (x & 7) == 0 && y >= 0 && (y & 31) == 0 &&
+                                x < p.tiles_n * tile_cols && y < p.tiles_m * kCtaGroup * kBlockM,
+                            g)) {
+        x = 0x7fffff00;   // beyond N: every store and `up` load of this chunk is skipped
+      }
     };
 
     const uint64_t pol_h = ptx::make_l2_policy((p.l2_hints >> 4) & 3);
