@@ -349,9 +349,9 @@ void default_config(int form, int64_t M, sgl_config* c) {
     c->cta_group = 2;
     c->block_k = 128;
     c->group_m = 16;   // silu_mul at 32768 x 3072 x 12288: 1.96 ms against 2.00 with bands of 8
-  } else if (M >= 1024) {
+  } else if (form == SGL_FORM_SILU_MUL && M >= 1024) {
     c->cta_group = 2;
-    c->block_k = 128;  // silu_mul / GEMM at 1024 rows: 111 against 116 us (4096 x 14336)
+    c->block_k = 128;  // silu_mul at 1024 x 4096 x 14336: 111 against 116 us
     c->group_m = 8;
   } else {
     c->cta_group = 2;
