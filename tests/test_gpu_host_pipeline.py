@@ -172,3 +172,41 @@ def test_pipeline_calls_leave_the_current_device_alone():
     assert torch.cuda.current_device() == 0
     pipe.close()
     assert torch.cuda.current_device() == 0
+
+
+def test_shared_weight_pipeline_reports_a_peer_that_never_sends():
+    """Two ranks' regions on one GPU, but only rank 0 ever runs: its launch over rank 1's slice
+    waits for a flag that nobody raises.  With the wait limit set to 50 ms the one-thread wait
+    kernel gives up, `run` returns a device-status error naming the missing rank - nothing
+    hangs - and the context keeps computing correct results afterwards."""
+    import ctypes as C
+
+    M, K, N = 1024, 128, 512
+    x, w = fused_problem(M, K, N, seed=91)
+    lib = _lib.load()
+    nbytes = lib.sgl_host_pipeline_shared_bytes(_lib.FORM_FUSED_SWIGLU, N, K)
+    regions = [torch.zeros(nbytes, dtype=torch.uint8, device=DEV) for _ in range(2)]
+    ptrs = (C.c_void_p * 2)(*[r.data_ptr() for r in regions])
+    handle = C.c_void_p()
+    _lib.check(lib.sgl_host_pipeline_create_shared(_lib.FORM_FUSED_SWIGLU, M, N, K, 0, 0, 0, None,
+                                                   2, 0, ptrs, C.byref(handle)))
+    xh, wh = x.pin_memory(), w.pin_memory()
+    hh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    _lib.set_wait_limit_ns(50_000_000)
+    try:
+        rc = lib.sgl_host_pipeline_run(handle, xh.data_ptr(), K, wh.data_ptr(), 2 * N, None, 0,
+                                       hh.data_ptr(), N, 1)
+        assert rc == -9, (rc, lib.sgl_last_error())           # SGL_ERR_DEVICE_STATUS
+        msg = lib.sgl_last_error().decode()
+        assert "rank 1" in msg and "did not arrive" in msg
+        # rank 0's own slice did reach the "peer": its flag is raised in rank 1's region
+        flags = regions[1][-1024:].view(torch.int32)
+        assert int(flags[0]) == 1
+    finally:
+        _lib.set_wait_limit_ns(2_000_000_000)
+        lib.sgl_host_pipeline_destroy(handle)
+    torch.cuda.synchronize()
+    _lib.device_status()                                      # the record was cleared by run
+    want = matmul_fused_swiglu(x.to(DEV), w.to(DEV))
+    ref32 = orc.fused_swiglu_f32(x, w)
+    assert orc.compare(want.cpu(), ref32.to(torch.bfloat16), ref32).ok
