@@ -94,3 +94,25 @@ def test_shipped_tile_table_entries_are_valid_configurations():
         assert M >= 1 and N % 8 == 0 and K % 8 == 0
     # the headline shape is tuned
     assert tile_table.lookup(_lib.FORM_FUSED_SWIGLU, 32768, 12288, 3072) is not None
+
+
+def test_gather_mode_is_validated_before_anything_is_launched():
+    """`fused_swiglu_n_sharded_fused_gather` rejects an unknown mode, and the multicast mode
+    without a multicast mapping, before it touches a barrier or a kernel."""
+    import types
+
+    import torch
+
+    from swiglu_fused_b200 import sharding
+
+    calls = []
+    out = types.SimpleNamespace(rank=0, world=2, multicast_ptr=0, ptrs=[0, 0],
+                                tensor=torch.zeros((4, 8), dtype=torch.bfloat16),
+                                barrier=lambda: calls.append("barrier"))
+    x = torch.zeros((4, 8), dtype=torch.bfloat16)
+    w = torch.zeros((8, 16), dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="unknown gather mode"):
+        sharding.fused_swiglu_n_sharded_fused_gather(x, w, out, mode="bogus")
+    with pytest.raises(ValueError, match="no multicast mapping"):
+        sharding.fused_swiglu_n_sharded_fused_gather(x, w, out, mode="multicast")
+    assert calls == []
