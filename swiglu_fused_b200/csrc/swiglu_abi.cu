@@ -1323,6 +1323,17 @@ int sgl_debug_counts(unsigned long long* out) {
 #endif
 
 #ifdef SGL_PROFILE
+// Profiling builds only: the per-CTA %globaltimer stamps of the LAST launch (512 x 8 words).
+int sgl_debug_timeline(unsigned long long* out) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
+  e = cudaMemcpyFromSymbol(out, sgl::g_tl, sizeof(unsigned long long) * 512 * 8);
+  if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyFromSymbol(tl)");
+  return SGL_OK;
+}
+#endif
+
+#ifdef SGL_PROFILE
 // Profiling builds only: copy the per-CTA cycle counters (512 x 8 words).
 int sgl_debug_profile(unsigned long long* out) {
   cudaError_t e = cudaDeviceSynchronize();

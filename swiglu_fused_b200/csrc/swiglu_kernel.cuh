@@ -128,6 +128,17 @@ __device__ __forceinline__ bool debug_coord_bad(bool ok, unsigned detail) {
 #define SGL_DBG_COORD_BAD(ok_expr, detail) false
 #endif
 
+// Profiling builds also stamp %globaltimer at eight points of every CTA's life: [0] CTA start,
+// [1] set-up done, [2] past the dependent-launch wait, [3] first operands landed, [4] last MMA
+// committed, [5] epilogue sees the last accumulator, [6] epilogue's stores have read their
+// staging, [7] teardown done.  What a single-tile launch spends outside its K loop.
+#ifdef SGL_PROFILE
+__device__ unsigned long long g_tl[512][8];
+#define SGL_TL(slot) g_tl[blockIdx.x & 511][slot] = ptx::globaltimer_ns()
+#else
+#define SGL_TL(slot)
+#endif
+
 struct KernelParams {
   int M, N, K;          // N = output columns of h
   int b_col0;           // first B column: gate (silu_mul form) / up (fused form)
@@ -331,6 +342,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) { SGL_TL(0); }
   const uint32_t rank = (kCtaGroup == 2) ? ptx::cluster_ctarank() : 0u;
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
@@ -418,8 +430,10 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   // be complete and its writes visible.  In turn the next kernel of the stream may be set up
   // from now on (it waits at the same point).  Both are no-ops when the neighbour in the
   // stream is an ordinary launch.
+  if (threadIdx.x == 0) { SGL_TL(1); }
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (threadIdx.x == 0) { SGL_TL(2); }
 
   const uint64_t limit = p.wait_limit_ns;
 
@@ -583,6 +597,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             break;
           }
           SGL_PROF_END(prof_fu, tm1);
+          if (kb == 0 && i == 0) { SGL_TL(3); }
           ptx::tc_fence_after_sync();
           const uint32_t a_base = sA + s * T::kAStageBytes;
           const uint32_t b_base = sB + s * T::kBStageBytes;
@@ -622,6 +637,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           }
         }
         if (ok) ptx::umma_commit<kCtaGroup>(bar_tfull + 8 * as, mask);
+        SGL_TL(4);
       }
       SGL_PROF_END(prof_tot, tm_all);
       SGL_PROF_STORE(0, prof_te);
@@ -699,6 +715,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
       }
       ptx::tc_fence_after_sync();
+      if (q == 0 && lane == 0) { SGL_TL(5); }
       SGL_PROF_BEGIN(te_busy);
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * kAccCols;
 
@@ -979,6 +996,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       SGL_PROF_END(prof_busy, te_busy);
     }
     if (lane == 0 && q == 0) {
+      SGL_TL(6);
       SGL_DBG_COUNT(2, ok ? my_tiles : 0);
       SGL_PROF_STORE(4, prof_tf);
       SGL_PROF_STORE(5, prof_up);
@@ -1014,6 +1032,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);
+    if (lane == 0) { SGL_TL(7); }
   }
 }
 

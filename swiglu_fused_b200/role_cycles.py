@@ -47,6 +47,9 @@ def main() -> None:
     ap.add_argument("--n", "--cols", dest="n", type=int, default=12288)
     ap.add_argument("--block-k", type=int, default=0, help="0 = the default configuration")
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--timeline", action="store_true",
+                    help="also print where a CTA's time goes outside the K loop (set-up, first "
+                         "operands, epilogue, teardown): %%globaltimer stamps of the last launch")
     ap.add_argument("--gather", choices=("none", "tma", "stores", "multicast"), default=None,
                     help="column-parallel launch over the ranks of a torchrun group: each rank "
                          "computes N / world columns; 'none' keeps them local, the others "
@@ -126,6 +129,8 @@ def main() -> None:
     n_ctas = min(512, _lib.query(_lib.QUERY_SM_COUNT))
     p = np.frombuffer(buf, dtype=np.uint64).reshape(512, 8)[:n_ctas].astype(np.float64)
     lead = p[0::cfg.cta_group]              # the MMA issuer runs in the leader CTA of a pair
+    lead = lead[lead[:, 2] > 0]             # a short problem does not occupy every SM
+    p = p[p[:, 7] > 0] if (p[:, 7] > 0).any() else p
     loop = lead[:, 2]
     tiles = np.maximum(lead[:, 7], 1)
     kblocks = tiles * (-(-K // 64))
@@ -147,6 +152,20 @@ def main() -> None:
           f"{100 * p[:, 6].mean() / loop.mean():.1f} %")
     print(f"  load balance: slowest / mean CTA = {loop.max() / loop.mean():.4f}, "
           f"tiles per CTA {int(tiles.min())}..{int(tiles.max())}")
+    if args.timeline:
+        lib.sgl_debug_timeline.restype = C.c_int
+        lib.sgl_debug_timeline.argtypes = [C.POINTER(C.c_ulonglong)]
+        tbuf = (C.c_ulonglong * (512 * 8))()
+        _lib.check(lib.sgl_debug_timeline(tbuf))
+        t = np.frombuffer(tbuf, dtype=np.uint64).reshape(512, 8).astype(np.int64)
+        t = t[t[:, 0] > 0]                  # the CTAs of this process's launches
+        t0 = t[:, 0].min()
+        names = ("CTA start", "set-up done", "past the dependent-launch wait",
+                 "first operands landed", "last MMA committed", "epilogue sees the accumulator",
+                 "epilogue's stores have read", "teardown done")
+        print("  timeline, ns after the first CTA started (mean / max over the CTAs):")
+        for i, name in enumerate(names):
+            print(f"    {name:34s} {np.mean(t[:, i] - t0):9.0f} {np.max(t[:, i] - t0):9.0f}")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
