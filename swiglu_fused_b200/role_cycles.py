@@ -1,7 +1,7 @@
 """Cycle accounting of the kernel's roles (developer tool).
 
     python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|fused_swiglu_save|silu_mul] [--rows M]
-                                            [--block-k 64|128] [--group-m G]
+                                            [--block-k 64|128] [--group-m G] [--timeline]
     torchrun --nproc-per-node W -m swiglu_fused_b200.role_cycles --k 8192 --cols 28672 \
              --gather none|tma|stores|multicast      # column-parallel over W GPUs, rank 0 reports
 
@@ -11,7 +11,9 @@ spends waiting: the MMA issuer for a free accumulator and for operands, the TMA 
 free ring slot, the epilogue for an accumulator and for ``up``.  Prints the averages as a share
 of the MMA loop, the cycles per 64-wide k-block against the 512-cycle tensor-core ideal, and the
 spread between the fastest and the slowest CTA pair (what a dynamic tile scheduler could gain).
-The normal library carries none of this code.
+``--timeline`` prints instead when, after the launch reached the GPU, a CTA passed eight points
+of its life (set-up done, first operands landed, last MMA committed, stores read, ...), which
+is how the fixed cost of a short launch splits up.  The normal library carries none of this code.
 """
 from __future__ import annotations
 
