@@ -42,8 +42,10 @@ def build_profile_library() -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--form", choices=("fused_swiglu", "fused_swiglu_save", "silu_mul"),
-                    default="fused_swiglu")
+    ap.add_argument("--form", choices=("fused_swiglu", "fused_swiglu_save", "silu_mul", "grad_x", "grad_w"),
+                    default="fused_swiglu",
+                    help="grad_x / grad_w: the backward GEMMs g @ W^T and x^T @ g of the same "
+                         "problem (GEMM form, transposed operand read in place)")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--n", "--cols", dest="n", type=int, default=12288)
@@ -63,7 +65,8 @@ def main() -> None:
     import torch
 
     from . import _lib
-    from .ops import matmul_fused_swiglu, matmul_fused_swiglu_save_factors, matmul_silu_mul
+    from .ops import (matmul_bf16, matmul_fused_swiglu, matmul_fused_swiglu_save_factors,
+                      matmul_silu_mul)
 
     rank, world, sym = 0, 1, None
     dev = torch.device("cuda:0")
@@ -78,8 +81,13 @@ def main() -> None:
     w = torch.empty((K, 2 * N), device=dev, dtype=torch.bfloat16).normal_(0, K ** -0.5, generator=g)
     out = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
     form = {"fused_swiglu": _lib.FORM_FUSED_SWIGLU, "fused_swiglu_save": _lib.FORM_FUSED_SWIGLU_SAVE,
-            "silu_mul": _lib.FORM_SILU_MUL}[args.form]
+            "silu_mul": _lib.FORM_SILU_MUL}.get(args.form, _lib.FORM_MATMUL)
+    depth = K                               # contraction depth of the launch that is profiled
     cfg = _lib.default_config(form, M, N, K)
+    if args.form == "grad_x":               # [M, 2N] @ [2N, K]
+        depth, cfg = 2 * N, _lib.default_config(form, M, K, 2 * N)
+    elif args.form == "grad_w":             # [K, M] @ [M, 2N]
+        depth, cfg = M, _lib.default_config(form, K, 2 * N, M)
     if args.block_k or args.group_m:
         cfg = _lib.TileConfig(cfg.cta_group, args.block_k or cfg.block_k, 0,
                               args.group_m or cfg.group_m)
@@ -100,6 +108,16 @@ def main() -> None:
     elif args.form == "fused_swiglu":
         def run():
             matmul_fused_swiglu(x, w, out=out, config=cfg)
+    elif args.form in ("grad_x", "grad_w"):
+        gp = torch.randn((M, 2 * N), device=dev, dtype=torch.bfloat16, generator=g)
+        grad = torch.empty((M, K) if args.form == "grad_x" else (K, 2 * N), device=dev,
+                           dtype=torch.bfloat16)
+        if args.form == "grad_x":
+            def run():
+                matmul_bf16(gp, w, transpose_b=True, out=grad, config=cfg)
+        else:
+            def run():
+                matmul_bf16(x, gp, transpose_a=True, out=grad, config=cfg)
     elif args.form == "fused_swiglu_save":
         factors = torch.empty((M, 2 * N), device=dev, dtype=torch.bfloat16)
 
@@ -135,7 +153,7 @@ def main() -> None:
     p = p[p[:, 7] > 0] if (p[:, 7] > 0).any() else p
     loop = lead[:, 2]
     tiles = np.maximum(lead[:, 7], 1)
-    kblocks = tiles * (-(-K // 64))
+    kblocks = tiles * (-(-depth // 64))
     if rank != 0:
         dist.barrier()
         dist.destroy_process_group()
