@@ -206,8 +206,19 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
  * caller owns; sgl_matmul_bf16_splitk_scratch_bytes says how much this problem needs
  * (negative sgl_status on a bad shape).  Contents of scratch are overwritten; two calls that
  * overlap on the GPU must not share it.  No counterpart in the reference.
+ *
+ * Where the K ranges of a tile can run as one thread-block cluster (single-CTA tiles - M <= 128
+ * with the default configuration -, 2 to 16 ranges, all clusters resident at once) neither the
+ * scratch nor the second kernel is used: every CTA keeps its fp32 partial tile in shared
+ * memory, the CTAs of a cluster read one another's (distributed shared memory) and each sums
+ * and stores its share of the tile.  The additions are the same in the same order, so the
+ * result is the two-kernel form's bit for bit; a K range that never reports is a bounded
+ * wait (code 0x106 in sgl_device_status).  sgl_set_splitk_cluster_sum(0), or
+ * SGL_SPLITK_CLUSTER_SUM=0 in the environment, keeps every problem on the two-kernel form;
+ * the call returns the previous setting.
  */
 int64_t sgl_matmul_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int64_t K, int splits);
+int sgl_set_splitk_cluster_sum(int enabled);
 int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                            int64_t lda, int64_t ldb, int64_t ldc, int splits, void* scratch,
                            int64_t scratch_bytes, const sgl_config* cfg, void* stream);

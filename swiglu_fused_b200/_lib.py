@@ -62,6 +62,7 @@ EXPORTED_SYMBOLS = (
     "sgl_device_status",
     "sgl_selftest_wait_timeout",
     "sgl_set_wait_limit_ns",
+    "sgl_set_splitk_cluster_sum",
     "sgl_host_pipeline_create",
     "sgl_host_pipeline_shared_bytes",
     "sgl_host_pipeline_plan",
@@ -235,6 +236,8 @@ def load() -> C.CDLL:
         lib.sgl_selftest_wait_timeout.argtypes = [C.c_uint64, vp]
         lib.sgl_set_wait_limit_ns.restype = ip
         lib.sgl_set_wait_limit_ns.argtypes = [C.c_uint64]
+        lib.sgl_set_splitk_cluster_sum.restype = ip
+        lib.sgl_set_splitk_cluster_sum.argtypes = [ip]
         lib.sgl_host_pipeline_create.restype = ip
         lib.sgl_host_pipeline_create.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp,
                                                  C.POINTER(vp)]
@@ -344,6 +347,13 @@ def device_status() -> list[int]:
 
 def set_wait_limit_ns(ns: int) -> None:
     check(load().sgl_set_wait_limit_ns(ns))
+
+
+def set_splitk_cluster_sum(enabled: bool) -> bool:
+    """Whether split-K problems whose K ranges can form thread-block clusters are summed inside
+    the GEMM launch through distributed shared memory (default) or always through scratch
+    memory and a second kernel.  Returns the previous setting."""
+    return bool(load().sgl_set_splitk_cluster_sum(int(bool(enabled))))
 
 
 def host_pipeline_plan(M: int, N: int, *, first_rows: int = 0, block_rows: int = 0,

@@ -102,6 +102,58 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+// Arrive on a barrier of another CTA of the cluster so that this thread's earlier writes to
+// its own shared memory (and those of threads it has synchronised with) are visible to whoever
+// then waits on that barrier with cluster-scope acquire.
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// mbar_wait for a barrier that CTAs of the whole cluster arrive on (same bound, same abort flag).
+__device__ __forceinline__ bool mbar_wait_acquire_cluster(uint32_t bar, uint32_t parity,
+                                                          uint64_t limit_ns,
+                                                          const volatile int* abort_flag) {
+  if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+  uint64_t t0 = 0;
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+    if ((it & 255u) == 0u) {
+      if (*abort_flag != 0) return false;
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > limit_ns) {
+        return false;
+      }
+    }
+  }
+}
+
+// 16 bytes from the shared memory of a CTA of this cluster (address from mapa).
+__device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_bar,
                                                               uint32_t bytes) {
   // Default semantics (release at CTA scope): a cluster-scope release here costs a

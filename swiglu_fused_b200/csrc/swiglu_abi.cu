@@ -243,6 +243,9 @@ struct DeviceInfo {
   int max_smem_optin = 0;
   int max_clusters[20] = {};  // per variant, 0 = not yet queried
   int smem_set[20] = {};      // dynamic smem attribute already raised to
+  // split-K summed in the cluster: clusters of n single-CTA tiles that can be resident at once,
+  // per variant and n (0 = not yet asked, -1 = such clusters cannot be launched here)
+  int max_k_clusters[20][17] = {};
 };
 
 std::mutex g_dev_mutex;
@@ -397,11 +400,32 @@ struct LaunchSpec {
   int out_f32 = 0;
   int reduce_rows = 0, reduce_add = 0, first_dst = 0;     // reduce-scatter epilogue
   int splits = 1, k_per_split = 0, slot_rows = 0;         // split-K
+  int acc_cols = 0;                                       // GEMM form: tile width (0 = choose)
   int a_rows = sgl::kBlockM;                              // rows of the A box (see a_box_rows)
   int peer_mode = 0, n_peer = 0;                          // gather by thread stores
   int64_t peer_ld = 0;
   const void* peer_ptr[sgl::kMaxDst] = {};
+  // split-K: where the K ranges may be summed inside the launch (KernelParams::cluster_sum)
+  void* sum_out = nullptr;           // bf16 result, row pitch sum_ld
+  int64_t sum_ld = 0;
+  bool* summed = nullptr;            // set to true when the launch wrote the result itself
 };
+
+// Split-K problems whose K ranges can form thread-block clusters are summed inside the GEMM
+// launch through distributed shared memory.  sgl_set_splitk_cluster_sum(0) switches that off
+// (partial tiles through scratch memory and a second kernel, as for every other problem);
+// SGL_SPLITK_CLUSTER_SUM=0 in the environment does the same from outside.
+std::atomic<int> g_splitk_cluster_sum{-1};   // -1 = not yet read from the environment
+
+bool splitk_cluster_sum_enabled() {
+  int v = g_splitk_cluster_sum.load();
+  if (v < 0) {
+    const char* e = getenv("SGL_SPLITK_CLUSTER_SUM");
+    v = (e && e[0] == '0') ? 0 : 1;
+    g_splitk_cluster_sum.store(v);
+  }
+  return v != 0;
+}
 
 // Rows of the A operand's TMA box.  A problem shorter than one 128-row tile loads only the rows
 // it has (rounded up to the 8-row swizzle atom): the rest of the tile's rows in shared memory
@@ -438,6 +462,69 @@ int query_max_clusters(const Variant& v, int cta_group, int sm_count) {
   return n > 0 ? n : 1;
 }
 
+// Clusters of n CTAs of a single-CTA variant that can be resident at once with `smem` bytes
+// each (sizes above 8 need the kernel's consent to a non-portable cluster size).  Negative:
+// the driver cannot place such clusters.  Call with g_dev_mutex held.
+int query_k_clusters(const Variant& v, int n, int smem) {
+  cudaError_t e;
+  if (n > 8) {
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
+                             cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+  }
+  cudaLaunchConfig_t qc = {};
+  qc.gridDim = dim3(static_cast<unsigned>(n), 1, 1);
+  qc.blockDim = dim3(sgl::kNumThreads, 1, 1);
+  qc.dynamicSmemBytes = static_cast<size_t>(smem);
+  cudaLaunchAttribute qa[1];
+  qa[0].id = cudaLaunchAttributeClusterDimension;
+  qa[0].val.clusterDim.x = static_cast<unsigned>(n);
+  qa[0].val.clusterDim.y = 1;
+  qa[0].val.clusterDim.z = 1;
+  qc.attrs = qa;
+  qc.numAttrs = 1;
+  int q = 0;
+  e = cudaOccupancyMaxActiveClusters(&q, reinterpret_cast<const void*>(v.fn), &qc);
+  if (e != cudaSuccess || q < 1) {
+    cudaGetLastError();
+    return -1;
+  }
+  return q;
+}
+
+// First use of this variant on this device: raise its dynamic shared-memory limit to the
+// deepest ring and ask how many clusters fit.
+int prepare_variant(DeviceInfo* info, const Variant& v, int vi, int cta_group) {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  const int smem_max = v.smem_bytes(v.max_stages);
+  if (info->smem_set[vi] < smem_max) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
+    if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(max dynamic smem)");
+    info->smem_set[vi] = smem_max;
+  }
+  if (info->max_clusters[vi] == 0)
+    info->max_clusters[vi] = query_max_clusters(v, cta_group, info->sm_count);
+  return SGL_OK;
+}
+
+// Clusters of n CTAs of single-CTA variant vi that fit at once (cached; <= 0: none).
+int k_clusters(DeviceInfo* info, const Variant& v, int vi, int n, int smem) {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  int& q = info->max_k_clusters[vi][n];
+  if (q == 0) q = query_k_clusters(v, n, smem);
+  return q;
+}
+
+// Whether this configuration's ring can hold a partial tile for the cluster sum.
+bool ring_holds_partial_tile(const Variant& v, int stages) {
+  return static_cast<int64_t>(stages) * (v.smem_bytes(2) - v.smem_bytes(1)) >=
+         static_cast<int64_t>(sgl::kRedBytes);
+}
+
 int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* stream) {
   const int wide = (cfg.wide && !s.b_kmajor) ? 1 : 0;   // the [n, k] layout has no wide form
   const int vi = variant_index(s.form, cfg.cta_group, cfg.block_k, wide);
@@ -453,7 +540,9 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   // problem with few 256-column tiles leaves most SMs idle while a handful stream all of B;
   // halve the tile width (down to 64) while the tiles still fit half the SMs.
   int acc_cols = sgl::kAccCols;
-  if (s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && !s.b_kmajor && s.splits == 1 &&
+  if (s.acc_cols > 0 && s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && !s.b_kmajor) {
+    acc_cols = s.acc_cols;   // the caller's plan (split-K summed in clusters)
+  } else if (s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && !s.b_kmajor && s.splits == 1 &&
       s.reduce_rows == 0) {
     while (acc_cols > 64 && tiles_m * ((s.N + acc_cols - 1) / acc_cols) * 2 <= info->sm_count)
       acc_cols /= 2;
@@ -464,26 +553,24 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   if (units > 0x7fffffffll) return fail(SGL_ERR_BAD_SHAPE, "too many tiles");
 
   cudaError_t e;
-  {
-    // First launch of this variant on this device: raise its dynamic shared-memory limit to
-    // the deepest ring and ask how many clusters fit.
-    std::lock_guard<std::mutex> lock(g_dev_mutex);
-    const int smem_max = v.smem_bytes(v.max_stages);
-    if (info->smem_set[vi] < smem_max) {
-      e = cudaFuncSetAttribute(reinterpret_cast<const void*>(v.fn),
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem_max);
-      if (e != cudaSuccess) return fail_cuda(e, "cudaFuncSetAttribute(max dynamic smem)");
-      info->smem_set[vi] = smem_max;
-    }
-    if (info->max_clusters[vi] == 0)
-      info->max_clusters[vi] = query_max_clusters(v, cfg.cta_group, info->sm_count);
+  int rc_ready = prepare_variant(info, v, vi, cfg.cta_group);
+  if (rc_ready) return rc_ready;
+  // Split-K summed in the cluster: the K ranges of a tile are the CTAs of one cluster, every
+  // unit has its own CTA, all clusters fit at once, and the ring holds a partial tile.
+  bool cluster_sum = false;
+  if (s.sum_out && s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && s.splits >= 2 &&
+      s.splits <= 16 && cfg.max_ctas == 0 && splitk_cluster_sum_enabled() &&
+      ring_holds_partial_tile(v, cfg.stages)) {
+    cluster_sum = tiles_m * tiles_n <= k_clusters(info, v, vi, s.splits, smem);
   }
+  if (s.summed) *s.summed = cluster_sum;
 
   int64_t clusters = info->max_clusters[vi];
   if (cfg.max_ctas > 0 && cfg.max_ctas / cfg.cta_group < clusters)
     clusters = cfg.max_ctas / cfg.cta_group;
   if (clusters < 1) clusters = 1;
   if (units < clusters) clusters = units;
+  if (cluster_sum) clusters = units;   // one unit per CTA
 
   sgl::KernelParams p;
   p.M = static_cast<int>(s.M);
@@ -520,6 +607,9 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
         (static_cast<int64_t>(s.first_dst) * s.reduce_rows / rows_per_tile) % tiles_m);
   }
   p.wait_limit_ns = g_wait_limit_ns.load();
+  p.cluster_sum = cluster_sum ? 1 : 0;
+  p.sum_out = reinterpret_cast<unsigned long long>(s.sum_out);
+  p.sum_ld = s.sum_ld;
 
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(clusters * cfg.cta_group), 1, 1);
@@ -528,7 +618,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   lc.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attrs[2];
   attrs[0].id = cudaLaunchAttributeClusterDimension;
-  attrs[0].val.clusterDim.x = static_cast<unsigned>(cfg.cta_group);
+  attrs[0].val.clusterDim.x = static_cast<unsigned>(cluster_sum ? s.splits : cfg.cta_group);
   attrs[0].val.clusterDim.y = 1;
   attrs[0].val.clusterDim.z = 1;
   // the kernel orders itself behind its predecessor with griddepcontrol.wait, so its set-up
@@ -541,11 +631,11 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   if (log_enabled() || nvtx_enabled()) {
     snprintf(label, sizeof(label),
              "sgl %s %lldx%lldx%lld cta_group=%d block_k=%d stages=%d group_m=%d group_n=%d "
-             "wide=%d splits=%d n_dst=%d grid=%lld smem=%d",
+             "wide=%d splits=%d%s n_dst=%d grid=%lld smem=%d",
              form_name(s.form), static_cast<long long>(s.M), static_cast<long long>(s.N),
              static_cast<long long>(s.K), cfg.cta_group, cfg.block_k, cfg.stages, cfg.group_m,
-             cfg.group_n, wide, s.splits, s.n_dst, static_cast<long long>(clusters * cfg.cta_group),
-             smem);
+             cfg.group_n, wide, s.splits, cluster_sum ? " (summed in the cluster)" : "", s.n_dst,
+             static_cast<long long>(clusters * cfg.cta_group), smem);
     if (log_enabled()) fprintf(stderr, "[libswiglu_b200] launch %s\n", label);
     if (nvtx_enabled()) nvtxRangePushA(label);
   }
@@ -777,6 +867,7 @@ struct SplitPlan {
   int k_per_split;
   int slot_rows;
   int64_t scratch_bytes;
+  bool automatic;          // the caller left the number of ranges to the library
 };
 
 int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, SplitPlan* out,
@@ -784,6 +875,7 @@ int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, Split
   if (splits < 0 || splits > 64)
     return fail(SGL_ERR_BAD_ARGUMENT, "splits=%d outside [0, 64] (0 = choose)", splits);
   const bool automatic = splits == 0;
+  out->automatic = automatic;
   if (automatic) {
     // As many K ranges as fill ONE wave of workers (a second, partly filled wave would cost
     // as much as a full one), at least 512 of K each.  Up to 128 rows the default
@@ -843,7 +935,42 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   spec.k_per_split = plan.k_per_split;
   spec.slot_rows = plan.slot_rows;
   spec.a_rows = a_box_rows(M, cf.cta_group);
+  // Left to choose, and on single-CTA tiles: prefer a plan whose K ranges can meet in a
+  // thread-block cluster (no scratch traffic, no second kernel).  Clusters have to be placed
+  // whole, so fewer of the larger ones fit; the plan that puts the most CTAs to work wins,
+  // the wider tile on a tie (a narrower tile re-reads the rows of a more often).
+  if (plan.automatic && cf.cta_group == 1 && splitk_cluster_sum_enabled() && M <= sgl::kBlockM) {
+    const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
+    const int vi = variant_index(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
+    if ((rc = prepare_variant(info, v, vi, cf.cta_group))) return rc;
+    if (ring_holds_partial_tile(v, cf.stages)) {
+      const int smem = v.smem_bytes(cf.stages);
+      int64_t best_ctas = 0;
+      for (int cols = 256; cols >= 64; cols -= 64) {   // whole 64-column slabs of b
+        const int64_t tiles = (N + cols - 1) / cols;
+        for (int n = 8; n >= 2; --n) {
+          int64_t per = (K + n - 1) / n;
+          per = (per + 127) / 128 * 128;
+          const int ranges = static_cast<int>((K + per - 1) / per);
+          if (ranges != n || per < 512) continue;
+          if (tiles > k_clusters(info, v, vi, n, smem)) continue;
+          if (tiles * n > best_ctas) {
+            best_ctas = tiles * n;
+            spec.acc_cols = cols;
+            spec.splits = n;
+            spec.k_per_split = static_cast<int>(per);
+          }
+          break;   // fewer ranges of the same width only put fewer CTAs to work
+        }
+      }
+    }
+  }
+  bool summed = false;
+  spec.sum_out = c;
+  spec.sum_ld = ldc;
+  spec.summed = &summed;
   if ((rc = launch(spec, cf, info, stream))) return rc;
+  if (summed) return SGL_OK;   // the K ranges met in their cluster: c is written
   const int64_t vecs = M * (N / 8);
   int64_t blocks = (vecs + 255) / 256;
   const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
@@ -917,6 +1044,12 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
                 static_cast<long long>(scratch_bytes), static_cast<long long>(plan.scratch_bytes),
                 plan.splits);
   return matmul_splitk_run(a, b, c, M, N, K, lda, ldb, ldc, plan, scratch, cfg, info, stream);
+}
+
+int sgl_set_splitk_cluster_sum(int enabled) {
+  const bool before = splitk_cluster_sum_enabled();
+  g_splitk_cluster_sum.store(enabled ? 1 : 0);
+  return before ? 1 : 0;
 }
 
 // ---------------------------------------------------------------- no-allocation split-K
@@ -1323,11 +1456,11 @@ int sgl_debug_counts(unsigned long long* out) {
 #endif
 
 #ifdef SGL_PROFILE
-// Profiling builds only: the per-CTA %globaltimer stamps of the LAST launch (512 x 8 words).
+// Profiling builds only: the per-CTA %globaltimer stamps of the LAST launch (512 x 10 words).
 int sgl_debug_timeline(unsigned long long* out) {
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
-  e = cudaMemcpyFromSymbol(out, sgl::g_tl, sizeof(unsigned long long) * 512 * 8);
+  e = cudaMemcpyFromSymbol(out, sgl::g_tl, sizeof(unsigned long long) * 512 * 10);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyFromSymbol(tl)");
   return SGL_OK;
 }

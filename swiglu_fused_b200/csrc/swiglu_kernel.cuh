@@ -70,6 +70,7 @@ enum : unsigned {
   kErrMmaTmemEmptyWait = 0x103,
   kErrEpiTmemFullWait = 0x104,
   kErrEpiUpWait = 0x105,
+  kErrClusterSumWait = 0x106,   // split-K summed in the cluster: a K range never reported
   kErrDebugCoord = 0x301,     // -DSGL_DEBUG builds: a TMA coordinate failed its check
   kErrSelfTestWait = 0x1ff,   // the deliberate timeout of wait_timeout_selftest_kernel
 };
@@ -133,7 +134,7 @@ __device__ __forceinline__ bool debug_coord_bad(bool ok, unsigned detail) {
 // committed, [5] epilogue sees the last accumulator, [6] epilogue's stores have read their
 // staging, [7] teardown done.  What a single-tile launch spends outside its K loop.
 #ifdef SGL_PROFILE
-__device__ unsigned long long g_tl[512][8];
+__device__ unsigned long long g_tl[512][10];
 #define SGL_TL(slot) g_tl[blockIdx.x & 511][slot] = ptx::globaltimer_ns()
 #else
 #define SGL_TL(slot)
@@ -180,8 +181,24 @@ struct KernelParams {
   int a_rows;           // rows of the A box actually loaded per CTA and k-block: kBlockM, or the
                         // (8-aligned) row count of a problem shorter than one tile, whose
                         // missing rows would otherwise be fetched as zero fill at full cost
+  // Split-K summed inside the launch through distributed shared memory (FORM_GEMM, single-CTA
+  // tiles, one work unit per CTA): the `splits` K ranges of a tile are the CTAs of one
+  // thread-block cluster.  Each CTA puts its fp32 partial tile into its own shared memory (the
+  // operand ring, idle by then), tells every CTA of the cluster, waits (bounded) until all of
+  // them have done so, sums its share of the tile's elements over the CTAs in K-range order
+  // with ld.shared::cluster and writes bf16 straight to the result.  No scratch traffic, no
+  // second kernel; the additions are those of the two-launch form, so are the bits.
+  int cluster_sum;              // 0 = off; else out maps are unused and the result goes to:
+  unsigned long long sum_out;   // address of the bf16 result, element (0, 0)
+  long long sum_ld;             // its row pitch, elements
   unsigned long long wait_limit_ns;
 };
+
+// Shared-memory layout of a partial tile for the cluster sum: kBlockM rows of 256 fp32 with 16
+// bytes of padding, so that 32 lanes storing 16 bytes each at one column of 32 different rows
+// spread over all banks.
+constexpr uint32_t kRedPitchBytes = 256 * 4 + 16;
+constexpr uint32_t kRedBytes = kBlockM * kRedPitchBytes;
 
 // kWide (fused form, CTA pairs): one tile is 256 output columns - two MMAs per k-step into two
 // 256-column accumulators, up in TMEM columns [0, 256) and gate in [256, 512) - instead of 128.
@@ -389,6 +406,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const uint32_t bar_up = bar_tempty + 8 * kAccStages;    // [kEpiWarps][kUpBufs]
   const uint32_t tmem_slot = bar_up + 8 * kEpiWarps * kUpBufs;
   const uint32_t abort_slot = tmem_slot + 8;
+  const uint32_t bar_sum = abort_slot + 8;   // cluster sum: every epilogue warp of every K range
+  const bool cluster_sum = (kForm == FORM_GEMM && kCtaGroup == 1) && p.cluster_sum != 0;
   // Generic pointers to the two scalar slots.
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr =
@@ -409,6 +428,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       ptx::mbar_init(bar_tempty + 8 * s, kEpiWarps * kCtaGroup);  // one arrive per epilogue warp
     }
     for (int i = 0; i < kEpiWarps * kUpBufs; ++i) ptx::mbar_init(bar_up + 8 * i, 1);
+    if (cluster_sum) ptx::mbar_init(bar_sum, kEpiWarps * p.splits);
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_x);
     ptx::prefetch_tensormap(&tm_w);
@@ -420,7 +440,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if constexpr (kCtaGroup == 2) ptx::cluster_sync();
+  // (cluster sum: no CTA may arrive on a peer's barrier before the peer has initialised it)
+  if (kCtaGroup == 2 || cluster_sum) ptx::cluster_sync();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
@@ -795,10 +816,135 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           // this unit's K range has its own slot of slot_rows rows in the output tensor
           yy = y + ((cluster_id + i * num_clusters) % splits) * p.slot_rows;
         }
-        uint32_t nbuf = out_buf0;
         const int units32 = tile_cols / 32;
+        if (cluster_sum) {
+          // ---- split-K summed in the cluster (one unit per CTA, cluster = the tile's ranges) ----
+          const uint32_t my_range = ptx::cluster_ctarank();
+          const uint32_t red = sA;   // the operand ring: every load has landed and been consumed
+          const uint32_t my_row = red + static_cast<uint32_t>(q * 32 + lane) * kRedPitchBytes;
+          // (a warp whose 32 rows lie below the last row of the problem keeps nothing; tiles
+          // are whole 64-column slabs wide, so the 32-column reads go in pairs: one wait for
+          // two TMEM loads)
+          if (y < p.M) {
 #pragma unroll 1
-        for (int u = 0; u < units32; ++u) {
+            for (int u = 0; u < units32; u += 2) {
+              float acc0[32], acc1[32];
+              ptx::tmem_ld_32x32b_x32(t_row + u * 32, acc0);
+              ptx::tmem_ld_32x32b_x32(t_row + u * 32 + 32, acc1);
+              ptx::tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
+                                 my_row + static_cast<uint32_t>(u * 32 + 4 * j) * 4u),
+                             "f"(acc0[4 * j]), "f"(acc0[4 * j + 1]), "f"(acc0[4 * j + 2]),
+                             "f"(acc0[4 * j + 3])
+                             : "memory");
+              }
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
+                                 my_row + static_cast<uint32_t>(u * 32 + 32 + 4 * j) * 4u),
+                             "f"(acc1[4 * j]), "f"(acc1[4 * j + 1]), "f"(acc1[4 * j + 2]),
+                             "f"(acc1[4 * j + 3])
+                             : "memory");
+              }
+            }
+          }
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+          // This warp's 32 rows are in place: tell every CTA of the cluster (this one
+          // included).  One lane per destination: a cluster-scope release is a fence, and
+          // `splits` of them from one lane in turn cost 2 us.
+          if (lane < splits)
+            ptx::mbar_arrive_release_cluster(ptx::mapa(bar_sum, static_cast<uint32_t>(lane)));
+          if (q == 0 && lane == 0) { SGL_TL(8); }
+          const bool met = ptx::mbar_wait_acquire_cluster(bar_sum, 0, limit, abort_flag);
+          if (q == 0 && lane == 0) { SGL_TL(9); }
+          if (!__all_sync(0xffffffffu, met)) {
+            if (lane == 0) report_error(kErrClusterSumWait, my_range, abort_flag);
+            ok = false;
+            break;
+          }
+          // This CTA's share of the tile, in groups of 4 columns, summed over the K ranges in
+          // order starting from 0.f - element by element the additions of sum_slots_f32_kernel.
+          // The loads of a batch of ranges for four groups are issued before the first addition.
+          // (Sending the rows to their owners with st.shared::cluster instead, so that this sum
+          // reads local memory only, measured the same: the exchange itself, about 40 KB per
+          // CTA, is what takes the time.)
+          const int row0 = y - q * 32;
+          const int rows_valid = min(kBlockM, p.M - row0);
+          const int n_vec = min(tile_cols, p.N - x0) / 4;
+          const int total = rows_valid * n_vec;
+          const int per = (total + splits - 1) / splits;
+          const int hi = min(total, (static_cast<int>(my_range) + 1) * per);
+          const int te = q * 32 + lane;
+          __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.sum_out);
+          constexpr int kItems = 4, kBatch = 8, kEpiThreads = kEpiWarps * 32;
+#pragma unroll 1
+          for (int e0 = static_cast<int>(my_range) * per + te; e0 < hi;
+               e0 += kItems * kEpiThreads) {
+            uint32_t src[kItems];
+            long long dst_off[kItems];
+            bool on[kItems];
+            float4 sum[kItems];
+#pragma unroll
+            for (int k = 0; k < kItems; ++k) {
+              const int e = e0 + k * kEpiThreads;
+              on[k] = e < hi;
+              const int ee = on[k] ? e : e0;
+              const int r = ee / n_vec;
+              const int v = ee - r * n_vec;
+              src[k] = red + static_cast<uint32_t>(r) * kRedPitchBytes +
+                       static_cast<uint32_t>(v) * 16u;
+              dst_off[k] = static_cast<long long>(row0 + r) * p.sum_ld + x0 + 4 * v;
+              sum[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll 1
+            for (int s0 = 0; s0 < splits; s0 += kBatch) {
+              float4 t[kItems][kBatch];
+#pragma unroll
+              for (int j = 0; j < kBatch; ++j) {
+#pragma unroll
+                for (int k = 0; k < kItems; ++k) {
+                  if (s0 + j < splits)
+                    t[k][j] = ptx::ld_shared_cluster_v4(
+                        ptx::mapa(src[k], static_cast<uint32_t>(s0 + j)));
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < kBatch; ++j) {
+#pragma unroll
+                for (int k = 0; k < kItems; ++k) {
+                  if (s0 + j < splits) {
+                    sum[k].x += t[k][j].x;
+                    sum[k].y += t[k][j].y;
+                    sum[k].z += t[k][j].z;
+                    sum[k].w += t[k][j].w;
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < kItems; ++k) {
+              if (on[k]) {
+                uint2 o;
+                o.x = pack_bf16x2(sum[k].x, sum[k].y);
+                o.y = pack_bf16x2(sum[k].z, sum[k].w);
+                *reinterpret_cast<uint2*>(outp + dst_off[k]) = o;
+              }
+            }
+          }
+        } else {
+        uint32_t nbuf = out_buf0;
+        if (y >= p.M) {
+          // rows that do not exist (short or ragged M): hand the accumulator back, store nothing
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+        }
+#pragma unroll 1
+        for (int u = (y < p.M) ? 0 : units32; u < units32; ++u) {
           const bool first = f32 || (u & 1) == 0;   // first 32-column unit of a staging buffer
           const bool last = f32 || (u & 1) == 1;    // buffer complete after this unit
           if (first) {
@@ -857,6 +1003,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             ++gemm_stores;
           }
         }
+        }  // cluster sum / stores
       } else {
 #pragma unroll 1
       for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
@@ -864,6 +1011,19 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         chunk_xy(g, x, y);
         const uint32_t ubuf = up_buf0 + (g % kUpBufs) * kChunkBytes;
         const uint32_t obuf = kInPlace ? ubuf : out_buf0 + (g & (kOutBufs - 1)) * kChunkBytes;
+        if constexpr (kForm == FORM_FUSED) {
+          if (y >= p.M && p.peer_mode == 0) {
+            // This warp's 32 rows lie below the last row of the problem (a tile of a short or
+            // ragged M): nothing to read, compute or store.  Its share of the accumulator is
+            // handed back and the TMEM ports are left to the warps that have rows.
+            if (c == T::kChunksPerTile - 1) {
+              ptx::tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+            }
+            continue;
+          }
+        }
 
         if constexpr (kInPlace) {
           // The other buffer is free once the previous chunk's store has read it:
@@ -1028,7 +1188,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   __syncwarp();
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if constexpr (kCtaGroup == 2) ptx::cluster_sync();
+  // (cluster sum: peers may still be reading this CTA's partial tile; every path of every CTA
+  // gets here, because every wait above is bounded)
+  if (kCtaGroup == 2 || cluster_sum) ptx::cluster_sync();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc<kCtaGroup>(tmem_base, kTmemCols);

@@ -42,10 +42,14 @@ def build_profile_library() -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--form", choices=("fused_swiglu", "fused_swiglu_save", "silu_mul", "grad_x", "grad_w"),
+    ap.add_argument("--form", choices=("fused_swiglu", "fused_swiglu_save", "silu_mul", "grad_x", "grad_w",
+                             "down", "down_splitk"),
                     default="fused_swiglu",
                     help="grad_x / grad_w: the backward GEMMs g @ W^T and x^T @ g of the same "
-                         "problem (GEMM form, transposed operand read in place)")
+                         "problem (GEMM form, transposed operand read in place); down / "
+                         "down_splitk: the plain product [rows, k] @ [k, cols], unsplit or with "
+                         "K cut into ranges (then the cycles are those of the GEMM launch; the "
+                         "time also covers the slot sum)")
     ap.add_argument("--rows", type=int, default=32768)
     ap.add_argument("--k", type=int, default=3072)
     ap.add_argument("--n", "--cols", dest="n", type=int, default=12288)
@@ -84,6 +88,8 @@ def main() -> None:
             "silu_mul": _lib.FORM_SILU_MUL}.get(args.form, _lib.FORM_MATMUL)
     depth = K                               # contraction depth of the launch that is profiled
     cfg = _lib.default_config(form, M, N, K)
+    if args.form in ("down", "down_splitk"):
+        w = w[:, :N]                        # [K, N], row pitch 2N
     if args.form == "grad_x":               # [M, 2N] @ [2N, K]
         depth, cfg = 2 * N, _lib.default_config(form, M, K, 2 * N)
     elif args.form == "grad_w":             # [K, M] @ [M, 2N]
@@ -108,6 +114,15 @@ def main() -> None:
     elif args.form == "fused_swiglu":
         def run():
             matmul_fused_swiglu(x, w, out=out, config=cfg)
+    elif args.form == "down":
+        def run():
+            matmul_bf16(x, w, out=out, config=cfg)
+    elif args.form == "down_splitk":
+        from .ops import matmul_bf16_splitk, splitk_scratch_bytes
+        scratch = torch.empty(splitk_scratch_bytes(M, N, K), dtype=torch.uint8, device=dev)
+
+        def run():
+            matmul_bf16_splitk(x, w, out=out, scratch=scratch, config=cfg)
     elif args.form in ("grad_x", "grad_w"):
         gp = torch.randn((M, 2 * N), device=dev, dtype=torch.bfloat16, generator=g)
         grad = torch.empty((M, K) if args.form == "grad_x" else (K, 2 * N), device=dev,
@@ -175,17 +190,21 @@ def main() -> None:
     if args.timeline:
         lib.sgl_debug_timeline.restype = C.c_int
         lib.sgl_debug_timeline.argtypes = [C.POINTER(C.c_ulonglong)]
-        tbuf = (C.c_ulonglong * (512 * 8))()
+        tbuf = (C.c_ulonglong * (512 * 10))()
         _lib.check(lib.sgl_debug_timeline(tbuf))
-        t = np.frombuffer(tbuf, dtype=np.uint64).reshape(512, 8).astype(np.int64)
+        t = np.frombuffer(tbuf, dtype=np.uint64).reshape(512, 10).astype(np.int64)
         t = t[t[:, 0] > 0]                  # the CTAs of this process's launches
         t0 = t[:, 0].min()
         names = ("CTA start", "set-up done", "past the dependent-launch wait",
                  "first operands landed", "last MMA committed", "epilogue sees the accumulator",
                  "epilogue's stores have read", "teardown done")
         print("  timeline, ns after the first CTA started (mean / max over the CTAs):")
-        for i, name in enumerate(names):
-            print(f"    {name:34s} {np.mean(t[:, i] - t0):9.0f} {np.max(t[:, i] - t0):9.0f}")
+        order = list(range(8))
+        if (t[:, 8] >= t0).all():           # split-K summed in thread-block clusters
+            names += ("partial tile in shared memory", "all K ranges have reported")
+            order = [0, 1, 2, 3, 4, 5, 8, 9, 6, 7]
+        for i in order:
+            print(f"    {names[i]:34s} {np.mean(t[:, i] - t0):9.0f} {np.max(t[:, i] - t0):9.0f}")
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -166,6 +166,60 @@ def test_splitk_matches_fp32_reference_and_unsplit_kernel(M, K, N, splits):
         matmul_bf16_splitk(ad, bd, splits=splits, scratch=scratch[:need - 64])
 
 
+@pytest.mark.parametrize("M,K,N,splits", [(64, 14336, 4096, 8), (64, 14336, 4096, 0), (33, 4096, 264, 4),
+                                           (128, 2048, 512, 8), (8, 1024, 4096, 2), (100, 8192, 1000, 3),
+                                           (16, 512, 128, 2), (64, 8192, 2048, 16)])
+def test_splitk_summed_in_the_cluster_gives_the_bits_of_the_two_kernel_form(M, K, N, splits):
+    """Where the K ranges of a tile run as one thread-block cluster the partial tiles never
+    leave the SMs: one launch instead of two kernels and no scratch traffic.  Same fp32
+    additions in the same order: the result must be the two-kernel form's bit for bit, and the
+    scratch (still passed, for the problems that need it) must stay untouched."""
+    from swiglu_fused_b200.ops import matmul_bf16_splitk, splitk_scratch_bytes
+
+    a, b = problem(M, K, N, seed=7 * M + K + N + splits)
+    ad, bd = a.to(DEV), b.to(DEV)
+    need = splitk_scratch_bytes(M, N, K, splits)
+    scratch = torch.full((need + 256,), 0xFF, dtype=torch.uint8, device=DEV)
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        n0 = _lib.kernel_launches()
+        two = matmul_bf16_splitk(ad, bd, splits=splits, scratch=scratch[:need])
+        torch.cuda.synchronize()
+        assert _lib.kernel_launches() - n0 == 2
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+    _lib.set_splitk_cluster_sum(True)
+    scratch.fill_(0xFF)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = big[1:M + 1, 8:8 + N]
+    n0 = _lib.kernel_launches()
+    for _ in range(3):           # back to back: a launch must not disturb its successor
+        matmul_bf16_splitk(ad, bd, out=out, splits=splits, scratch=scratch[:need])
+    torch.cuda.synchronize()
+    launches = (_lib.kernel_launches() - n0) // 3
+    tiles = -(-N // 256)
+    if splits == 0:
+        # left to choose, the library takes a plan whose clusters all fit at once (narrower
+        # tiles, fewer ranges): one launch, and other K ranges than the two-kernel choice, so
+        # the fp32 additions differ in order
+        assert launches == 1
+        both = orc.compare(out.contiguous(), two)
+        assert both.ok and both.frac_exact >= 0.99, str(both)
+    else:
+        # clusters are placed whole: 15 of 8 CTAs fit a B200, so 16 tiles x 8 ranges stay on
+        # the two-kernel form; a handful of tiles always fits
+        assert launches == 1 if tiles <= 4 else launches in (1, 2), (launches, tiles)
+        assert torch.equal(out.contiguous().view(torch.int16), two.view(torch.int16))
+    if launches == 1:
+        assert bool((scratch == 0xFF).all()), "the cluster sum touched the scratch"
+    guard = big.clone()
+    guard[1:M + 1, 8:8 + N] = float("nan")
+    assert torch.isnan(guard).all(), "wrote outside the output"
+    ref32 = orc.matmul_f32(a, b)
+    assert orc.compare(out.cpu(), ref32.to(torch.bfloat16), ref32).ok
+    _lib.device_status()
+
+
 def test_reduce_scatter_rejects_bad_row_blocks():
     a = torch.zeros((256, 64), dtype=torch.bfloat16, device=DEV)
     b = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)

@@ -86,6 +86,17 @@ def test_automatic_split_count_gives_way_to_the_fixed_scratch():
     caller-scratch entry point told to use 4.  The driver's view of device memory must not
     move either (a cudaMalloc inside the library would not show in torch's own counters)."""
     lib = _lib.load()
+    # (with the K ranges summed in thread-block clusters the library would not touch the scratch
+    # at all for this problem and would choose its ranges differently; this test is about the
+    # two-kernel form, which every problem whose clusters do not fit still takes)
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        _automatic_split_count_gives_way(lib)
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+
+
+def _automatic_split_count_gives_way(lib):
     M, K, N = 128, 14336, 4096
     assert lib.sgl_matmul_bf16_splitk_scratch_bytes(M, N, K, 0) > STATIC_BYTES   # unconstrained
     assert lib.sgl_matmul_bf16_splitk_scratch_bytes(M, N, K, 4) == STATIC_BYTES
@@ -124,3 +135,29 @@ def test_static_scratch_entry_point_rejects_what_does_not_fit():
     assert _lib.kernel_launches() == n0            # nothing was launched
     torch.cuda.synchronize()
     assert bool((c == 7.0).all())                  # and the output was left alone
+
+
+def test_static_entry_point_with_the_cluster_sum_allocates_nothing_either():
+    """Left to choose its K ranges, the static entry point sums them in thread-block clusters
+    where they fit: no scratch traffic, still no allocation, and the product within the
+    tolerance of the fp32 reference."""
+    lib = _lib.load()
+    _lib.set_splitk_cluster_sum(True)
+    M, K, N = 128, 14336, 4096
+    a_h, b_h = _problem(M, K, N, 404)
+    a, b = a_h.to(DEV), b_h.to(DEV)
+    got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert _call_static(lib, a, b, got, 0) == 0, lib.sgl_last_error()
+    torch.cuda.synchronize()
+    got.fill_(float("nan"))
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    n0 = _lib.kernel_launches()
+    assert _call_static(lib, a, b, got, 0) == 0, lib.sgl_last_error()
+    torch.cuda.synchronize()
+    assert _lib.kernel_launches() - n0 == 1
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    ref32 = orc.matmul_f32(a_h, b_h)
+    assert orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32).ok
+    _lib.device_status()
