@@ -129,10 +129,11 @@ __device__ __forceinline__ bool debug_coord_bad(bool ok, unsigned detail) {
 #define SGL_DBG_COORD_BAD(ok_expr, detail) false
 #endif
 
-// Profiling builds also stamp %globaltimer at eight points of every CTA's life: [0] CTA start,
+// Profiling builds also stamp %globaltimer at points of every CTA's life: [0] CTA start,
 // [1] set-up done, [2] past the dependent-launch wait, [3] first operands landed, [4] last MMA
 // committed, [5] epilogue sees the last accumulator, [6] epilogue's stores have read their
-// staging, [7] teardown done.  What a single-tile launch spends outside its K loop.
+// staging, [7] teardown done; split-K summed in clusters: [8] partial tile in shared memory,
+// [9] all K ranges have reported.  What a single-tile launch spends outside its K loop.
 #ifdef SGL_PROFILE
 __device__ unsigned long long g_tl[512][10];
 #define SGL_TL(slot) g_tl[blockIdx.x & 511][slot] = ptx::globaltimer_ns()
@@ -822,6 +823,17 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           const uint32_t my_range = ptx::cluster_ctarank();
           const uint32_t red = sA;   // the operand ring: every load has landed and been consumed
           const uint32_t my_row = red + static_cast<uint32_t>(q * 32 + lane) * kRedPitchBytes;
+          if (SGL_DBG_COORD_BAD(my_tiles == 1 && static_cast<int>(my_range) == cluster_id % splits &&
+                                    stages * (T::kAStageBytes + T::kBStageBytes) >=
+                                        static_cast<int>(kRedBytes),
+                                my_range)) {
+            // the launch does not have the shape this path relies on (one unit per CTA, cluster
+            // rank = K range, a ring that holds a partial tile): record it and leave; the other
+            // ranges of the tile run into their bounded wait
+            *reinterpret_cast<volatile int*>(abort_flag) = 1;
+            ok = false;
+            break;
+          }
           // (a warp whose 32 rows lie below the last row of the problem keeps nothing; tiles
           // are whole 64-column slabs wide, so the 32-column reads go in pairs: one wait for
           // two TMEM loads)

@@ -63,6 +63,16 @@ CHILD = textwrap.dedent('''
         out[(M, K, N, "gemm")] = matmul_bf16(x, wg).cpu()
         torch.cuda.synchronize()
         _lib.device_status()
+    # split-K with the K ranges summed in thread-block clusters (explicit and chosen ranges)
+    from swiglu_fused_b200.ops import matmul_bf16_splitk
+    g = torch.Generator().manual_seed(5)
+    a = torch.randn((72, 2048), generator=g).to(torch.bfloat16).to(dev)
+    b = (torch.randn((2048, 520), generator=g) * 2048 ** -0.5).to(torch.bfloat16).to(dev)
+    for splits in (4, 0):
+        n0 = _lib.kernel_launches()
+        out[("splitk", splits)] = matmul_bf16_splitk(a, b, splits=splits).cpu()
+        assert _lib.kernel_launches() - n0 == 1, "the K ranges were not summed in their clusters"
+        _lib.device_status()
     torch.save(out, sys.argv[1])
     print("counts" if has_counts else "plain", len(out))
 ''')
