@@ -641,6 +641,16 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   }
   e = cudaLaunchKernelEx(&lc, v.fn, *s.x, *s.w, *s.up, *s.out, p);
   if (nvtx_enabled()) nvtxRangePop();
+  if (e != cudaSuccess && cluster_sum) {
+    // The driver would not place clusters of this size after all (the occupancy query said it
+    // could): remember that for this variant and size and take the two-kernel form instead.
+    cudaGetLastError();
+    {
+      std::lock_guard<std::mutex> lock(g_dev_mutex);
+      info->max_k_clusters[vi][s.splits] = -1;
+    }
+    return launch(s, cfg, info, stream);
+  }
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
   g_launches.fetch_add(1);
   return SGL_OK;
@@ -971,6 +981,8 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   spec.summed = &summed;
   if ((rc = launch(spec, cf, info, stream))) return rc;
   if (summed) return SGL_OK;   // the K ranges met in their cluster: c is written
+  // (spec.splits <= plan.splits: a plan made for clusters that then could not be launched has
+  // fewer ranges than the scratch was sized for)
   const int64_t vecs = M * (N / 8);
   int64_t blocks = (vecs + 255) / 256;
   const int64_t cap = static_cast<int64_t>(info->sm_count) * 8;
@@ -990,7 +1002,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   lc.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(
       &lc, sgl::sum_slots_f32_kernel, static_cast<const float4*>(scratch),
-      static_cast<uint4*>(c), plan.splits, static_cast<int64_t>(plan.slot_rows) * N / 4,
+      static_cast<uint4*>(c), spec.splits, static_cast<int64_t>(plan.slot_rows) * N / 4,
       static_cast<int>(M), static_cast<int>(N / 8), static_cast<int64_t>(N / 4),
       static_cast<int64_t>(ldc / 8));
   if (e != cudaSuccess) return fail_cuda(e, "sum_slots_f32_kernel launch");
