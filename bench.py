@@ -401,7 +401,9 @@ def leg_c4(dev, act_fused, peaks) -> dict:
 
 def leg_neighbours(dev, peaks) -> dict:
     """The callers either side of the path (the rows after the hot path itself): the down
-    projection at decode sizes (unsplit, split-K with caller scratch, cuBLAS), the side-store
+    projection at decode sizes (the plain entry point, which cuts K into ranges summed in
+    thread-block clusters where that pays; the whole-K kernel; split-K with caller scratch;
+    cuBLAS), the side-store
     training forward, the backward elementwise kernel and the two backward GEMMs at the
     headline shape, each beside its library counterpart on the same tensors."""
     from swiglu_fused_b200 import _lib, matmul_bf16, matmul_fused_swiglu
@@ -419,8 +421,14 @@ def leg_neighbours(dev, peaks) -> dict:
         a = ha[:m]
         c = torch.empty((m, Nd), dtype=torch.bfloat16, device=dev)
         scratch = torch.empty(splitk_scratch_bytes(m, Nd, Kd, 0), dtype=torch.uint8, device=dev)
+        def whole_k():
+            before = _lib.set_splitk_cluster_sum(False)
+            matmul_bf16(a, wd, out=c)
+            _lib.set_splitk_cluster_sum(before)
+
         r = rotated_round_robin({
-            "unsplit": lambda: matmul_bf16(a, wd, out=c),
+            "matmul_bf16": lambda: matmul_bf16(a, wd, out=c),
+            "unsplit": whole_k,
             "split_k": lambda: matmul_bf16_splitk(a, wd, out=c, splits=0, scratch=scratch),
             "cublas": lambda: torch.matmul(a, wd, out=c)}, rounds=5, window_s=0.05)
         want = a.float() @ wd.float()

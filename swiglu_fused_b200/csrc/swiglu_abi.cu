@@ -409,7 +409,11 @@ struct LaunchSpec {
   void* sum_out = nullptr;           // bf16 result, row pitch sum_ld
   int64_t sum_ld = 0;
   bool* summed = nullptr;            // set to true when the launch wrote the result itself
+  bool cluster_only = false;         // launch only if the K ranges can be summed in clusters,
+                                     // else return kClustersNotPlaced without launching
 };
+
+constexpr int kClustersNotPlaced = 1;   // internal to this file, never returned to a caller
 
 // Split-K problems whose K ranges can form thread-block clusters are summed inside the GEMM
 // launch through distributed shared memory.  sgl_set_splitk_cluster_sum(0) switches that off
@@ -564,6 +568,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
     cluster_sum = tiles_m * tiles_n <= k_clusters(info, v, vi, s.splits, smem);
   }
   if (s.summed) *s.summed = cluster_sum;
+  if (s.cluster_only && !cluster_sum) return kClustersNotPlaced;
 
   int64_t clusters = info->max_clusters[vi];
   if (cfg.max_ctas > 0 && cfg.max_ctas / cfg.cta_group < clusters)
@@ -914,6 +919,46 @@ int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, Split
   return SGL_OK;
 }
 
+// Split-K plan whose K ranges can be summed in thread-block clusters, for a problem of one
+// 128-row tile row on single-CTA tiles.  Clusters have to be placed whole, so fewer of the
+// larger ones fit; of the tile widths (whole 64-column slabs of b) and 2 to 8 ranges whose
+// clusters all fit at once, the plan that puts the most CTAs to work wins, the wider tile on a
+// tie (a narrower tile re-reads the rows of a more often).  ctas = 0: no such plan.
+struct ClusterPlan {
+  int cols = 0, ranges = 0, k_per_range = 0;
+  int64_t ctas = 0;
+};
+
+int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t N, int64_t K,
+                        ClusterPlan* out) {
+  *out = ClusterPlan();
+  if (cf.cta_group != 1 || cf.max_ctas != 0 || !splitk_cluster_sum_enabled()) return SGL_OK;
+  const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
+  const int vi = variant_index(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
+  int rc;
+  if ((rc = prepare_variant(info, v, vi, cf.cta_group))) return rc;
+  if (!ring_holds_partial_tile(v, cf.stages)) return SGL_OK;
+  const int smem = v.smem_bytes(cf.stages);
+  for (int cols = 256; cols >= 64; cols -= 64) {
+    const int64_t tiles = (N + cols - 1) / cols;
+    for (int n = 8; n >= 2; --n) {
+      int64_t per = (K + n - 1) / n;
+      per = (per + 127) / 128 * 128;
+      const int ranges = static_cast<int>((K + per - 1) / per);
+      if (ranges != n || per < 512) continue;
+      if (tiles > k_clusters(info, v, vi, n, smem)) continue;
+      if (tiles * n > out->ctas) {
+        out->ctas = tiles * n;
+        out->cols = cols;
+        out->ranges = n;
+        out->k_per_range = static_cast<int>(per);
+      }
+      break;   // fewer ranges of the same width only put fewer CTAs to work
+    }
+  }
+  return SGL_OK;
+}
+
 // a @ b through `plan.splits` fp32 partial tiles in `scratch`, then the fp32 slot sum into c.
 int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                       int64_t lda, int64_t ldb, int64_t ldc, const SplitPlan& plan,
@@ -946,33 +991,14 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   spec.slot_rows = plan.slot_rows;
   spec.a_rows = a_box_rows(M, cf.cta_group);
   // Left to choose, and on single-CTA tiles: prefer a plan whose K ranges can meet in a
-  // thread-block cluster (no scratch traffic, no second kernel).  Clusters have to be placed
-  // whole, so fewer of the larger ones fit; the plan that puts the most CTAs to work wins,
-  // the wider tile on a tie (a narrower tile re-reads the rows of a more often).
-  if (plan.automatic && cf.cta_group == 1 && splitk_cluster_sum_enabled() && M <= sgl::kBlockM) {
-    const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
-    const int vi = variant_index(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
-    if ((rc = prepare_variant(info, v, vi, cf.cta_group))) return rc;
-    if (ring_holds_partial_tile(v, cf.stages)) {
-      const int smem = v.smem_bytes(cf.stages);
-      int64_t best_ctas = 0;
-      for (int cols = 256; cols >= 64; cols -= 64) {   // whole 64-column slabs of b
-        const int64_t tiles = (N + cols - 1) / cols;
-        for (int n = 8; n >= 2; --n) {
-          int64_t per = (K + n - 1) / n;
-          per = (per + 127) / 128 * 128;
-          const int ranges = static_cast<int>((K + per - 1) / per);
-          if (ranges != n || per < 512) continue;
-          if (tiles > k_clusters(info, v, vi, n, smem)) continue;
-          if (tiles * n > best_ctas) {
-            best_ctas = tiles * n;
-            spec.acc_cols = cols;
-            spec.splits = n;
-            spec.k_per_split = static_cast<int>(per);
-          }
-          break;   // fewer ranges of the same width only put fewer CTAs to work
-        }
-      }
+  // thread-block cluster (no scratch traffic, no second kernel).
+  if (plan.automatic && cf.cta_group == 1 && M <= sgl::kBlockM) {
+    ClusterPlan cp;
+    if ((rc = plan_cluster_splitk(info, cf, N, K, &cp))) return rc;
+    if (cp.ctas > 0) {
+      spec.acc_cols = cp.cols;
+      spec.splits = cp.ranges;
+      spec.k_per_split = cp.k_per_range;
     }
   }
   bool summed = false;
@@ -1244,8 +1270,7 @@ static int matmul_impl(const void* a, const void* b, void* const* dsts, int n_ds
 
 int sgl_matmul_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, const sgl_config* cfg, void* stream) {
-  void* dst[1] = {c};
-  return matmul_impl(a, b, dst, 1, 0, 0, 0, 0, M, N, K, lda, ldb, ldc, cfg, stream);
+  return sgl_matmul_bf16_ex(a, b, c, M, N, K, lda, ldb, ldc, 0, 0, cfg, stream);
 }
 
 int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
@@ -1295,6 +1320,31 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   spec.a_mnmajor = a_transposed ? 1 : 0;
   spec.b_kmajor = b_transposed ? 1 : 0;
   spec.a_rows = a_transposed ? sgl::kBlockM : a_box_rows(M, cf.cta_group);
+  // A short, deep problem with the library's own configuration (the down projection at decode
+  // batch sizes): cut K into ranges that run as thread-block clusters and sum themselves, if
+  // that puts clearly more SMs to work than the widest grid of whole-K tiles does.  Needs no
+  // scratch, so the plain entry point can do it; the result is deterministic, and differs from
+  // the whole-K kernel's only in the order of the fp32 additions.
+  if (!cfg && !a_transposed && !b_transposed && M <= sgl::kBlockM && K >= 4096) {
+    ClusterPlan cp;
+    if ((rc = plan_cluster_splitk(info, cf, N, K, &cp))) return rc;
+    int whole_cols = sgl::kAccCols;   // what launch() does for whole-K single-CTA tiles
+    while (whole_cols > 64 && ((N + whole_cols - 1) / whole_cols) * 2 <= info->sm_count)
+      whole_cols /= 2;
+    const int64_t whole_ctas = (N + whole_cols - 1) / whole_cols;
+    if (cp.ctas * 4 >= whole_ctas * 5) {
+      LaunchSpec ks = spec;
+      ks.acc_cols = cp.cols;
+      ks.splits = cp.ranges;
+      ks.k_per_split = cp.k_per_range;
+      ks.slot_rows = static_cast<int>((M + 31) / 32 * 32);
+      ks.sum_out = c;
+      ks.sum_ld = ldc;
+      ks.cluster_only = true;
+      rc = launch(ks, cf, info, stream);
+      if (rc != kClustersNotPlaced) return rc;
+    }
+  }
   return launch(spec, cf, info, stream);
 }
 

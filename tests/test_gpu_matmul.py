@@ -220,6 +220,45 @@ def test_splitk_summed_in_the_cluster_gives_the_bits_of_the_two_kernel_form(M, K
     _lib.device_status()
 
 
+def test_plain_matmul_cuts_k_into_clusters_where_that_fills_the_gpu():
+    """The plain entry point needs no scratch for K ranges that sum themselves in thread-block
+    clusters, so with the library's own configuration it takes that plan for short, deep
+    problems (the down projection at decode sizes) and only there: same bits as the split-K
+    entry point left to choose, the whole-K kernel's bits where the whole-K grid already fills
+    the GPU, and the fp32 reference's value either way."""
+    from swiglu_fused_b200.ops import matmul_bf16_splitk
+
+    a, b = problem(64, 14336, 4096, seed=77)
+    ad, bd = a.to(DEV), b.to(DEV)
+    n0 = _lib.kernel_launches()
+    got = matmul_bf16(ad, bd)
+    assert _lib.kernel_launches() - n0 == 1
+    assert torch.equal(got.view(torch.int16), matmul_bf16_splitk(ad, bd).view(torch.int16))
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        whole = matmul_bf16(ad, bd)
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+    both = orc.compare(got, whole)
+    assert both.ok and both.frac_exact >= 0.99 and not torch.equal(got, whole), str(both)
+    ref32 = orc.matmul_f32(a, b)
+    assert orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32).ok
+    # an explicit configuration is taken literally: whole-K tiles
+    assert torch.equal(matmul_bf16(ad, bd, config=TileConfig(1, 64, 0, 8)).view(torch.int16),
+                       whole.view(torch.int16))
+    # 112 whole-K tiles already occupy as many SMs as any cluster plan would: nothing changes
+    a2, b2 = problem(64, 4096, 14336, seed=78)
+    a2d, b2d = a2.to(DEV), b2.to(DEV)
+    got2 = matmul_bf16(a2d, b2d)
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        whole2 = matmul_bf16(a2d, b2d)
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+    assert torch.equal(got2.view(torch.int16), whole2.view(torch.int16))
+    _lib.device_status()
+
+
 def test_reduce_scatter_rejects_bad_row_blocks():
     a = torch.zeros((256, 64), dtype=torch.bfloat16, device=DEV)
     b = torch.zeros((64, 64), dtype=torch.bfloat16, device=DEV)
@@ -242,7 +281,12 @@ def test_short_problems_use_narrow_tiles_and_stay_exact(M, K, N):
     ad, bd = a.to(DEV), b.to(DEV)
     big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
     out = big[1:M + 1, 8:8 + N]
-    matmul_bf16(ad, bd, out=out)                       # default: cta_group 1, narrowed tiles
+    # (whole-K tiles are what this test is about: keep the deep shapes off the cluster plan)
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        matmul_bf16(ad, bd, out=out)                   # default: cta_group 1, narrowed tiles
+    finally:
+        _lib.set_splitk_cluster_sum(before)
     rep = orc.compare(out.cpu(), ref32.to(torch.bfloat16), ref32)
     assert rep.ok, str(rep)
     wide = matmul_bf16(ad, bd, config=TileConfig(2, 64, 0, 8))
