@@ -929,8 +929,8 @@ struct ClusterPlan {
   int64_t ctas = 0;
 };
 
-int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t N, int64_t K,
-                        ClusterPlan* out) {
+int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m, int64_t N,
+                        int64_t K, ClusterPlan* out) {
   *out = ClusterPlan();
   if (cf.cta_group != 1 || cf.max_ctas != 0 || !splitk_cluster_sum_enabled()) return SGL_OK;
   const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
@@ -940,7 +940,7 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t N, int64
   if (!ring_holds_partial_tile(v, cf.stages)) return SGL_OK;
   const int smem = v.smem_bytes(cf.stages);
   for (int cols = 256; cols >= 64; cols -= 64) {
-    const int64_t tiles = (N + cols - 1) / cols;
+    const int64_t tiles = tiles_m * ((N + cols - 1) / cols);
     for (int n = 8; n >= 2; --n) {
       int64_t per = (K + n - 1) / n;
       per = (per + 127) / 128 * 128;
@@ -994,7 +994,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   // thread-block cluster (no scratch traffic, no second kernel).
   if (plan.automatic && cf.cta_group == 1 && M <= sgl::kBlockM) {
     ClusterPlan cp;
-    if ((rc = plan_cluster_splitk(info, cf, N, K, &cp))) return rc;
+    if ((rc = plan_cluster_splitk(info, cf, 1, N, K, &cp))) return rc;
     if (cp.ctas > 0) {
       spec.acc_cols = cp.cols;
       spec.splits = cp.ranges;
@@ -1325,15 +1325,37 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   // that puts clearly more SMs to work than the widest grid of whole-K tiles does.  Needs no
   // scratch, so the plain entry point can do it; the result is deterministic, and differs from
   // the whole-K kernel's only in the order of the fp32 additions.
-  if (!cfg && !a_transposed && !b_transposed && M <= sgl::kBlockM && K >= 4096) {
+  // (Up to 256 rows - two rows of single-CTA tiles instead of one row of CTA pairs - the same
+  // holds: 256 x 14336 x 4096 takes 90 us on 16 whole-K pair tiles.)
+  if (!cfg && !a_transposed && !b_transposed && M <= 2 * sgl::kBlockM && K >= 4096) {
+    sgl_config cf1;   // the library's configuration for single-CTA tiles
+    if ((rc = resolve_config(SGL_FORM_MATMUL, nullptr, sgl::kBlockM, &cf1))) return rc;
+    const int64_t tiles_m = (M + sgl::kBlockM - 1) / sgl::kBlockM;
     ClusterPlan cp;
-    if ((rc = plan_cluster_splitk(info, cf, N, K, &cp))) return rc;
-    int whole_cols = sgl::kAccCols;   // what launch() does for whole-K single-CTA tiles
-    while (whole_cols > 64 && ((N + whole_cols - 1) / whole_cols) * 2 <= info->sm_count)
+    if ((rc = plan_cluster_splitk(info, cf1, tiles_m, N, K, &cp))) return rc;
+    // what launch() does for whole-K tiles: CTA pairs on 256 x 256 tiles above 128 rows, else
+    // single-CTA tiles narrowed while they fit half the SMs
+    int whole_cols = sgl::kAccCols;
+    while (tiles_m == 1 && whole_cols > 64 &&
+           ((N + whole_cols - 1) / whole_cols) * 2 <= info->sm_count)
       whole_cols /= 2;
-    const int64_t whole_ctas = (N + whole_cols - 1) / whole_cols;
+    const int64_t whole_ctas = tiles_m * ((N + whole_cols - 1) / whole_cols);
     if (cp.ctas * 4 >= whole_ctas * 5) {
+      CUtensorMap ta1, tb1;
+      if (tiles_m > 1) {
+        // operand boxes of the single-CTA configuration
+        if ((rc = make_map(&ta1, a, M, K, lda, sgl::kBlockM, 64,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "a")) ||
+            (rc = make_map(&tb1, b, K, N, ldb, cf1.block_k, 64,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, "b")))
+          return rc;
+      }
       LaunchSpec ks = spec;
+      if (tiles_m > 1) {
+        ks.x = &ta1;
+        ks.w = &tb1;
+        ks.a_rows = sgl::kBlockM;
+      }
       ks.acc_cols = cp.cols;
       ks.splits = cp.ranges;
       ks.k_per_split = cp.k_per_range;
@@ -1341,7 +1363,7 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
       ks.sum_out = c;
       ks.sum_ld = ldc;
       ks.cluster_only = true;
-      rc = launch(ks, cf, info, stream);
+      rc = launch(ks, tiles_m > 1 ? cf1 : cf, info, stream);
       if (rc != kClustersNotPlaced) return rc;
     }
   }

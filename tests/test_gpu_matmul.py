@@ -256,6 +256,26 @@ def test_plain_matmul_cuts_k_into_clusters_where_that_fills_the_gpu():
     finally:
         _lib.set_splitk_cluster_sum(before)
     assert torch.equal(got2.view(torch.int16), whole2.view(torch.int16))
+    # 129 to 256 rows: two rows of single-CTA tiles in clusters instead of one row of CTA pairs
+    for (M3, K3, N3) in ((256, 14336, 4096), (136, 8192, 2056)):
+        a3, b3 = problem(M3, K3, N3, seed=M3)
+        a3d, b3d = a3.to(DEV), b3.to(DEV)
+        big = torch.full((M3 + 2, N3 + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+        out3 = big[1:M3 + 1, 8:8 + N3]
+        matmul_bf16(a3d, b3d, out=out3)
+        before = _lib.set_splitk_cluster_sum(False)
+        try:
+            whole3 = matmul_bf16(a3d, b3d)
+        finally:
+            _lib.set_splitk_cluster_sum(before)
+        both = orc.compare(out3.contiguous(), whole3)
+        assert both.ok and both.frac_exact >= 0.99, str(both)
+        assert not torch.equal(out3.contiguous(), whole3)        # it did take the other plan
+        ref32 = orc.matmul_f32(a3, b3)
+        assert orc.compare(out3.cpu(), ref32.to(torch.bfloat16), ref32).ok
+        guard = big.clone()
+        guard[1:M3 + 1, 8:8 + N3] = float("nan")
+        assert torch.isnan(guard).all(), "wrote outside the output"
     _lib.device_status()
 
 
