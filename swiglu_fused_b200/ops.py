@@ -368,6 +368,12 @@ def matmul_bf16(A, B, *, out=None, stream=None, config: TileConfig | None = None
     A : [M, K] bf16, or [K, M] with ``transpose_a`` (read in place, no transpose copy)
     B : [K, N] bf16, or [N, K] with ``transpose_b``
     returns [M, N] bf16.
+
+    Without ``config`` and transposes, problems of up to 256 rows and K >= 4096 (a down
+    projection at decode batch sizes) are cut along K into ranges that run as thread-block
+    clusters and sum themselves through distributed shared memory when that occupies clearly
+    more SMs; the result is deterministic and differs from whole-K tiles only in the order of
+    the fp32 additions (``_lib.set_splitk_cluster_sum(False)`` keeps whole-K tiles).
     """
     _check_matrix(A, "A", allow_empty_rows=not transpose_a)
     _check_matrix(B, "B")
