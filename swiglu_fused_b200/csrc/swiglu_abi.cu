@@ -935,6 +935,19 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m,
   if (cf.cta_group != 1 || cf.max_ctas != 0 || !splitk_cluster_sum_enabled()) return SGL_OK;
   const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
   const int vi = variant_index(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
+  // A decode loop asks for the same problem over and over: remember the last answer.
+  struct Memo {
+    const DeviceInfo* info = nullptr;
+    int vi = -1, stages = 0;
+    int64_t tiles_m = 0, N = 0, K = 0;
+    ClusterPlan plan;
+  };
+  thread_local Memo memo;
+  if (memo.info == info && memo.vi == vi && memo.stages == cf.stages &&
+      memo.tiles_m == tiles_m && memo.N == N && memo.K == K) {
+    *out = memo.plan;
+    return SGL_OK;
+  }
   int rc;
   if ((rc = prepare_variant(info, v, vi, cf.cta_group))) return rc;
   if (!ring_holds_partial_tile(v, cf.stages)) return SGL_OK;
@@ -956,6 +969,13 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m,
       break;   // fewer ranges of the same width only put fewer CTAs to work
     }
   }
+  memo.info = info;
+  memo.vi = vi;
+  memo.stages = cf.stages;
+  memo.tiles_m = tiles_m;
+  memo.N = N;
+  memo.K = K;
+  memo.plan = *out;
   return SGL_OK;
 }
 
