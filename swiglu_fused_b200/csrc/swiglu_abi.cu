@@ -31,6 +31,9 @@ namespace {
 thread_local std::string t_last_error;
 std::atomic<int64_t> g_launches{0};
 std::atomic<uint64_t> g_wait_limit_ns{2000000000ull};
+// Self-checking builds only (sgl_debug_cluster_sum_missing_arrivals): arrivals the barrier of
+// the cluster sum expects on top of those that will come, so that its bounded wait runs out.
+std::atomic<int> g_debug_missing_arrivals{0};
 
 // Tracing, off by default (the reference prints from its tuner and loader unconditionally,
 // swiglu/matmul_silu_mul.py:135,156,159).  SGL_LOG=1 writes one line per kernel launch to
@@ -612,7 +615,7 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
         (static_cast<int64_t>(s.first_dst) * s.reduce_rows / rows_per_tile) % tiles_m);
   }
   p.wait_limit_ns = g_wait_limit_ns.load();
-  p.cluster_sum = cluster_sum ? 1 : 0;
+  p.cluster_sum = cluster_sum ? 1 + 2 * g_debug_missing_arrivals.load() : 0;
   p.sum_out = reinterpret_cast<unsigned long long>(s.sum_out);
   p.sum_ld = s.sum_ld;
 
@@ -1555,6 +1558,18 @@ int sgl_debug_counts(unsigned long long* out) {
   if (e != cudaSuccess) return fail_cuda(e, "cudaDeviceSynchronize");
   e = cudaMemcpyFromSymbol(out, sgl::g_debug_counts, sizeof(unsigned long long) * 512 * 4);
   if (e != cudaSuccess) return fail_cuda(e, "cudaMemcpyFromSymbol(debug counts)");
+  return SGL_OK;
+}
+#endif
+
+#ifdef SGL_DEBUG
+// Self-checking builds only: make the barrier of the split-K cluster sum expect `n` arrivals
+// that never come (0 = normal).  Every CTA's wait then runs out after the wait limit, records
+// status 0x106 and leaves through the closing cluster barrier: the time-out path is exercised
+// without a kernel that stops half way.  Lower the limit first (sgl_set_wait_limit_ns).
+int sgl_debug_cluster_sum_missing_arrivals(int n) {
+  if (n < 0 || n > 4) return fail(SGL_ERR_BAD_ARGUMENT, "n=%d outside [0, 4]", n);
+  g_debug_missing_arrivals.store(n);
   return SGL_OK;
 }
 #endif

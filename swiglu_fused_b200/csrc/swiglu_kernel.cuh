@@ -189,7 +189,8 @@ struct KernelParams {
   // them have done so, sums its share of the tile's elements over the CTAs in K-range order
   // with ld.shared::cluster and writes bf16 straight to the result.  No scratch traffic, no
   // second kernel; the additions are those of the two-launch form, so are the bits.
-  int cluster_sum;              // 0 = off; else out maps are unused and the result goes to:
+  int cluster_sum;              // 0 = off; odd = on (out maps are unused, the result goes to
+                                // sum_out); bits 1.. = extra arrivals its barrier expects
   unsigned long long sum_out;   // address of the bf16 result, element (0, 0)
   long long sum_ld;             // its row pitch, elements
   unsigned long long wait_limit_ns;
@@ -429,7 +430,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       ptx::mbar_init(bar_tempty + 8 * s, kEpiWarps * kCtaGroup);  // one arrive per epilogue warp
     }
     for (int i = 0; i < kEpiWarps * kUpBufs; ++i) ptx::mbar_init(bar_up + 8 * i, 1);
-    if (cluster_sum) ptx::mbar_init(bar_sum, kEpiWarps * p.splits);
+    // (p.cluster_sum >> 1: arrivals that never come - the self-checking build's way of making
+    // this barrier's bounded wait run out; 0 in every other launch)
+    if (cluster_sum) ptx::mbar_init(bar_sum, kEpiWarps * p.splits + (p.cluster_sum >> 1));
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tm_x);
     ptx::prefetch_tensormap(&tm_w);

@@ -73,6 +73,27 @@ CHILD = textwrap.dedent('''
         out[("splitk", splits)] = matmul_bf16_splitk(a, b, splits=splits).cpu()
         assert _lib.kernel_launches() - n0 == 1, "the K ranges were not summed in their clusters"
         _lib.device_status()
+    if hasattr(lib, "sgl_debug_cluster_sum_missing_arrivals"):
+        # the cluster sum's bounded wait: its barrier is told to expect one arrival that never
+        # comes, every CTA's wait runs out after 20 ms, the launch returns, the status names
+        # the wait, and the next launch computes the right product again
+        lib.sgl_debug_cluster_sum_missing_arrivals.restype = C.c_int
+        lib.sgl_debug_cluster_sum_missing_arrivals.argtypes = [C.c_int]
+        _lib.set_wait_limit_ns(20_000_000)
+        _lib.check(lib.sgl_debug_cluster_sum_missing_arrivals(1))
+        matmul_bf16_splitk(a, b, splits=4)
+        torch.cuda.synchronize()
+        try:
+            _lib.device_status()
+            raise SystemExit("the missing arrival went unnoticed")
+        except _lib.SglError as e:
+            assert "106" in str(e), str(e)
+        _lib.check(lib.sgl_debug_cluster_sum_missing_arrivals(0))
+        _lib.set_wait_limit_ns(2_000_000_000)
+        again = matmul_bf16_splitk(a, b, splits=4).cpu()
+        _lib.device_status()
+        assert torch.equal(again.view(torch.int16), out[("splitk", 4)].view(torch.int16))
+        print("cluster-sum wait timed out as told")
     torch.save(out, sys.argv[1])
     print("counts" if has_counts else "plain", len(out))
 ''')
@@ -103,7 +124,8 @@ def test_debug_build_records_nothing_and_matches_the_normal_library(tmp_path):
         except RuntimeError as e:
             pytest.skip(f"debug library not built and no compiler here: {e}")
     a, b = str(tmp_path / "debug.pt"), str(tmp_path / "normal.pt")
-    assert _run(debug_lib, a).startswith("counts")
+    said = _run(debug_lib, a)
+    assert "cluster-sum wait timed out as told" in said and "counts" in said, said
     assert _run(None, b).startswith("plain")
     da, db = torch.load(a), torch.load(b)
     assert da.keys() == db.keys() and len(da) > 20
