@@ -224,6 +224,18 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
  */
 int64_t sgl_matmul_bf16_splitk_scratch_bytes(int64_t M, int64_t N, int64_t K, int splits);
 int sgl_set_splitk_cluster_sum(int enabled);
+/*
+ * The plan the library makes for a problem of up to 256 rows whose K ranges are to be summed in
+ * thread-block clusters, given how many clusters of n CTAs the GPU can hold at once
+ * (clusters_that_fit[n] for n = 2..8; index 0 and 1 unused; what cudaOccupancyMaxActiveClusters
+ * says for the GEMM kernel - 74, 45, 33, 26, 22, 15, 15 on a B200).  Among tile widths of 256,
+ * 192, 128 and 64 columns and 2 to 8 ranges of at least 512 of K whose clusters all fit, the
+ * plan that puts the most CTAs to work wins, the wider tile on a tie.  Returns the number of
+ * CTAs (0 = no such plan) and writes the tile width, the number of ranges and the K extent of
+ * a range (a multiple of 128); negative sgl_status on bad arguments.  No device is touched.
+ */
+int sgl_splitk_cluster_plan(int64_t M, int64_t N, int64_t K, const int* clusters_that_fit,
+                            int* tile_cols, int* ranges, int* k_per_range);
 int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                            int64_t lda, int64_t ldb, int64_t ldc, int splits, void* scratch,
                            int64_t scratch_bytes, const sgl_config* cfg, void* stream);

@@ -63,6 +63,7 @@ EXPORTED_SYMBOLS = (
     "sgl_selftest_wait_timeout",
     "sgl_set_wait_limit_ns",
     "sgl_set_splitk_cluster_sum",
+    "sgl_splitk_cluster_plan",
     "sgl_host_pipeline_create",
     "sgl_host_pipeline_shared_bytes",
     "sgl_host_pipeline_plan",
@@ -238,6 +239,8 @@ def load() -> C.CDLL:
         lib.sgl_set_wait_limit_ns.argtypes = [C.c_uint64]
         lib.sgl_set_splitk_cluster_sum.restype = ip
         lib.sgl_set_splitk_cluster_sum.argtypes = [ip]
+        lib.sgl_splitk_cluster_plan.restype = ip
+        lib.sgl_splitk_cluster_plan.argtypes = [i64, i64, i64, C.POINTER(ip)] + [C.POINTER(ip)] * 3
         lib.sgl_host_pipeline_create.restype = ip
         lib.sgl_host_pipeline_create.argtypes = [ip, i64, i64, i64, i64, i64, ip, cfgp,
                                                  C.POINTER(vp)]
@@ -354,6 +357,20 @@ def set_splitk_cluster_sum(enabled: bool) -> bool:
     the GEMM launch through distributed shared memory (default) or always through scratch
     memory and a second kernel.  Returns the previous setting."""
     return bool(load().sgl_set_splitk_cluster_sum(int(bool(enabled))))
+
+
+B200_CLUSTERS_THAT_FIT = (0, 0, 74, 45, 33, 26, 22, 15, 15)   # GEMM kernel, clusters of n CTAs
+
+
+def splitk_cluster_plan(M: int, N: int, K: int, clusters_that_fit=B200_CLUSTERS_THAT_FIT) -> dict:
+    """The split-K plan for K ranges summed in thread-block clusters (no device needed):
+    ``{"ctas", "tile_cols", "ranges", "k_per_range"}``, ``ctas == 0`` if there is none."""
+    fit = (C.c_int * 9)(*clusters_that_fit)
+    cols, ranges, per = C.c_int(0), C.c_int(0), C.c_int(0)
+    n = load().sgl_splitk_cluster_plan(M, N, K, fit, C.byref(cols), C.byref(ranges), C.byref(per))
+    if n < 0:
+        check(n)
+    return {"ctas": n, "tile_cols": cols.value, "ranges": ranges.value, "k_per_range": per.value}
 
 
 def host_pipeline_plan(M: int, N: int, *, first_rows: int = 0, block_rows: int = 0,

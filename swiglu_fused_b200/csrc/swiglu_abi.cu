@@ -932,6 +932,28 @@ struct ClusterPlan {
   int64_t ctas = 0;
 };
 
+// The choice itself, given how many clusters of n CTAs fit at once (fit[n], n = 2..8).
+void choose_cluster_plan(int64_t tiles_m, int64_t N, int64_t K, const int* fit, ClusterPlan* out) {
+  *out = ClusterPlan();
+  for (int cols = 256; cols >= 64; cols -= 64) {   // whole 64-column slabs of b
+    const int64_t tiles = tiles_m * ((N + cols - 1) / cols);
+    for (int n = 8; n >= 2; --n) {
+      int64_t per = (K + n - 1) / n;
+      per = (per + 127) / 128 * 128;
+      const int ranges = static_cast<int>((K + per - 1) / per);
+      if (ranges != n || per < 512) continue;   // empty or very short ranges
+      if (tiles > fit[n]) continue;
+      if (tiles * n > out->ctas) {
+        out->ctas = tiles * n;
+        out->cols = cols;
+        out->ranges = n;
+        out->k_per_range = static_cast<int>(per);
+      }
+      break;   // fewer ranges of the same width only put fewer CTAs to work
+    }
+  }
+}
+
 int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m, int64_t N,
                         int64_t K, ClusterPlan* out) {
   *out = ClusterPlan();
@@ -955,23 +977,9 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m,
   if ((rc = prepare_variant(info, v, vi, cf.cta_group))) return rc;
   if (!ring_holds_partial_tile(v, cf.stages)) return SGL_OK;
   const int smem = v.smem_bytes(cf.stages);
-  for (int cols = 256; cols >= 64; cols -= 64) {
-    const int64_t tiles = tiles_m * ((N + cols - 1) / cols);
-    for (int n = 8; n >= 2; --n) {
-      int64_t per = (K + n - 1) / n;
-      per = (per + 127) / 128 * 128;
-      const int ranges = static_cast<int>((K + per - 1) / per);
-      if (ranges != n || per < 512) continue;
-      if (tiles > k_clusters(info, v, vi, n, smem)) continue;
-      if (tiles * n > out->ctas) {
-        out->ctas = tiles * n;
-        out->cols = cols;
-        out->ranges = n;
-        out->k_per_range = static_cast<int>(per);
-      }
-      break;   // fewer ranges of the same width only put fewer CTAs to work
-    }
-  }
+  int fit[9] = {};
+  for (int n = 2; n <= 8; ++n) fit[n] = k_clusters(info, v, vi, n, smem);
+  choose_cluster_plan(tiles_m, N, K, fit, out);
   memo.info = info;
   memo.vi = vi;
   memo.stages = cf.stages;
@@ -1105,6 +1113,23 @@ int sgl_matmul_bf16_splitk(const void* a, const void* b, void* c, int64_t M, int
                 static_cast<long long>(scratch_bytes), static_cast<long long>(plan.scratch_bytes),
                 plan.splits);
   return matmul_splitk_run(a, b, c, M, N, K, lda, ldb, ldc, plan, scratch, cfg, info, stream);
+}
+
+int sgl_splitk_cluster_plan(int64_t M, int64_t N, int64_t K, const int* clusters_that_fit,
+                            int* tile_cols, int* ranges, int* k_per_range) {
+  if (!clusters_that_fit || !tile_cols || !ranges || !k_per_range)
+    return fail(SGL_ERR_NULL_POINTER, "NULL argument");
+  if (M < 1 || M > 2 * sgl::kBlockM)
+    return fail(SGL_ERR_BAD_SHAPE, "M=%lld: the cluster plan covers 1 to 256 rows",
+                static_cast<long long>(M));
+  int rc;
+  if ((rc = validate_shape(M, N, K))) return rc;
+  ClusterPlan cp;
+  choose_cluster_plan((M + sgl::kBlockM - 1) / sgl::kBlockM, N, K, clusters_that_fit, &cp);
+  *tile_cols = cp.cols;
+  *ranges = cp.ranges;
+  *k_per_range = cp.k_per_range;
+  return static_cast<int>(cp.ctas);
 }
 
 int sgl_set_splitk_cluster_sum(int enabled) {

@@ -363,3 +363,31 @@ def test_ctypes_prototypes_match_the_header():
                 assert ctype is C.c_uint64, (name, decl, ctype)
             elif decl.startswith("int "):
                 assert ctype is C.c_int, (name, decl, ctype)
+
+
+def test_splitk_cluster_plan_choice():
+    """Which tile width and how many K ranges the library picks when the ranges are to run as
+    thread-block clusters, for a given table of how many clusters fit (a B200's by default)."""
+    plan = _lib.splitk_cluster_plan
+    # decode down projection: 16 tiles of 256 columns would need 16 clusters of 8 (15 fit);
+    # 22 tiles of 192 columns x 6 ranges = 132 CTAs beat 32 x 4 = 128 and 64 x 2 = 128
+    assert plan(64, 4096, 14336) == {"ctas": 132, "tile_cols": 192, "ranges": 6, "k_per_range": 2432}
+    # two rows of tiles double the tile count: 44 tiles of 192 columns x 3 ranges (45 clusters
+    # of 3 fit) beat 32 tiles of 256 columns x 4 ranges = 128
+    assert plan(256, 4096, 14336) == {"ctas": 132, "tile_cols": 192, "ranges": 3, "k_per_range": 4864}
+    # few tiles: the widest tile with the most ranges that still have 512 of K each
+    assert plan(64, 256, 14336) == {"ctas": 32, "tile_cols": 64, "ranges": 8, "k_per_range": 1792}
+    assert plan(16, 512, 1024)["ranges"] == 2 and plan(16, 512, 1024)["k_per_range"] == 512
+    # K too short for two ranges of 512, or more tiles than clusters of two: no plan
+    assert plan(64, 4096, 768)["ctas"] == 0
+    assert plan(64, 28672, 8192)["ctas"] == 0
+    # a GPU that holds no clusters at all
+    assert plan(64, 4096, 14336, clusters_that_fit=(0,) * 9)["ctas"] == 0
+    # ranges are multiples of 128 and none is empty
+    for K in (1024, 1500 // 8 * 8, 4096, 5000 // 8 * 8, 14336):
+        p = plan(64, 1024, K)
+        if p["ctas"]:
+            assert p["k_per_range"] % 128 == 0 and p["k_per_range"] >= 512
+            assert (p["ranges"] - 1) * p["k_per_range"] < K <= p["ranges"] * p["k_per_range"]
+    with pytest.raises(ValueError):
+        plan(300, 4096, 14336)
