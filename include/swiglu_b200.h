@@ -177,9 +177,9 @@ int sgl_matmul_fused_swiglu_gather(const void* x, const void* w, void* h_local,
  * c[M,N] = a[M,K] @ b[K,N], bf16 in, fp32 accumulate, bf16 out: the down projection
  * y = h @ W_down that consumes the stage's output, on the same TMA/tcgen05 pipeline.
  * With cfg == NULL, M <= 256 and K >= 4096 (decode batch sizes) K may be cut into ranges that
- * run as thread-block clusters and sum themselves through distributed shared memory, where that
- * puts at least a quarter more SMs to work than whole-K tiles do (64 x 14336 x 4096: 27 us
- * instead of 80 us; 256 x 14336 x 4096: 46 us instead of 94 us).  The result stays deterministic; against the whole-K kernel only the
+ * run as thread-block clusters and sum themselves through distributed shared memory, where a
+ * CTA then loads at most 4/5 of the operand bytes a whole-K tile does (64 x 14336 x 4096: 27 us
+ * instead of 80 us; 256 x 14336 x 4096: 37 us instead of 82-94 us).  The result stays deterministic; against the whole-K kernel only the
  * order of the fp32 additions differs.  An explicit cfg, sgl_set_splitk_cluster_sum(0) or
  * SGL_SPLITK_CLUSTER_SUM=0 keep whole-K tiles.  The reference stops at h; no counterpart there.
  */
@@ -230,9 +230,10 @@ int sgl_set_splitk_cluster_sum(int enabled);
  * (clusters_that_fit[n] for n = 2..8; index 0 and 1 unused; what cudaOccupancyMaxActiveClusters
  * says for the GEMM kernel - 74, 45, 33, 26, 22, 15, 15 on a B200).  Among tile widths of 256,
  * 192, 128 and 64 columns and 2 to 8 ranges of at least 512 of K whose clusters all fit, the
- * plan that puts the most CTAs to work wins, the wider tile on a tie.  Returns the number of
- * CTAs (0 = no such plan) and writes the tile width, the number of ranges and the K extent of
- * a range (a multiple of 128); negative sgl_status on bad arguments.  No device is touched.
+ * plan whose CTAs each load the fewest operand bytes (K extent of a range x (rows of a +
+ * columns of b)) wins, the wider tile on a tie.  Returns the number of CTAs (0 = no such plan)
+ * and writes the tile width, the number of ranges and the K extent of a range (a multiple of
+ * 128); negative sgl_status on bad arguments.  No device is touched.
  */
 int sgl_splitk_cluster_plan(int64_t M, int64_t N, int64_t K, const int* clusters_that_fit,
                             int* tile_cols, int* ranges, int* k_per_range);

@@ -932,9 +932,14 @@ struct ClusterPlan {
   int64_t ctas = 0;
 };
 
-// The choice itself, given how many clusters of n CTAs fit at once (fit[n], n = 2..8).
-void choose_cluster_plan(int64_t tiles_m, int64_t N, int64_t K, const int* fit, ClusterPlan* out) {
+// The choice itself, given how many clusters of n CTAs fit at once (fit[n], n = 2..8).  These
+// problems are bound by what one SM can pull in, so the plan whose CTAs each load the fewest
+// operand bytes wins: K extent of a range x (rows of a + columns of b); a_rows = rows of a
+// that a tile loads.  On a tie the wider tile, which comes first.
+void choose_cluster_plan(int64_t tiles_m, int a_rows, int64_t N, int64_t K, const int* fit,
+                         ClusterPlan* out) {
   *out = ClusterPlan();
+  int64_t best = 0;
   for (int cols = 256; cols >= 64; cols -= 64) {   // whole 64-column slabs of b
     const int64_t tiles = tiles_m * ((N + cols - 1) / cols);
     for (int n = 8; n >= 2; --n) {
@@ -943,19 +948,21 @@ void choose_cluster_plan(int64_t tiles_m, int64_t N, int64_t K, const int* fit, 
       const int ranges = static_cast<int>((K + per - 1) / per);
       if (ranges != n || per < 512) continue;   // empty or very short ranges
       if (tiles > fit[n]) continue;
-      if (tiles * n > out->ctas) {
+      const int64_t load = per * (a_rows + cols);
+      if (best == 0 || load < best) {
+        best = load;
         out->ctas = tiles * n;
         out->cols = cols;
         out->ranges = n;
         out->k_per_range = static_cast<int>(per);
       }
-      break;   // fewer ranges of the same width only put fewer CTAs to work
+      break;   // fewer ranges of the same width only make every range longer
     }
   }
 }
 
-int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m, int64_t N,
-                        int64_t K, ClusterPlan* out) {
+int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m, int a_rows,
+                        int64_t N, int64_t K, ClusterPlan* out) {
   *out = ClusterPlan();
   if (cf.cta_group != 1 || cf.max_ctas != 0 || !splitk_cluster_sum_enabled()) return SGL_OK;
   const Variant& v = variant(SGL_FORM_MATMUL, cf.cta_group, cf.block_k, 0);
@@ -965,11 +972,12 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m,
     const DeviceInfo* info = nullptr;
     int vi = -1, stages = 0;
     int64_t tiles_m = 0, N = 0, K = 0;
+    int a_rows = 0;
     ClusterPlan plan;
   };
   thread_local Memo memo;
   if (memo.info == info && memo.vi == vi && memo.stages == cf.stages &&
-      memo.tiles_m == tiles_m && memo.N == N && memo.K == K) {
+      memo.tiles_m == tiles_m && memo.a_rows == a_rows && memo.N == N && memo.K == K) {
     *out = memo.plan;
     return SGL_OK;
   }
@@ -979,11 +987,12 @@ int plan_cluster_splitk(DeviceInfo* info, const sgl_config& cf, int64_t tiles_m,
   const int smem = v.smem_bytes(cf.stages);
   int fit[9] = {};
   for (int n = 2; n <= 8; ++n) fit[n] = k_clusters(info, v, vi, n, smem);
-  choose_cluster_plan(tiles_m, N, K, fit, out);
+  choose_cluster_plan(tiles_m, a_rows, N, K, fit, out);
   memo.info = info;
   memo.vi = vi;
   memo.stages = cf.stages;
   memo.tiles_m = tiles_m;
+  memo.a_rows = a_rows;
   memo.N = N;
   memo.K = K;
   memo.plan = *out;
@@ -1025,7 +1034,7 @@ int matmul_splitk_run(const void* a, const void* b, void* c, int64_t M, int64_t 
   // thread-block cluster (no scratch traffic, no second kernel).
   if (plan.automatic && cf.cta_group == 1 && M <= sgl::kBlockM) {
     ClusterPlan cp;
-    if ((rc = plan_cluster_splitk(info, cf, 1, N, K, &cp))) return rc;
+    if ((rc = plan_cluster_splitk(info, cf, 1, a_box_rows(M, 1), N, K, &cp))) return rc;
     if (cp.ctas > 0) {
       spec.acc_cols = cp.cols;
       spec.splits = cp.ranges;
@@ -1125,7 +1134,9 @@ int sgl_splitk_cluster_plan(int64_t M, int64_t N, int64_t K, const int* clusters
   int rc;
   if ((rc = validate_shape(M, N, K))) return rc;
   ClusterPlan cp;
-  choose_cluster_plan((M + sgl::kBlockM - 1) / sgl::kBlockM, N, K, clusters_that_fit, &cp);
+  choose_cluster_plan((M + sgl::kBlockM - 1) / sgl::kBlockM,
+                      M > sgl::kBlockM ? sgl::kBlockM : a_box_rows(M, 1), N, K,
+                      clusters_that_fit, &cp);
   *tile_cols = cp.cols;
   *ranges = cp.ranges;
   *k_per_range = cp.k_per_range;
@@ -1380,15 +1391,19 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
     if ((rc = resolve_config(SGL_FORM_MATMUL, nullptr, sgl::kBlockM, &cf1))) return rc;
     const int64_t tiles_m = (M + sgl::kBlockM - 1) / sgl::kBlockM;
     ClusterPlan cp;
-    if ((rc = plan_cluster_splitk(info, cf1, tiles_m, N, K, &cp))) return rc;
+    const int rows_a = tiles_m > 1 ? sgl::kBlockM : a_box_rows(M, 1);
+    if ((rc = plan_cluster_splitk(info, cf1, tiles_m, rows_a, N, K, &cp))) return rc;
     // what launch() does for whole-K tiles: CTA pairs on 256 x 256 tiles above 128 rows, else
     // single-CTA tiles narrowed while they fit half the SMs
     int whole_cols = sgl::kAccCols;
     while (tiles_m == 1 && whole_cols > 64 &&
            ((N + whole_cols - 1) / whole_cols) * 2 <= info->sm_count)
       whole_cols /= 2;
-    const int64_t whole_ctas = tiles_m * ((N + whole_cols - 1) / whole_cols);
-    if (cp.ctas * 4 >= whole_ctas * 5) {
+    // operand bytes one CTA loads either way (a pair member loads 128 rows of a and half of
+    // the pair's 256 columns of b): the cluster plan has to be a quarter lighter to be taken
+    const int64_t whole_load = K * (rows_a + (tiles_m > 1 ? whole_cols / 2 : whole_cols));
+    const int64_t plan_load = static_cast<int64_t>(cp.k_per_range) * (rows_a + cp.cols);
+    if (cp.ctas > 0 && plan_load * 5 <= whole_load * 4) {
       CUtensorMap ta1, tb1;
       if (tiles_m > 1) {
         // operand boxes of the single-CTA configuration

@@ -370,12 +370,14 @@ def test_splitk_cluster_plan_choice():
     thread-block clusters, for a given table of how many clusters fit (a B200's by default)."""
     plan = _lib.splitk_cluster_plan
     # decode down projection: 16 tiles of 256 columns would need 16 clusters of 8 (15 fit);
-    # 22 tiles of 192 columns x 6 ranges = 132 CTAs beat 32 x 4 = 128 and 64 x 2 = 128
+    # 22 tiles of 192 columns x 6 ranges load 2432 x (64 + 192) operand elements per CTA, less
+    # than 128 columns x 4 ranges (3584 x 192) and 64 columns x 2 ranges (7168 x 128)
     assert plan(64, 4096, 14336) == {"ctas": 132, "tile_cols": 192, "ranges": 6, "k_per_range": 2432}
-    # two rows of tiles double the tile count: 44 tiles of 192 columns x 3 ranges (45 clusters
-    # of 3 fit) beat 32 tiles of 256 columns x 4 ranges = 128
-    assert plan(256, 4096, 14336) == {"ctas": 132, "tile_cols": 192, "ranges": 3, "k_per_range": 4864}
-    # few tiles: the widest tile with the most ranges that still have 512 of K each
+    # two rows of tiles double the tile count: 32 tiles of 256 columns x 4 ranges load
+    # 3584 x (128 + 256) operand elements per CTA, 44 tiles of 192 columns x 3 ranges (more
+    # CTAs) 4864 x (128 + 192): the lighter CTA wins
+    assert plan(256, 4096, 14336) == {"ctas": 128, "tile_cols": 256, "ranges": 4, "k_per_range": 3584}
+    # one tile's worth of columns: narrow tiles, as many ranges as fit
     assert plan(64, 256, 14336) == {"ctas": 32, "tile_cols": 64, "ranges": 8, "k_per_range": 1792}
     assert plan(16, 512, 1024)["ranges"] == 2 and plan(16, 512, 1024)["k_per_range"] == 512
     # K too short for two ranges of 512, or more tiles than clusters of two: no plan
