@@ -96,6 +96,14 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
  * (swiglu/matmul_fused_swiglu.py:85-103,152-172) and the kernels
  * matmul_fused_swiglu_bm128_* (swiglu/_matmul_fused_swiglu.cu:513-533).
  * x is streamed once: both products come from one K loop.
+  *
+ * With cfg == NULL, M <= 128, K >= 4096 and so few 128-column tiles that two-CTA clusters of
+ * them all fit on the GPU at once (a narrow FFN at decode batch sizes) K is cut into 2 to 8
+ * ranges that run as thread-block clusters; the CTAs of a cluster exchange their fp32 partial
+ * tiles through distributed shared memory and each applies silu(gate) * up to the columns it
+ * sums (64 x 4096 x 4096: 16 us instead of 28 us).  Deterministic; against whole-K tiles only the
+ * order of the fp32 additions differs.  An explicit cfg, sgl_set_splitk_cluster_sum(0) or
+ * SGL_SPLITK_CLUSTER_SUM=0 keep whole-K tiles.
  */
 int sgl_matmul_fused_swiglu(const void* x, const void* w, void* h, int64_t M, int64_t N, int64_t K,
                             int64_t ldx, int64_t ldw, int64_t ldh, int64_t up_col0,

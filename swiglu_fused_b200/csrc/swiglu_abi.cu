@@ -565,7 +565,10 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   // Split-K summed in the cluster: the K ranges of a tile are the CTAs of one cluster, every
   // unit has its own CTA, all clusters fit at once, and the ring holds a partial tile.
   bool cluster_sum = false;
-  if (s.sum_out && s.form == SGL_FORM_MATMUL && cfg.cta_group == 1 && s.splits >= 2 &&
+  const bool form_splits = s.form == SGL_FORM_MATMUL ||
+                           (s.form == SGL_FORM_FUSED_SWIGLU && !wide && !s.b_kmajor &&
+                            s.n_dst == 1 && s.peer_mode == 0);
+  if (s.sum_out && form_splits && cfg.cta_group == 1 && s.splits >= 2 &&
       s.splits <= 16 && cfg.max_ctas == 0 && splitk_cluster_sum_enabled() &&
       ring_holds_partial_tile(v, cfg.stages)) {
     cluster_sum = tiles_m * tiles_n <= k_clusters(info, v, vi, s.splits, smem);
@@ -818,6 +821,35 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
     spec.peer_mode = peers->mode;
     spec.n_peer = peers->n;
     spec.peer_ld = ldh;
+  }
+  // A short, deep problem with few tiles (the gate/up stage of a narrow FFN at decode batch
+  // sizes) under the library's own configuration: cut K into as many ranges as still form
+  // clusters that all fit at once; each sums its share of the tile and applies the activation.
+  // Every range then loads 1/n of what the whole-K tile loads.
+  if (!cfg && form == SGL_FORM_FUSED_SWIGLU && !w_is_nk && n_dsts == 1 && !peers &&
+      M <= sgl::kBlockM && c.cta_group == 1 && !c.wide && K >= 4096 &&
+      splitk_cluster_sum_enabled()) {
+    const Variant& v = variant(form, c.cta_group, c.block_k, 0);
+    const int vi = variant_index(form, c.cta_group, c.block_k, 0);
+    if ((rc = prepare_variant(info, v, vi, c.cta_group))) return rc;
+    if (ring_holds_partial_tile(v, c.stages)) {
+      const int64_t tiles = (N + v.out_cols - 1) / v.out_cols;
+      for (int n = 8; n >= 2; --n) {
+        int64_t per = (K + n - 1) / n;
+        per = (per + 127) / 128 * 128;
+        if ((K + per - 1) / per != n || per < 512) continue;
+        if (tiles > k_clusters(info, v, vi, n, v.smem_bytes(c.stages))) continue;
+        LaunchSpec ks = spec;
+        ks.splits = n;
+        ks.k_per_split = static_cast<int>(per);
+        ks.sum_out = h_dsts[0];
+        ks.sum_ld = ldh;
+        ks.cluster_only = true;
+        rc = launch(ks, c, info, stream);
+        if (rc != kClustersNotPlaced) return rc;
+        break;
+      }
+    }
   }
   return launch(spec, c, info, stream);
 }

@@ -42,6 +42,7 @@
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <type_traits>
 #include <cuda_runtime.h>
 
 #include "ptx_sm100.cuh"
@@ -366,7 +367,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const int cluster_id = blockIdx.x / kCtaGroup;
   const int num_clusters = gridDim.x / kCtaGroup;
   // Work units: one per output tile, or (split-K, FORM_GEMM only) one per tile and K range.
-  const int splits = (kForm == FORM_GEMM) ? p.splits : 1;
+  // K may be cut into ranges in the GEMM form and in the fused form on single-CTA tiles
+  constexpr bool kCanSplitK = (kForm == FORM_GEMM) || (kForm == FORM_FUSED && kCtaGroup == 1 && !kWide);
+  const int splits = kCanSplitK ? p.splits : 1;
   const int total_tiles = p.tiles_m * p.tiles_n * splits;
   auto shifted_tile = [&](int t) {
     TileCoord tc = tile_coord(t, p.tiles_m, p.tiles_n, p.group_m, p.group_n);
@@ -409,7 +412,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const uint32_t tmem_slot = bar_up + 8 * kEpiWarps * kUpBufs;
   const uint32_t abort_slot = tmem_slot + 8;
   const uint32_t bar_sum = abort_slot + 8;   // cluster sum: every epilogue warp of every K range
-  const bool cluster_sum = (kForm == FORM_GEMM && kCtaGroup == 1) && p.cluster_sum != 0;
+  const bool cluster_sum = (kCanSplitK && kCtaGroup == 1) && p.cluster_sum != 0;
   // Generic pointers to the two scalar slots.
   uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr =
@@ -720,6 +723,161 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       }
     }
 
+    // Split-K summed in the cluster (one unit per CTA, cluster = the K ranges of one tile): the
+    // epilogue of such a unit.  acc_cols accumulator columns are exchanged; out_cols result
+    // columns come out of them (the same in the GEMM form; in the fused form 256 accumulator
+    // columns, up | gate, give 128 columns of silu(gate) * up).  Returns false after a
+    // time-out, which has been recorded.
+    auto cluster_epilogue = [&](auto fused, int i, int as, uint32_t t_row, int x0, int y,
+                                int acc_cols, int out_cols) -> bool {
+      (void)i;
+      const uint32_t my_range = ptx::cluster_ctarank();
+      const uint32_t red = sA;   // the operand ring: every load has landed and been consumed
+      const uint32_t my_row = red + static_cast<uint32_t>(q * 32 + lane) * kRedPitchBytes;
+      if (SGL_DBG_COORD_BAD(my_tiles == 1 && static_cast<int>(my_range) == cluster_id % splits &&
+                                stages * (T::kAStageBytes + T::kBStageBytes) >=
+                                    static_cast<int>(kRedBytes),
+                            my_range)) {
+        // the launch does not have the shape this path relies on (one unit per CTA, cluster
+        // rank = K range, a ring that holds a partial tile): record it and leave; the other
+        // ranges of the tile run into their bounded wait
+        *reinterpret_cast<volatile int*>(abort_flag) = 1;
+        return false;
+      }
+      // (a warp whose 32 rows lie below the last row of the problem keeps nothing; tiles
+      // are whole 64-column slabs wide, so the 32-column reads go in pairs: one wait for
+      // two TMEM loads)
+      if (y < p.M) {
+#pragma unroll 1
+        for (int u = 0; u < acc_cols / 32; u += 2) {
+          float acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(t_row + u * 32, acc0);
+          ptx::tmem_ld_32x32b_x32(t_row + u * 32 + 32, acc1);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
+                             my_row + static_cast<uint32_t>(u * 32 + 4 * j) * 4u),
+                         "f"(acc0[4 * j]), "f"(acc0[4 * j + 1]), "f"(acc0[4 * j + 2]),
+                         "f"(acc0[4 * j + 3])
+                         : "memory");
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
+                             my_row + static_cast<uint32_t>(u * 32 + 32 + 4 * j) * 4u),
+                         "f"(acc1[4 * j]), "f"(acc1[4 * j + 1]), "f"(acc1[4 * j + 2]),
+                         "f"(acc1[4 * j + 3])
+                         : "memory");
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
+      // This warp's 32 rows are in place: tell every CTA of the cluster (this one
+      // included).  One lane per destination: a cluster-scope release is a fence, and
+      // `splits` of them from one lane in turn cost 2 us.
+      if (lane < splits)
+        ptx::mbar_arrive_release_cluster(ptx::mapa(bar_sum, static_cast<uint32_t>(lane)));
+      if (q == 0 && lane == 0) { SGL_TL(8); }
+      const bool met = ptx::mbar_wait_acquire_cluster(bar_sum, 0, limit, abort_flag);
+      if (q == 0 && lane == 0) { SGL_TL(9); }
+      if (!__all_sync(0xffffffffu, met)) {
+        if (lane == 0) report_error(kErrClusterSumWait, my_range, abort_flag);
+        return false;
+      }
+      // This CTA's share of the tile, in groups of 4 columns, summed over the K ranges in
+      // order starting from 0.f - element by element the additions of sum_slots_f32_kernel.
+      // The loads of a batch of ranges for four groups are issued before the first addition.
+      // (Sending the rows to their owners with st.shared::cluster instead, so that this sum
+      // reads local memory only, measured the same: the exchange itself, about 40 KB per
+      // CTA, is what takes the time.)
+      const int row0 = y - q * 32;
+      const int rows_valid = min(kBlockM, p.M - row0);
+      const int n_vec = min(out_cols, p.N - x0) / 4;
+      const int total = rows_valid * n_vec;
+      const int per = (total + splits - 1) / splits;
+      const int hi = min(total, (static_cast<int>(my_range) + 1) * per);
+      const int te = q * 32 + lane;
+      __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.sum_out);
+      // (fused form: the partial tile holds up in columns [0, 128) and gate in [128, 256); a
+      // group of the result needs both, so half as many groups are in flight)
+      constexpr bool kAct = decltype(fused)::value;
+      constexpr int kItems = kAct ? 2 : 4, kBatch = 8, kEpiThreads = kEpiWarps * 32;
+#pragma unroll 1
+      for (int e0 = static_cast<int>(my_range) * per + te; e0 < hi;
+           e0 += kItems * kEpiThreads) {
+        uint32_t src[kItems];
+        long long dst_off[kItems];
+        bool on[kItems];
+        float4 sum[kItems];
+        float4 gsum[kItems];   // fused form: the gate columns of the same group
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+          const int e = e0 + k * kEpiThreads;
+          on[k] = e < hi;
+          const int ee = on[k] ? e : e0;
+          const int r = ee / n_vec;
+          const int v = ee - r * n_vec;
+          src[k] = red + static_cast<uint32_t>(r) * kRedPitchBytes +
+                   static_cast<uint32_t>(v) * 16u;
+          dst_off[k] = static_cast<long long>(row0 + r) * p.sum_ld + x0 + 4 * v;
+          sum[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+          gsum[k] = sum[k];
+        }
+#pragma unroll 1
+        for (int s0 = 0; s0 < splits; s0 += kBatch) {
+          float4 t[kItems][kBatch];
+          float4 tg[kAct ? kItems : 1][kAct ? kBatch : 1];
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+#pragma unroll
+            for (int k = 0; k < kItems; ++k) {
+              if (s0 + j < splits) {
+                const uint32_t remote = ptx::mapa(src[k], static_cast<uint32_t>(s0 + j));
+                t[k][j] = ptx::ld_shared_cluster_v4(remote);
+                if constexpr (kAct) tg[k][j] = ptx::ld_shared_cluster_v4(remote + T::kGateCol * 4);
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < kBatch; ++j) {
+#pragma unroll
+            for (int k = 0; k < kItems; ++k) {
+              if (s0 + j < splits) {
+                sum[k].x += t[k][j].x;
+                sum[k].y += t[k][j].y;
+                sum[k].z += t[k][j].z;
+                sum[k].w += t[k][j].w;
+                if constexpr (kAct) {
+                  gsum[k].x += tg[k][j].x;
+                  gsum[k].y += tg[k][j].y;
+                  gsum[k].z += tg[k][j].z;
+                  gsum[k].w += tg[k][j].w;
+                }
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < kItems; ++k) {
+          if (on[k]) {
+            uint2 o;
+            if constexpr (kAct) {
+              o.x = pack_bf16x2(silu_mul(gsum[k].x, sum[k].x), silu_mul(gsum[k].y, sum[k].y));
+              o.y = pack_bf16x2(silu_mul(gsum[k].z, sum[k].z), silu_mul(gsum[k].w, sum[k].w));
+            } else {
+              o.x = pack_bf16x2(sum[k].x, sum[k].y);
+              o.y = pack_bf16x2(sum[k].z, sum[k].w);
+            }
+            *reinterpret_cast<uint2*>(outp + dst_off[k]) = o;
+          }
+        }
+      }
+      return true;
+    };
+
     bool ok = true;
     int g = 0;            // running chunk index
     int gemm_stores = 0;  // FORM_GEMM: staging buffers filled so far
@@ -823,132 +981,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int units32 = tile_cols / 32;
         if (cluster_sum) {
           // ---- split-K summed in the cluster (one unit per CTA, cluster = the tile's ranges) ----
-          const uint32_t my_range = ptx::cluster_ctarank();
-          const uint32_t red = sA;   // the operand ring: every load has landed and been consumed
-          const uint32_t my_row = red + static_cast<uint32_t>(q * 32 + lane) * kRedPitchBytes;
-          if (SGL_DBG_COORD_BAD(my_tiles == 1 && static_cast<int>(my_range) == cluster_id % splits &&
-                                    stages * (T::kAStageBytes + T::kBStageBytes) >=
-                                        static_cast<int>(kRedBytes),
-                                my_range)) {
-            // the launch does not have the shape this path relies on (one unit per CTA, cluster
-            // rank = K range, a ring that holds a partial tile): record it and leave; the other
-            // ranges of the tile run into their bounded wait
-            *reinterpret_cast<volatile int*>(abort_flag) = 1;
+          if (!cluster_epilogue(std::false_type{}, i, as, t_row, x0, y, tile_cols, tile_cols)) {
             ok = false;
             break;
-          }
-          // (a warp whose 32 rows lie below the last row of the problem keeps nothing; tiles
-          // are whole 64-column slabs wide, so the 32-column reads go in pairs: one wait for
-          // two TMEM loads)
-          if (y < p.M) {
-#pragma unroll 1
-            for (int u = 0; u < units32; u += 2) {
-              float acc0[32], acc1[32];
-              ptx::tmem_ld_32x32b_x32(t_row + u * 32, acc0);
-              ptx::tmem_ld_32x32b_x32(t_row + u * 32 + 32, acc1);
-              ptx::tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
-                                 my_row + static_cast<uint32_t>(u * 32 + 4 * j) * 4u),
-                             "f"(acc0[4 * j]), "f"(acc0[4 * j + 1]), "f"(acc0[4 * j + 2]),
-                             "f"(acc0[4 * j + 3])
-                             : "memory");
-              }
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(
-                                 my_row + static_cast<uint32_t>(u * 32 + 32 + 4 * j) * 4u),
-                             "f"(acc1[4 * j]), "f"(acc1[4 * j + 1]), "f"(acc1[4 * j + 2]),
-                             "f"(acc1[4 * j + 3])
-                             : "memory");
-              }
-            }
-          }
-          ptx::tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_cluster(tempty_leader_base + 8 * as);
-          // This warp's 32 rows are in place: tell every CTA of the cluster (this one
-          // included).  One lane per destination: a cluster-scope release is a fence, and
-          // `splits` of them from one lane in turn cost 2 us.
-          if (lane < splits)
-            ptx::mbar_arrive_release_cluster(ptx::mapa(bar_sum, static_cast<uint32_t>(lane)));
-          if (q == 0 && lane == 0) { SGL_TL(8); }
-          const bool met = ptx::mbar_wait_acquire_cluster(bar_sum, 0, limit, abort_flag);
-          if (q == 0 && lane == 0) { SGL_TL(9); }
-          if (!__all_sync(0xffffffffu, met)) {
-            if (lane == 0) report_error(kErrClusterSumWait, my_range, abort_flag);
-            ok = false;
-            break;
-          }
-          // This CTA's share of the tile, in groups of 4 columns, summed over the K ranges in
-          // order starting from 0.f - element by element the additions of sum_slots_f32_kernel.
-          // The loads of a batch of ranges for four groups are issued before the first addition.
-          // (Sending the rows to their owners with st.shared::cluster instead, so that this sum
-          // reads local memory only, measured the same: the exchange itself, about 40 KB per
-          // CTA, is what takes the time.)
-          const int row0 = y - q * 32;
-          const int rows_valid = min(kBlockM, p.M - row0);
-          const int n_vec = min(tile_cols, p.N - x0) / 4;
-          const int total = rows_valid * n_vec;
-          const int per = (total + splits - 1) / splits;
-          const int hi = min(total, (static_cast<int>(my_range) + 1) * per);
-          const int te = q * 32 + lane;
-          __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.sum_out);
-          constexpr int kItems = 4, kBatch = 8, kEpiThreads = kEpiWarps * 32;
-#pragma unroll 1
-          for (int e0 = static_cast<int>(my_range) * per + te; e0 < hi;
-               e0 += kItems * kEpiThreads) {
-            uint32_t src[kItems];
-            long long dst_off[kItems];
-            bool on[kItems];
-            float4 sum[kItems];
-#pragma unroll
-            for (int k = 0; k < kItems; ++k) {
-              const int e = e0 + k * kEpiThreads;
-              on[k] = e < hi;
-              const int ee = on[k] ? e : e0;
-              const int r = ee / n_vec;
-              const int v = ee - r * n_vec;
-              src[k] = red + static_cast<uint32_t>(r) * kRedPitchBytes +
-                       static_cast<uint32_t>(v) * 16u;
-              dst_off[k] = static_cast<long long>(row0 + r) * p.sum_ld + x0 + 4 * v;
-              sum[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll 1
-            for (int s0 = 0; s0 < splits; s0 += kBatch) {
-              float4 t[kItems][kBatch];
-#pragma unroll
-              for (int j = 0; j < kBatch; ++j) {
-#pragma unroll
-                for (int k = 0; k < kItems; ++k) {
-                  if (s0 + j < splits)
-                    t[k][j] = ptx::ld_shared_cluster_v4(
-                        ptx::mapa(src[k], static_cast<uint32_t>(s0 + j)));
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < kBatch; ++j) {
-#pragma unroll
-                for (int k = 0; k < kItems; ++k) {
-                  if (s0 + j < splits) {
-                    sum[k].x += t[k][j].x;
-                    sum[k].y += t[k][j].y;
-                    sum[k].z += t[k][j].z;
-                    sum[k].w += t[k][j].w;
-                  }
-                }
-              }
-            }
-#pragma unroll
-            for (int k = 0; k < kItems; ++k) {
-              if (on[k]) {
-                uint2 o;
-                o.x = pack_bf16x2(sum[k].x, sum[k].y);
-                o.y = pack_bf16x2(sum[k].z, sum[k].w);
-                *reinterpret_cast<uint2*>(outp + dst_off[k]) = o;
-              }
-            }
           }
         } else {
         uint32_t nbuf = out_buf0;
@@ -1020,6 +1055,18 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
         }  // cluster sum / stores
       } else {
+      if constexpr (kForm == FORM_FUSED && kCanSplitK) {
+        if (cluster_sum) {
+          int x0, y0;
+          chunk_xy(g, x0, y0);
+          g += T::kChunksPerTile;
+          if (!cluster_epilogue(std::true_type{}, i, as, t_row, x0, y0, kAccCols, T::kOutCols)) {
+            ok = false;
+            break;
+          }
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < T::kChunksPerTile; ++c, ++g) {
         int x, y;

@@ -462,3 +462,54 @@ def test_wide_tiles_give_the_same_bits(M, K, N):
         assert torch.equal(b[:, c0:c0 + n].contiguous().view(torch.int16), win.view(torch.int16))
     with pytest.raises(ValueError):       # wide tiles exist for CTA pairs with BLOCK_K 64 only
         matmul_fused_swiglu(x, w, config=TileConfig(2, 128, 0, 8, 0, 0, 0, 1))
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 4096, 4096), (16, 4096, 5632), (100, 8192, 1000), (128, 4096, 256),
+                                    (8, 16384, 520)])
+def test_narrow_fused_problems_cut_k_into_clusters(M, K, N):
+    """A gate/up stage with few tiles at decode sizes (up to 128 rows, K >= 4096, the library's
+    own configuration): K is cut into ranges that run as thread-block clusters; each CTA sums
+    its share of the tile over the ranges and applies silu(gate) * up.  One launch, the fp32
+    reference's value (the sum order differs from the whole-K kernel's, the per-element
+    arithmetic after it does not), and nothing outside the output is touched; column windows
+    and strided outputs included."""
+    inp = make_inputs(M, K, N, form="fused_swiglu", seed=M + K + N)
+    x, w = inp["x"].to(DEV), inp["w"].to(DEV)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = big[1:M + 1, 8:8 + N]
+    n0 = _lib.kernel_launches()
+    for _ in range(3):
+        matmul_fused_swiglu(x, w, out=out)
+    torch.cuda.synchronize()
+    assert _lib.kernel_launches() - n0 == 3
+    _lib.device_status()
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        whole = matmul_fused_swiglu(x, w)
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+    got = out.contiguous()
+    ref64 = orc.fused_swiglu_exact(inp["x"], inp["w"])
+    rep = orc.compare(got.cpu(), ref64.to(torch.bfloat16), ref64, k_depth=K)
+    assert rep.ok, str(rep)
+    # two kernels that each sit within one ulp of the exact value can be two apart
+    both = orc.compare(got, whole, k_depth=K)
+    assert both.n_nonfinite == 0 and both.frac_within_1ulp >= 0.99 and \
+        both.max_floored_rel <= 2 * orc.MAX_FLOORED_REL_ERR, str(both)
+    assert not torch.equal(got, whole), "the whole-K kernel ran: no cluster plan was taken"
+    guard = big.clone()
+    guard[1:M + 1, 8:8 + N] = float("nan")
+    assert torch.isnan(guard).all(), "wrote outside the output"
+    # a column window of the packed weight (what a column-parallel rank computes)
+    if N >= 512:
+        c0, n = 128, 264
+        win = matmul_fused_swiglu(x, w, up_col0=c0, gate_col0=N + c0, n_out=n)
+        # (fewer tiles, so possibly more K ranges than the full width got: same value, not
+        # necessarily the same bits)
+        rep = orc.compare(win, got[:, c0:c0 + n].contiguous(), k_depth=K)
+        assert rep.n_nonfinite == 0 and rep.frac_within_1ulp >= 0.99 and \
+            rep.max_floored_rel <= 2 * orc.MAX_FLOORED_REL_ERR, str(rep)
+    # an explicit configuration is taken literally: whole-K tiles
+    lit = matmul_fused_swiglu(x, w, config=TileConfig(1, 64, 0, 8))
+    assert torch.equal(lit.view(torch.int16), whole.view(torch.int16))
+    _lib.device_status()
