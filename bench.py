@@ -440,6 +440,34 @@ def leg_neighbours(dev, peaks) -> dict:
     out["down_proj_decode_14336x4096"] = dec
     del wd, ha
 
+    # a narrow gate/up stage at decode size: few tiles, so the fused form cuts K into ranges
+    # that run as thread-block clusters (beside its own whole-K tiles and the library pair)
+    Mn, Kn, Nn = 64, 4096, 4096
+    xn = torch.randn((Mn, Kn), dtype=torch.bfloat16, device=dev, generator=g)
+    wn = torch.empty((Kn, 2 * Nn), dtype=torch.bfloat16, device=dev).normal_(0, Kn ** -0.5,
+                                                                            generator=g)
+    hn = torch.empty((Mn, Nn), dtype=torch.bfloat16, device=dev)
+
+    def narrow_whole_k():
+        before = _lib.set_splitk_cluster_sum(False)
+        matmul_fused_swiglu(xn, wn, out=hn)
+        _lib.set_splitk_cluster_sum(before)
+
+    def narrow_cublas():
+        pre = xn @ wn
+        return torch.nn.functional.silu(pre[:, Nn:]) * pre[:, :Nn]
+
+    r = rotated_round_robin({
+        "this_build": lambda: matmul_fused_swiglu(xn, wn, out=hn),
+        "whole_k_tiles": narrow_whole_k,
+        "cublas_plus_eager_act": narrow_cublas}, rounds=5, window_s=0.05)
+    matmul_fused_swiglu(xn, wn, out=hn)
+    want = narrow_cublas().float()
+    r["max_err_over_scale"] = ((hn.float() - want).abs().max() / want.abs().max()).item()
+    r["hbm_frac"] = 2.0 * Kn * 2 * Nn / (r["this_build"]["median"] * 1e-3) / 1e9 / peaks["hbm_gbs"]
+    out["fused_narrow_decode_64x4096x4096"] = r
+    del xn, wn, hn
+
     # training side at the headline shape
     import torch.nn.functional as F
     M, K, N = M_TOTAL, K_DIM, N_OUT

@@ -198,6 +198,12 @@ def matmul_fused_swiglu(A, W, *, out=None, stream=None, config: TileConfig | Non
 
     ``w_layout="nk"``: W is the checkpoint (``nn.Linear``) layout ``[2N, K]`` = ``[W_up^T ;
     W_gate^T]`` and is consumed as is (no transpose); the window arguments then count rows.
+
+    Without ``config``, problems of up to 128 rows with K >= 4096 and few tiles (a narrow FFN at
+    decode batch sizes) are cut along K into ranges that run as thread-block clusters; the CTAs
+    of a cluster exchange their partial tiles through distributed shared memory and apply the
+    activation to the columns they sum.  Deterministic; ``_lib.set_splitk_cluster_sum(False)``
+    keeps whole-K tiles.
     """
     if w_layout not in ("kn", "nk"):
         raise ValueError(f"w_layout must be 'kn' or 'nk', got {w_layout!r}")
