@@ -954,11 +954,10 @@ int plan_splitk(int64_t M, int64_t N, int64_t K, int splits, int sm_count, Split
   return SGL_OK;
 }
 
-// Split-K plan whose K ranges can be summed in thread-block clusters, for a problem of one
-// 128-row tile row on single-CTA tiles.  Clusters have to be placed whole, so fewer of the
-// larger ones fit; of the tile widths (whole 64-column slabs of b) and 2 to 8 ranges whose
-// clusters all fit at once, the plan that puts the most CTAs to work wins, the wider tile on a
-// tie (a narrower tile re-reads the rows of a more often).  ctas = 0: no such plan.
+// Split-K plan whose K ranges can be summed in thread-block clusters, for a problem of one or
+// two rows of single-CTA tiles: tile width (whole 64-column slabs of b), number of ranges and
+// K extent of a range.  Clusters have to be placed whole, so fewer of the larger ones fit; only
+// plans whose clusters all fit at once are considered.  ctas = 0: no such plan.
 struct ClusterPlan {
   int cols = 0, ranges = 0, k_per_range = 0;
   int64_t ctas = 0;
@@ -1413,9 +1412,9 @@ int sgl_matmul_bf16_ex(const void* a, const void* b, void* c, int64_t M, int64_t
   spec.a_rows = a_transposed ? sgl::kBlockM : a_box_rows(M, cf.cta_group);
   // A short, deep problem with the library's own configuration (the down projection at decode
   // batch sizes): cut K into ranges that run as thread-block clusters and sum themselves, if
-  // that puts clearly more SMs to work than the widest grid of whole-K tiles does.  Needs no
-  // scratch, so the plain entry point can do it; the result is deterministic, and differs from
-  // the whole-K kernel's only in the order of the fp32 additions.
+  // a CTA then has clearly less to load than a CTA of the whole-K grid.  Needs no scratch, so
+  // the plain entry point can do it; the result is deterministic, and differs from the whole-K
+  // kernel's only in the order of the fp32 additions.
   // (Up to 256 rows - two rows of single-CTA tiles instead of one row of CTA pairs - the same
   // holds: 256 x 14336 x 4096 takes 90 us on 16 whole-K pair tiles.)
   if (!cfg && !a_transposed && !b_transposed && M <= 2 * sgl::kBlockM && K >= 4096) {
