@@ -393,3 +393,12 @@ def test_splitk_cluster_plan_choice():
             assert (p["ranges"] - 1) * p["k_per_range"] < K <= p["ranges"] * p["k_per_range"]
     with pytest.raises(ValueError):
         plan(300, 4096, 14336)
+
+
+def test_cluster_sum_switch_returns_the_previous_setting():
+    was = _lib.set_splitk_cluster_sum(False)
+    try:
+        assert _lib.set_splitk_cluster_sum(True) is False
+        assert _lib.set_splitk_cluster_sum(True) is True
+    finally:
+        _lib.set_splitk_cluster_sum(was)
