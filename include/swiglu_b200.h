@@ -101,7 +101,7 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
  * them all fit on the GPU at once (a narrow FFN at decode batch sizes) K is cut into 2 to 8
  * ranges that run as thread-block clusters; the CTAs of a cluster exchange their fp32 partial
  * tiles through distributed shared memory and each applies silu(gate) * up to the columns it
- * sums (64 x 4096 x 4096: 16 us instead of 28 us).  Deterministic; against whole-K tiles only the
+ * sums (64 x 4096 x 4096: 18 us instead of 30 us).  Deterministic; against whole-K tiles only the
  * order of the fp32 additions differs.  An explicit cfg, sgl_set_splitk_cluster_sum(0) or
  * SGL_SPLITK_CLUSTER_SUM=0 keep whole-K tiles.
  */

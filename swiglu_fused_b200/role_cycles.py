@@ -1,7 +1,7 @@
 """Cycle accounting of the kernel's roles (developer tool).
 
     python -m swiglu_fused_b200.role_cycles [--form fused_swiglu|fused_swiglu_save|silu_mul] [--rows M]
-                                            [--block-k 64|128] [--group-m G] [--timeline]
+                                            [--block-k 64|128] [--group-m G] [--timeline] [--auto]
     torchrun --nproc-per-node W -m swiglu_fused_b200.role_cycles --k 8192 --cols 28672 \
              --gather none|tma|stores|multicast      # column-parallel over W GPUs, rank 0 reports
 
@@ -55,6 +55,10 @@ def main() -> None:
     ap.add_argument("--n", "--cols", dest="n", type=int, default=12288)
     ap.add_argument("--block-k", type=int, default=0, help="0 = the default configuration")
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--auto", action="store_true",
+                    help="pass no configuration: the library chooses, which for short, deep "
+                         "problems means K ranges summed in thread-block clusters (read the "
+                         "timeline then; the per-k-block figures assume whole-K tiles)")
     ap.add_argument("--timeline", action="store_true",
                     help="also print where a CTA's time goes outside the K loop (set-up, first "
                          "operands, epilogue, teardown): %%globaltimer stamps of the last launch")
@@ -113,10 +117,10 @@ def main() -> None:
                 sharding.fused_swiglu_n_sharded_fused_gather(x, w, sym, mode=args.gather, config=cfg)
     elif args.form == "fused_swiglu":
         def run():
-            matmul_fused_swiglu(x, w, out=out, config=cfg)
+            matmul_fused_swiglu(x, w, out=out, config=None if args.auto else cfg)
     elif args.form == "down":
         def run():
-            matmul_bf16(x, w, out=out, config=cfg)
+            matmul_bf16(x, w, out=out, config=None if args.auto else cfg)
     elif args.form == "down_splitk":
         from .ops import matmul_bf16_splitk, splitk_scratch_bytes
         scratch = torch.empty(splitk_scratch_bytes(M, N, K), dtype=torch.uint8, device=dev)
