@@ -83,6 +83,10 @@ typedef struct sgl_config {
  * Replaces matmul_silu_mul / _launch (swiglu/matmul_silu_mul.py:78-95,142-161)
  * and the kernels matmul_silu_mul_bm128_* (swiglu/_matmul_silu_mul.cu:657-681).
  * cfg may be NULL: the built-in tile table chooses.
+  *
+ * With cfg == NULL, M <= 128, K >= 4096 and few 256-column tiles, K is cut into ranges that run
+ * as thread-block clusters, as described for sgl_matmul_fused_swiglu below; the CTA that sums a
+ * group of gate columns reads up for it and applies the activation.
  */
 int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void* h, int64_t M,
                         int64_t N, int64_t K, int64_t ldx, int64_t ldw, int64_t ldup, int64_t ldh,

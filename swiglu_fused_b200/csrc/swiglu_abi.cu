@@ -412,6 +412,8 @@ struct LaunchSpec {
   void* sum_out = nullptr;           // bf16 result, row pitch sum_ld
   int64_t sum_ld = 0;
   bool* summed = nullptr;            // set to true when the launch wrote the result itself
+  const void* up_raw = nullptr;      // silu_mul form summed in clusters: up, row pitch up_ld
+  int64_t up_ld = 0;
   bool cluster_only = false;         // launch only if the K ranges can be summed in clusters,
                                      // else return kClustersNotPlaced without launching
 };
@@ -567,7 +569,8 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   bool cluster_sum = false;
   const bool form_splits = s.form == SGL_FORM_MATMUL ||
                            (s.form == SGL_FORM_FUSED_SWIGLU && !wide && !s.b_kmajor &&
-                            s.n_dst == 1 && s.peer_mode == 0);
+                            s.n_dst == 1 && s.peer_mode == 0) ||
+                           (s.form == SGL_FORM_SILU_MUL && s.up_raw && s.n_dst == 1);
   if (s.sum_out && form_splits && cfg.cta_group == 1 && s.splits >= 2 &&
       s.splits <= 16 && cfg.max_ctas == 0 && splitk_cluster_sum_enabled() &&
       ring_holds_partial_tile(v, cfg.stages)) {
@@ -621,6 +624,8 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   p.cluster_sum = cluster_sum ? 1 + 2 * g_debug_missing_arrivals.load() : 0;
   p.sum_out = reinterpret_cast<unsigned long long>(s.sum_out);
   p.sum_ld = s.sum_ld;
+  p.up_raw = reinterpret_cast<unsigned long long>(s.up_raw);
+  p.up_ld = s.up_ld;
 
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(static_cast<unsigned>(clusters * cfg.cta_group), 1, 1);
@@ -665,6 +670,37 @@ int launch(const LaunchSpec& s, const sgl_config& cfg, DeviceInfo* info, void* s
   if (e != cudaSuccess) return fail_cuda(e, "cudaLaunchKernelEx");
   g_launches.fetch_add(1);
   return SGL_OK;
+}
+
+// A short, deep activation-form problem with few tiles (the gate/up stage of a narrow FFN at
+// decode batch sizes) under the library's own configuration: cut K into as many ranges as still
+// form clusters that all fit at once; each CTA sums its share of the tile and applies the
+// activation.  Every range then loads 1/n of what the whole-K tile loads.  Returns
+// kClustersNotPlaced if nothing was launched (the caller then launches whole-K tiles).
+int launch_in_clusters_if_narrow(LaunchSpec ks, const sgl_config& c, DeviceInfo* info,
+                                 void* stream, void* out, int64_t ld_out) {
+  if (ks.M > sgl::kBlockM || c.cta_group != 1 || c.wide || ks.K < 4096 || c.max_ctas != 0 ||
+      !splitk_cluster_sum_enabled())
+    return kClustersNotPlaced;
+  const Variant& v = variant(ks.form, c.cta_group, c.block_k, 0);
+  const int vi = variant_index(ks.form, c.cta_group, c.block_k, 0);
+  int rc;
+  if ((rc = prepare_variant(info, v, vi, c.cta_group))) return rc;
+  if (!ring_holds_partial_tile(v, c.stages)) return kClustersNotPlaced;
+  const int64_t tiles = (ks.N + v.out_cols - 1) / v.out_cols;
+  for (int n = 8; n >= 2; --n) {
+    int64_t per = (ks.K + n - 1) / n;
+    per = (per + 127) / 128 * 128;
+    if ((ks.K + per - 1) / per != n || per < 512) continue;
+    if (tiles > k_clusters(info, v, vi, n, v.smem_bytes(c.stages))) continue;
+    ks.splits = n;
+    ks.k_per_split = static_cast<int>(per);
+    ks.sum_out = out;
+    ks.sum_ld = ld_out;
+    ks.cluster_only = true;
+    return launch(ks, c, info, stream);
+  }
+  return kClustersNotPlaced;
 }
 
 int check_device(DeviceInfo** info) {
@@ -726,6 +762,13 @@ int sgl_matmul_silu_mul(const void* x, const void* w_gate, const void* up, void*
   spec.N = N;
   spec.K = K;
   spec.a_rows = a_box_rows(M, c.cta_group);
+  if (!cfg) {
+    LaunchSpec ks = spec;
+    ks.up_raw = up;
+    ks.up_ld = ldup;
+    rc = launch_in_clusters_if_narrow(ks, c, info, stream, h, ldh);
+    if (rc != kClustersNotPlaced) return rc;
+  }
   return launch(spec, c, info, stream);
 }
 
@@ -822,34 +865,9 @@ static int fused_swiglu_impl(const void* x, const void* w, int w_is_nk, void* co
     spec.n_peer = peers->n;
     spec.peer_ld = ldh;
   }
-  // A short, deep problem with few tiles (the gate/up stage of a narrow FFN at decode batch
-  // sizes) under the library's own configuration: cut K into as many ranges as still form
-  // clusters that all fit at once; each sums its share of the tile and applies the activation.
-  // Every range then loads 1/n of what the whole-K tile loads.
-  if (!cfg && form == SGL_FORM_FUSED_SWIGLU && !w_is_nk && n_dsts == 1 && !peers &&
-      M <= sgl::kBlockM && c.cta_group == 1 && !c.wide && K >= 4096 &&
-      splitk_cluster_sum_enabled()) {
-    const Variant& v = variant(form, c.cta_group, c.block_k, 0);
-    const int vi = variant_index(form, c.cta_group, c.block_k, 0);
-    if ((rc = prepare_variant(info, v, vi, c.cta_group))) return rc;
-    if (ring_holds_partial_tile(v, c.stages)) {
-      const int64_t tiles = (N + v.out_cols - 1) / v.out_cols;
-      for (int n = 8; n >= 2; --n) {
-        int64_t per = (K + n - 1) / n;
-        per = (per + 127) / 128 * 128;
-        if ((K + per - 1) / per != n || per < 512) continue;
-        if (tiles > k_clusters(info, v, vi, n, v.smem_bytes(c.stages))) continue;
-        LaunchSpec ks = spec;
-        ks.splits = n;
-        ks.k_per_split = static_cast<int>(per);
-        ks.sum_out = h_dsts[0];
-        ks.sum_ld = ldh;
-        ks.cluster_only = true;
-        rc = launch(ks, c, info, stream);
-        if (rc != kClustersNotPlaced) return rc;
-        break;
-      }
-    }
+  if (!cfg && form == SGL_FORM_FUSED_SWIGLU && !w_is_nk && n_dsts == 1 && !peers) {
+    rc = launch_in_clusters_if_narrow(spec, c, info, stream, h_dsts[0], ldh);
+    if (rc != kClustersNotPlaced) return rc;
   }
   return launch(spec, c, info, stream);
 }

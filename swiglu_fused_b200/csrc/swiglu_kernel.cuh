@@ -192,6 +192,8 @@ struct KernelParams {
   // second kernel; the additions are those of the two-launch form, so are the bits.
   int cluster_sum;              // 0 = off; odd = on (out maps are unused, the result goes to
                                 // sum_out); bits 1.. = extra arrivals its barrier expects
+  unsigned long long up_raw;    // silu_mul form summed in clusters: address of up (0, 0), which
+  long long up_ld;              // the CTA that sums a group of columns reads with plain loads
   unsigned long long sum_out;   // address of the bf16 result, element (0, 0)
   long long sum_ld;             // its row pitch, elements
   unsigned long long wait_limit_ns;
@@ -368,7 +370,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
   const int num_clusters = gridDim.x / kCtaGroup;
   // Work units: one per output tile, or (split-K, FORM_GEMM only) one per tile and K range.
   // K may be cut into ranges in the GEMM form and in the fused form on single-CTA tiles
-  constexpr bool kCanSplitK = (kForm == FORM_GEMM) || (kForm == FORM_FUSED && kCtaGroup == 1 && !kWide);
+  constexpr bool kCanSplitK =
+      (kForm == FORM_GEMM) || (kForm == FORM_FUSED && kCtaGroup == 1 && !kWide) ||
+      (kForm == FORM_SILU_MUL && kCtaGroup == 1);
   const int splits = kCanSplitK ? p.splits : 1;
   const int total_tiles = p.tiles_m * p.tiles_n * splits;
   auto shifted_tile = [&](int t) {
@@ -715,7 +719,7 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
                               pol_up);
     };
     if constexpr (kForm == FORM_SILU_MUL) {
-      if (lane == 0) {
+      if (lane == 0 && !cluster_sum) {
         // In-place staging refills a buffer only after its store has drained, so it runs
         // one chunk ahead; separate staging runs kUpBufs chunks ahead.
         const int ahead = kInPlace ? 1 : kUpBufs;
@@ -728,7 +732,9 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
     // columns come out of them (the same in the GEMM form; in the fused form 256 accumulator
     // columns, up | gate, give 128 columns of silu(gate) * up).  Returns false after a
     // time-out, which has been recorded.
-    auto cluster_epilogue = [&](auto fused, int i, int as, uint32_t t_row, int x0, int y,
+    // mode (a std::integral_constant): 0 = plain sum (GEMM form), 1 = fused form, 2 = silu_mul
+    // form (256 gate columns summed, up read from global memory by the CTA that sums).
+    auto cluster_epilogue = [&](auto mode, int i, int as, uint32_t t_row, int x0, int y,
                                 int acc_cols, int out_cols) -> bool {
       (void)i;
       const uint32_t my_range = ptx::cluster_ctarank();
@@ -803,7 +809,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
       __nv_bfloat16* outp = reinterpret_cast<__nv_bfloat16*>(p.sum_out);
       // (fused form: the partial tile holds up in columns [0, 128) and gate in [128, 256); a
       // group of the result needs both, so half as many groups are in flight)
-      constexpr bool kAct = decltype(fused)::value;
+      constexpr bool kAct = decltype(mode)::value == 1;
+      constexpr bool kUpFromGlobal = decltype(mode)::value == 2;
       constexpr int kItems = kAct ? 2 : 4, kBatch = 8, kEpiThreads = kEpiWarps * 32;
 #pragma unroll 1
       for (int e0 = static_cast<int>(my_range) * per + te; e0 < hi;
@@ -825,6 +832,14 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
           dst_off[k] = static_cast<long long>(row0 + r) * p.sum_ld + x0 + 4 * v;
           sum[k] = make_float4(0.f, 0.f, 0.f, 0.f);
           gsum[k] = sum[k];
+          if constexpr (kUpFromGlobal) {
+            // four bf16 of up for this group, fetched now so that they are here when the sum is
+            const uint2 u4 = __ldg(reinterpret_cast<const uint2*>(
+                reinterpret_cast<const __nv_bfloat16*>(p.up_raw) +
+                static_cast<long long>(row0 + r) * p.up_ld + x0 + 4 * v));
+            gsum[k] = make_float4(__uint_as_float(u4.x << 16), __uint_as_float(u4.x & 0xffff0000u),
+                                  __uint_as_float(u4.y << 16), __uint_as_float(u4.y & 0xffff0000u));
+          }
         }
 #pragma unroll 1
         for (int s0 = 0; s0 < splits; s0 += kBatch) {
@@ -867,6 +882,10 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
             if constexpr (kAct) {
               o.x = pack_bf16x2(silu_mul(gsum[k].x, sum[k].x), silu_mul(gsum[k].y, sum[k].y));
               o.y = pack_bf16x2(silu_mul(gsum[k].z, sum[k].z), silu_mul(gsum[k].w, sum[k].w));
+            } else if constexpr (kUpFromGlobal) {
+              // sum = the gate pre-activation, gsum = up
+              o.x = pack_bf16x2(silu_mul(sum[k].x, gsum[k].x), silu_mul(sum[k].y, gsum[k].y));
+              o.y = pack_bf16x2(silu_mul(sum[k].z, gsum[k].z), silu_mul(sum[k].w, gsum[k].w));
             } else {
               o.x = pack_bf16x2(sum[k].x, sum[k].y);
               o.y = pack_bf16x2(sum[k].z, sum[k].w);
@@ -981,7 +1000,8 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         const int units32 = tile_cols / 32;
         if (cluster_sum) {
           // ---- split-K summed in the cluster (one unit per CTA, cluster = the tile's ranges) ----
-          if (!cluster_epilogue(std::false_type{}, i, as, t_row, x0, y, tile_cols, tile_cols)) {
+          if (!cluster_epilogue(std::integral_constant<int, 0>{}, i, as, t_row, x0, y, tile_cols,
+                                tile_cols)) {
             ok = false;
             break;
           }
@@ -1055,12 +1075,13 @@ swiglu_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ 
         }
         }  // cluster sum / stores
       } else {
-      if constexpr (kForm == FORM_FUSED && kCanSplitK) {
+      if constexpr ((kForm == FORM_FUSED || kForm == FORM_SILU_MUL) && kCanSplitK) {
         if (cluster_sum) {
           int x0, y0;
           chunk_xy(g, x0, y0);
           g += T::kChunksPerTile;
-          if (!cluster_epilogue(std::true_type{}, i, as, t_row, x0, y0, kAccCols, T::kOutCols)) {
+          if (!cluster_epilogue(std::integral_constant<int, kForm == FORM_FUSED ? 1 : 2>{}, i, as,
+                                t_row, x0, y0, kAccCols, T::kOutCols)) {
             ok = false;
             break;
           }

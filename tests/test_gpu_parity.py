@@ -513,3 +513,41 @@ def test_narrow_fused_problems_cut_k_into_clusters(M, K, N):
     lit = matmul_fused_swiglu(x, w, config=TileConfig(1, 64, 0, 8))
     assert torch.equal(lit.view(torch.int16), whole.view(torch.int16))
     _lib.device_status()
+
+
+@pytest.mark.parametrize("M,K,N", [(64, 4096, 4096), (16, 8192, 1000), (128, 4096, 520), (72, 16384, 256)])
+def test_narrow_silu_mul_problems_cut_k_into_clusters(M, K, N):
+    """The same plan in the silu_mul form: the K ranges of a 256-column tile run as a thread-block
+    cluster, the gate pre-activation is summed over them and the CTA that sums a group of
+    columns reads `up` for it from global memory and applies silu(gate) * up."""
+    x, wg, up = silu_mul_problem(M, K, N, seed=M + K + N)
+    xd, wd, ud = x.to(DEV), wg.to(DEV), up.to(DEV)
+    big = torch.full((M + 2, N + 16), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = big[1:M + 1, 8:8 + N]
+    upbig = torch.zeros((M, N + 24), dtype=torch.bfloat16, device=DEV)   # a strided `up`
+    upbig[:, 8:8 + N] = ud
+    n0 = _lib.kernel_launches()
+    for _ in range(3):
+        matmul_silu_mul(xd, wd, upbig[:, 8:8 + N], out=out)
+    torch.cuda.synchronize()
+    assert _lib.kernel_launches() - n0 == 3
+    _lib.device_status()
+    before = _lib.set_splitk_cluster_sum(False)
+    try:
+        whole = matmul_silu_mul(xd, wd, ud)
+    finally:
+        _lib.set_splitk_cluster_sum(before)
+    got = out.contiguous()
+    ref32 = orc.silu_mul_f32(x, wg, up)
+    rep = orc.compare(got.cpu(), ref32.to(torch.bfloat16), ref32, k_depth=K)
+    assert rep.ok, str(rep)
+    both = orc.compare(got, whole, k_depth=K)
+    assert both.n_nonfinite == 0 and both.frac_within_1ulp >= 0.99 and \
+        both.max_floored_rel <= 2 * orc.MAX_FLOORED_REL_ERR, str(both)
+    assert not torch.equal(got, whole), "the whole-K kernel ran: no cluster plan was taken"
+    guard = big.clone()
+    guard[1:M + 1, 8:8 + N] = float("nan")
+    assert torch.isnan(guard).all(), "wrote outside the output"
+    lit = matmul_silu_mul(xd, wd, ud, config=TileConfig(1, 64, 0, 8))
+    assert torch.equal(lit.view(torch.int16), whole.view(torch.int16))
+    _lib.device_status()
