@@ -151,7 +151,7 @@ def matmul_silu_mul(A, B_gate, up, *, out=None, stream=None, config: TileConfig 
     B_gate : [K, N] bf16
     up     : [M, N] bf16  (precomputed x @ W_up)
     returns: [M, N] bf16
-    
+
     Without ``config``, narrow problems at decode sizes (up to 128 rows, K >= 4096, few tiles)
     take the cluster plan described for ``matmul_fused_swiglu``.
     """
